@@ -1,0 +1,338 @@
+/*
+ * tqb200.h -- C ABI of the B200 TurboQuant engine (libtqb200.so).
+ *
+ * Plain pointers and sizes only.  Every pointer named "device" must be valid on the
+ * CUDA device that is current when the call is made; launches are asynchronous on the
+ * given stream unless stated otherwise.  Functions returning `int` return a tqb_status;
+ * the `void` symbols of section 1 keep the reference's own signatures so that a Rust
+ * `extern "C"` block written for the reference links unchanged.
+ *
+ * Citations are file:line inside the reference crate turboquant-rs 0.3.1.
+ */
+#ifndef TQB200_H
+#define TQB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* cudaStream_t / CUstream, passed as an opaque pointer (src/cache/cuda/ffi.rs:7). */
+typedef void *tqb_stream_t;
+
+/* Status codes.  1..5 mirror TurboQuantError (src/error.rs:4-29). */
+typedef enum tqb_status {
+    TQB_OK = 0,
+    TQB_ERR_INVALID_DIMENSION = 1,   /* InvalidDimension: dim not a power of two / not a multiple of 32 */
+    TQB_ERR_UNSUPPORTED_BITS = 2,    /* UnsupportedBits */
+    TQB_ERR_DIMENSION_MISMATCH = 3,  /* DimensionMismatch */
+    TQB_ERR_LAYER_OUT_OF_RANGE = 4,  /* LayerOutOfRange */
+    TQB_ERR_RANGE_OUT_OF_BOUNDS = 5, /* RangeOutOfBounds */
+    TQB_ERR_NULL_POINTER = 6,
+    TQB_ERR_INVALID_ARGUMENT = 7,
+    TQB_ERR_MISALIGNED = 8,
+    TQB_ERR_UNSUPPORTED = 9,         /* valid for the reference, outside what this build covers */
+    TQB_ERR_CUDA = 10,               /* a CUDA call failed; see tqb_last_cuda_error() */
+    TQB_ERR_OUT_OF_MEMORY = 11,
+    TQB_ERR_TOO_LARGE = 12           /* exceeds a fixed capacity of the called entry point */
+} tqb_status;
+
+const char *tqb_status_string(int status);
+/* cudaError_t of the last failing CUDA call made by this library on the calling thread. */
+int tqb_last_cuda_error(void);
+/* Library version, for the loader's sanity check. */
+int tqb_version(void);
+
+/* Element types accepted for K, V, Q and outputs. */
+typedef enum tqb_dtype { TQB_F32 = 0, TQB_F16 = 1, TQB_BF16 = 2 } tqb_dtype;
+/* QuantNormMode (src/cache/config.rs:21-31). */
+typedef enum tqb_norm_mode { TQB_MAXNORM = 0, TQB_L2NORM = 1 } tqb_norm_mode;
+/* outlier_blocks = usize::MAX in the reference (src/cache/config.rs:49-50). */
+#define TQB_ALL_BLOCKS (-1)
+
+/* =====================================================================================
+ * 1. The reference's own FFI (src/cache/cuda/ffi.rs:10-79), same names and arguments.
+ *    Defined in the reference at tq_dequant_kernel.cu:104, tq_quant_kernel.cu:416,441,
+ *    tq_attention_kernel.cu:337.  All pointers are device pointers.  `void`, no error
+ *    report, early return on zero counts -- exactly the reference's convention; the
+ *    tqb_* twins in section 2 do the same work and return a status.
+ * ===================================================================================== */
+void tq_dequant_batch(const uint8_t *packed_indices, const uint16_t *scales, const float *codebook,
+                      const float *sign_pattern, float *output, int32_t num_blocks, int32_t block_size,
+                      int32_t bits, int32_t bytes_per_block, tqb_stream_t stream);
+
+void tq_quant_maxnorm_batch(const float *rotated_input, const float *boundaries, uint8_t *packed_out,
+                            uint16_t *scales_out, int32_t num_blocks, int32_t block_size, int32_t bits,
+                            int32_t num_boundaries, int32_t bytes_per_block, float outer_centroid,
+                            float scale_sign, tqb_stream_t stream);
+
+void tq_pack_indices(const uint8_t *indices, uint8_t *packed_out, int32_t num_vectors, int32_t block_size,
+                     int32_t bits, int32_t bytes_per_block, tqb_stream_t stream);
+
+void tq_fused_attention(const float *q, const uint8_t *k_indices, const uint16_t *k_scales,
+                        const uint8_t *v_indices, const uint16_t *v_scales, const float *codebook,
+                        const float *sign_pattern, float *output, float *partial_out, float *partial_max,
+                        float *partial_sum, const uint8_t *qjl_signs, const uint16_t *qjl_residual_norms,
+                        const float *rq, int32_t qjl_enabled, int32_t num_attention_heads,
+                        int32_t num_kv_heads, int32_t head_dim, int32_t kv_len, int32_t kv_stride,
+                        int32_t packed_dim, int32_t num_qblocks, int32_t bits, float softmax_scale,
+                        int32_t num_partitions, tqb_stream_t stream);
+
+/* =====================================================================================
+ * 2. Status-returning twins of section 1 (same arguments, validated before any launch).
+ * ===================================================================================== */
+int tqb_dequant_batch(const uint8_t *packed_indices, const uint16_t *scales, const float *codebook,
+                      const float *sign_pattern, float *output, int32_t num_blocks, int32_t block_size,
+                      int32_t bits, int32_t bytes_per_block, tqb_stream_t stream);
+int tqb_quant_maxnorm_batch(const float *rotated_input, const float *boundaries, uint8_t *packed_out,
+                            uint16_t *scales_out, int32_t num_blocks, int32_t block_size, int32_t bits,
+                            int32_t num_boundaries, int32_t bytes_per_block, float outer_centroid,
+                            float scale_sign, tqb_stream_t stream);
+int tqb_pack_indices(const uint8_t *indices, uint8_t *packed_out, int32_t num_vectors, int32_t block_size,
+                     int32_t bits, int32_t bytes_per_block, tqb_stream_t stream);
+int tqb_fused_attention(const float *q, const uint8_t *k_indices, const uint16_t *k_scales,
+                        const uint8_t *v_indices, const uint16_t *v_scales, const float *codebook,
+                        const float *sign_pattern, float *output, float *partial_out, float *partial_max,
+                        float *partial_sum, const uint8_t *qjl_signs, const uint16_t *qjl_residual_norms,
+                        const float *rq, int32_t qjl_enabled, int32_t num_attention_heads,
+                        int32_t num_kv_heads, int32_t head_dim, int32_t kv_len, int32_t kv_stride,
+                        int32_t packed_dim, int32_t num_qblocks, int32_t bits, float softmax_scale,
+                        int32_t num_partitions, tqb_stream_t stream);
+
+/* =====================================================================================
+ * 3. Whole-vector format of the core crate, batched over n vectors resident on the device.
+ *    Storage is the flat layout of PackedImport (src/attention.rs:147-166):
+ *      packed  [n, tqb_packed_bytes(bits, dim)]  u8   bit stream of src/packed/mod.rs:242-309
+ *      scales  [n]                               u16  IEEE f16 bits of the L2 norm
+ *      signs   [n, dim/8]                        u8   QJL sign bits, LSB first
+ *      rnorms  [n]                               u16  f16 bits of the residual norm
+ * ===================================================================================== */
+
+/* TurboQuantConfig (src/packed/mod.rs:93-139): bits in {2,3,4}, dim a power of two.
+ * This build carries the reference's twelve static codebooks (src/codebook/tables.rs),
+ * i.e. dim in {32, 64, 128, 256}; other powers of two return TQB_ERR_UNSUPPORTED. */
+typedef struct tqb_config {
+    int32_t bits;
+    int32_t dim;
+    uint64_t rotation_seed;
+} tqb_config;
+
+int tqb_config_validate(const tqb_config *cfg);
+/* Bytes of the packed index stream for `count` codes (src/packed/indices.rs). */
+size_t tqb_packed_bytes(int32_t bits, size_t count);
+/* get_codebook (src/codebook/mod.rs:118-122): copies 2^bits centroids and 2^bits-1
+ * boundaries (f64) to host arrays. */
+int tqb_get_codebook(int32_t bits, int32_t dim, double *centroids, double *boundaries);
+/* generate_sign_pattern (src/rotation.rs:60-70), host output. */
+int tqb_generate_sign_pattern(int32_t dim, uint64_t seed, float *out);
+
+/* quantize_vec over a batch (src/quantize.rs:142-157).  x: device [n, dim] f32. */
+int tqb_quantize_batch(const tqb_config *cfg, const float *x, int64_t n, uint8_t *packed, uint16_t *scales,
+                       tqb_stream_t stream);
+/* dequantize_vec over a batch (src/quantize.rs:207-239).  out: device [n, dim] f32. */
+int tqb_dequantize_batch(const tqb_config *cfg, const uint8_t *packed, const uint16_t *scales, int64_t n,
+                         float *out, tqb_stream_t stream);
+/* dequantize_rotated (src/quantize.rs:306-316): no inverse rotation. */
+int tqb_dequantize_rotated_batch(const tqb_config *cfg, const uint8_t *packed, const uint16_t *scales,
+                                 int64_t n, float *out, tqb_stream_t stream);
+
+/* The hash Rademacher matrix of src/qjl.rs:143-171 as a bit matrix: host output
+ * [dim, dim/32] u32, bit c%32 of word [row, c/32] set when the entry is -1/sqrt(dim).
+ * The QJL kernels read it from a device copy that the caller owns. */
+int tqb_qjl_rademacher_bits(int32_t dim, uint64_t qjl_seed, uint32_t *host_out);
+
+/* quantize_with_qjl over a batch (src/qjl.rs:355-377): cfg->bits is the TOTAL width
+ * (3 or 4); the polar stage uses bits-1.  rbits: device bit matrix (see above). */
+int tqb_qjl_quantize_batch(const tqb_config *cfg, const uint32_t *rbits, const float *x, int64_t n,
+                           uint8_t *packed, uint16_t *scales, uint8_t *signs, uint16_t *rnorms,
+                           tqb_stream_t stream);
+/* precompute_query_projections (src/qjl.rs:488-492) for nq queries: rq [nq, dim]. */
+int tqb_qjl_query_projections(int32_t dim, const uint32_t *rbits, const float *q, int64_t nq, float *rq,
+                              tqb_stream_t stream);
+/* QuantizedKVCache::attention_scores (src/attention.rs:319-353): raw, unscaled,
+ * un-softmaxed scores [n] for one query.  cfg->bits is the total width. */
+int tqb_qjl_attention_scores(const tqb_config *cfg, const float *q, const float *rq, const uint8_t *packed,
+                             const uint16_t *scales, const uint8_t *signs, const uint16_t *rnorms, int64_t n,
+                             float *scores, tqb_stream_t stream);
+/* QuantizedKVCache::weighted_values (src/attention.rs:371-408): out [dim] = sum_i w[i] *
+ * dequantize(polar part of value i).  scratch: device, tqb_weighted_values_scratch_bytes(). */
+size_t tqb_weighted_values_scratch_bytes(int32_t dim);
+int tqb_weighted_values(const tqb_config *cfg, const float *w, const uint8_t *packed, const uint16_t *scales,
+                        int64_t n, float *out, void *scratch, size_t scratch_bytes, tqb_stream_t stream);
+
+/* =====================================================================================
+ * 4. Block-32 format of the cache module ("PQ" / "PQO" / "TQ" caches).
+ *      indices [rows, head_dim*bits/8] u8, scales [rows, head_dim/32] u16 (f16 bits; a
+ *      negative scale marks a block coded with the outlier codebook,
+ *      src/cache/storage.rs:122-125, src/cache/quantize_tensor.rs:68-70).
+ * ===================================================================================== */
+
+/* CacheConfig (src/cache/config.rs:52-66) plus the two seeds (config.rs:15,18) and a
+ * batch count (the reference is batch 1; equal-length sequences fold into heads). */
+typedef struct tqb_cache_config {
+    int32_t bits;           /* 3 or 4 */
+    int32_t head_dim;       /* multiple of 32 */
+    int32_t num_kv_heads;
+    int32_t num_layers;
+    int32_t norm_mode;      /* tqb_norm_mode */
+    int32_t outlier_blocks; /* TQB_ALL_BLOCKS = PQO, 0 = PQ/TQ */
+    int32_t batch;          /* >= 1 */
+    int32_t reserved;
+    uint64_t rotation_seed; /* unused for block size 32 (fixed pattern), kept for parity */
+    uint64_t qjl_seed;
+} tqb_cache_config;
+
+/* build_codebooks (src/cache/precomputed/codebooks.rs:18-88): host output of the
+ * codebook with 2^cb_bits entries for the norm mode; returns the entry count or <0. */
+int tqb_block_codebook(int32_t cb_bits, int32_t norm_mode, float *centroids, float *boundaries);
+/* The fixed 32-entry sign pattern (src/cache/precomputed/rotation.rs:16-20), host output. */
+void tqb_block_sign_pattern(float *out32);
+
+/* polar_quantize (src/cache/quantize_tensor.rs:40-79) with the rotation fused in
+ * (replaces the sgemm at src/cache/cuda/quantize.rs:111-113 + tq_quant_maxnorm_batch).
+ * x: device [n, head_dim] of x_dtype, rows x_row_stride elements apart (0 = dense).
+ * Row i is written to output row  (i / rows_per_group) * out_group_stride + out_row_offset
+ * + i % rows_per_group  -- with rows_per_group = new tokens, out_group_stride = capacity
+ * and out_row_offset = old length this is CompressedStorage::append
+ * (src/cache/storage.rs:145-172) without a staging copy.  rows_per_group = 0 means
+ * dense output (row i -> i). */
+int tqb_block_quantize(int32_t bits, int32_t head_dim, int32_t norm_mode, int32_t outlier_blocks,
+                       const void *x, int32_t x_dtype, int64_t n, int64_t x_row_stride, uint8_t *indices,
+                       uint16_t *scales, int64_t rows_per_group, int64_t out_group_stride,
+                       int64_t out_row_offset, tqb_stream_t stream);
+
+/* polar_dequantize (src/cache/quantize_tensor.rs:179-220).  Input row mapping as above
+ * (rows_per_group = 0: dense); out: device [n, head_dim] of out_dtype, dense. */
+int tqb_block_dequantize(int32_t bits, int32_t head_dim, int32_t norm_mode, int32_t outlier_blocks,
+                         const uint8_t *indices, const uint16_t *scales, int64_t n, int64_t rows_per_group,
+                         int64_t in_group_stride, int64_t in_row_offset, void *out, int32_t out_dtype,
+                         tqb_stream_t stream);
+
+/* Fused decode attention over the packed cache (tq_attention_kernel.cu:63-392,
+ * src/cache/cuda/attention.rs:41-174), one query token per head.
+ *   q, out      [num_q_heads, head_dim]   (batch folded into heads: query head h reads KV
+ *                                          head h / (num_q_heads / num_kv_heads))
+ *   k/v_indices [num_kv_heads, kv_stride, head_dim*bits/8], k/v_scales [.., head_dim/32]
+ *   scratch     device, >= tqb_decode_scratch_bytes(...); holds the split-K partials.
+ * With lse_out != NULL the per-head (max, sum) pair is written to lse_out[num_q_heads][2]
+ * and `out` receives the UN-normalised output (f32 only): the shard-local result that a
+ * sequence-parallel caller gathers and merges with tqb_lse_combine(). */
+typedef struct tqb_decode_params {
+    const void *q;
+    const uint8_t *k_indices;
+    const uint16_t *k_scales;
+    const uint8_t *v_indices;
+    const uint16_t *v_scales;
+    void *out;
+    float *lse_out;
+    void *scratch;
+    size_t scratch_bytes;
+    const uint8_t *qjl_signs;     /* [num_kv_heads, kv_stride, head_dim/8] or NULL */
+    const uint16_t *qjl_norms;    /* [num_kv_heads, kv_stride] or NULL */
+    const float *rq;              /* [num_q_heads, head_dim] or NULL */
+    int32_t qjl_enabled;
+    int32_t q_dtype;
+    int32_t out_dtype;
+    int32_t bits;
+    int32_t head_dim;
+    int32_t norm_mode;
+    int32_t outlier_blocks;
+    int32_t num_q_heads;
+    int32_t num_kv_heads;
+    int32_t kv_len;
+    int32_t kv_stride;
+    int32_t num_partitions;       /* 0 = let the library choose */
+    float softmax_scale;
+    int32_t reserved;
+} tqb_decode_params;
+
+/* Partitions the library would use for this shape, and the scratch it then needs. */
+int32_t tqb_decode_num_partitions(int32_t num_kv_heads, int32_t kv_len);
+size_t tqb_decode_scratch_bytes(int32_t num_q_heads, int32_t head_dim, int32_t num_partitions);
+int tqb_decode_attention(const tqb_decode_params *p, tqb_stream_t stream);
+
+/* Log-sum-exp merge of `num_shards` shard-local results (the algebra of
+ * tq_fused_attention_reduce, tq_attention_kernel.cu:299-332, one level up):
+ *   partial_out [num_shards, num_q_heads, head_dim] f32 un-normalised,
+ *   partial_lse [num_shards, num_q_heads, 2] f32 (max, sum);  out [num_q_heads, head_dim]. */
+int tqb_lse_combine(const float *partial_out, const float *partial_lse, int32_t num_shards,
+                    int32_t num_q_heads, int32_t head_dim, void *out, int32_t out_dtype, tqb_stream_t stream);
+
+/* =====================================================================================
+ * 5. Host-side cache objects (own their device memory; calls are ordered on `stream`).
+ * ===================================================================================== */
+
+/* PqoCache (src/cache/pqo.rs:21-236) over CompressedStorage (src/cache/storage.rs:24-203).
+ * k, v: [batch, num_kv_heads, new_tokens, head_dim]; q: [batch, num_q_heads, 1, head_dim];
+ * `host_buffers` != 0 means k, v, q and the outputs are HOST pointers (pinned or pageable)
+ * and the copies are part of the call. */
+typedef struct tqb_pqo_cache tqb_pqo_cache;
+int tqb_pqo_cache_create(const tqb_cache_config *cfg, tqb_pqo_cache **out);
+void tqb_pqo_cache_destroy(tqb_pqo_cache *c);
+/* prefill (pqo.rs:184-200): quantize and append.  When the layer already held tokens and
+ * k_out/v_out are non-NULL they receive the full dequantized cache
+ * [batch, num_kv_heads, seq_len, head_dim]; on the first call the reference returns the
+ * original tensors, so nothing is written. */
+int tqb_pqo_cache_prefill(tqb_pqo_cache *c, int32_t layer, const void *k, const void *v, int32_t dtype,
+                          int32_t new_tokens, void *k_out, void *v_out, int32_t host_buffers,
+                          tqb_stream_t stream);
+/* decode (pqo.rs:202-222): append one token per sequence, then fused attention;
+ * out: [batch, num_q_heads, 1, head_dim] of `dtype` (DecodeOutput::Fused). */
+int tqb_pqo_cache_decode(tqb_pqo_cache *c, int32_t layer, const void *k, const void *v, const void *q,
+                         int32_t dtype, int32_t num_q_heads, float softmax_scale, void *out,
+                         int32_t host_buffers, tqb_stream_t stream);
+/* dequantize_full (pqo.rs:176-180): [batch, num_kv_heads, seq_len, head_dim] of `dtype`. */
+int tqb_pqo_cache_dequantize_full(tqb_pqo_cache *c, int32_t layer, void *k_out, void *v_out, int32_t dtype,
+                                  int32_t host_buffers, tqb_stream_t stream);
+int64_t tqb_pqo_cache_seq_len(const tqb_pqo_cache *c, int32_t layer);
+int64_t tqb_pqo_cache_capacity(const tqb_pqo_cache *c, int32_t layer);
+int tqb_pqo_cache_reset(tqb_pqo_cache *c);
+size_t tqb_pqo_cache_memory_usage(const tqb_pqo_cache *c);
+/* Device pointers of one layer's storage (k_indices, k_scales, v_indices, v_scales). */
+int tqb_pqo_cache_layer_ptrs(const tqb_pqo_cache *c, int32_t layer, const uint8_t **k_indices,
+                             const uint16_t **k_scales, const uint8_t **v_indices, const uint16_t **v_scales);
+/* Sequence-parallel decode: shard-local un-normalised output + (max, sum), no append. */
+int tqb_pqo_cache_attend_partial(tqb_pqo_cache *c, int32_t layer, const void *q, int32_t dtype,
+                                 int32_t num_q_heads, float softmax_scale, float *out_unnorm, float *lse_out,
+                                 tqb_stream_t stream);
+
+/* QuantizedKVCache (src/attention.rs:45-694): whole-vector polar + QJL blocks for keys
+ * and values, one growable device array set per layer.  Vectors are HOST pointers unless
+ * the name says otherwise; these calls synchronise the stream before returning. */
+typedef struct tqb_kv_cache tqb_kv_cache;
+int tqb_kv_cache_create(const tqb_config *cfg, int32_t num_layers, uint64_t qjl_seed, tqb_kv_cache **out);
+void tqb_kv_cache_destroy(tqb_kv_cache *c);
+/* push / push_batch (attention.rs:238-305): keys, values host [n, vec_dim] f32; vec_dim
+ * must equal the configured dim (DimensionMismatch otherwise). */
+int tqb_kv_cache_push_batch(tqb_kv_cache *c, int32_t layer, const float *keys, const float *values, int64_t n,
+                            int64_t vec_dim, tqb_stream_t stream);
+/* attention_scores (attention.rs:319-353): scores host [entry_count]. */
+int tqb_kv_cache_attention_scores(tqb_kv_cache *c, int32_t layer, const float *query, int64_t query_len,
+                                  float *scores, tqb_stream_t stream);
+/* weighted_values (attention.rs:371-408): weights host [num_weights], out host [dim]. */
+int tqb_kv_cache_weighted_values(tqb_kv_cache *c, int32_t layer, const float *weights, int64_t num_weights,
+                                 float *out, tqb_stream_t stream);
+/* dequantize_{keys,values}_range (attention.rs:589-611): out host [end-start, dim]. */
+int tqb_kv_cache_dequantize_range(tqb_kv_cache *c, int32_t layer, int64_t start, int64_t end, int32_t is_keys,
+                                  float *out, tqb_stream_t stream);
+/* export_packed_range / import_packed_range (attention.rs:663-693) in PackedImport's
+ * field layout; signs and rnorms may be NULL on export. */
+int tqb_kv_cache_export_packed_range(tqb_kv_cache *c, int32_t layer, int64_t start, int64_t end,
+                                     int32_t is_keys, uint8_t *packed_bytes, uint16_t *scales,
+                                     uint8_t *qjl_signs, uint16_t *residual_norms, tqb_stream_t stream);
+int tqb_kv_cache_import_packed_range(tqb_kv_cache *c, int32_t layer, int32_t polar_bits,
+                                     const uint8_t *packed_bytes, const uint16_t *scales,
+                                     const uint8_t *qjl_signs_flat, const uint16_t *residual_norms,
+                                     int64_t count, int64_t bytes_per_block, int64_t signs_per_block,
+                                     int32_t is_keys, tqb_stream_t stream);
+int64_t tqb_kv_cache_entry_count(const tqb_kv_cache *c, int32_t layer);
+int32_t tqb_kv_cache_num_layers(const tqb_kv_cache *c);
+size_t tqb_kv_cache_memory_usage(const tqb_kv_cache *c);          /* attention.rs:414-428 */
+size_t tqb_kv_cache_fp16_equivalent_memory(const tqb_kv_cache *c); /* attention.rs:437-440 */
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TQB200_H */

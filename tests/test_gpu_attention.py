@@ -1,0 +1,266 @@
+"""GPU parity of fused decode attention over the packed block-32 cache (tolerance 2e-3 max-abs
+against the CPU oracle over the IDENTICAL packed bytes), of the split/shard merge, and of
+PqoCache."""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle_lib as o
+import turboquant_b200 as tq
+from turboquant_b200._lib import lib
+
+pytestmark = pytest.mark.gpu
+CASES = np.load(os.path.join(os.path.dirname(__file__), "golden", "oracle_cases.npz"))
+TOL = 2e-3   # attention outputs: max-abs error allowed by the parity contract
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def u16(t):
+    return t.cpu().numpy().view(np.uint16)
+
+
+def ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def make_cache(rng, hkv, L, stride, bits, head_dim=128, outliers=True, nm=0, ob=-1):
+    k = rng.standard_normal((hkv, L, head_dim)).astype(np.float32)
+    v = rng.standard_normal((hkv, L, head_dim)).astype(np.float32)
+    if outliers:
+        ch = rng.choice(head_dim, max(1, head_dim * 2 // 100 + 1), replace=False)
+        k[:, :, ch] *= 8
+        v[:, :, ch] *= 8
+    pd, nb = head_dim * bits // 8, head_dim // 32
+    ki = np.zeros((hkv, stride, pd), np.uint8); ks = np.zeros((hkv, stride, nb), np.uint16)
+    vi = np.zeros((hkv, stride, pd), np.uint8); vs = np.zeros((hkv, stride, nb), np.uint16)
+    if L:
+        p, s = o.block_quantize(bits, head_dim, nm, ob, k.reshape(-1, head_dim), nthreads=8)
+        ki[:, :L], ks[:, :L] = p.reshape(hkv, L, pd), s.reshape(hkv, L, nb)
+        p, s = o.block_quantize(bits, head_dim, nm, ob, v.reshape(-1, head_dim), nthreads=8)
+        vi[:, :L], vs[:, :L] = p.reshape(hkv, L, pd), s.reshape(hkv, L, nb)
+    return ki, ks, vi, vs
+
+
+def gpu_attend(q, ki, ks, vi, vs, L, bits, scale, **kw):
+    return tq.decode_attention(dev(q), dev(ki), dev(ks.view(np.int16)), dev(vi), dev(vs.view(np.int16)), L, bits, scale, **kw)
+
+
+@pytest.mark.parametrize("tag,bits", [("pqo3", 3), ("pqo4", 4)])
+def test_golden_fixture(tag, bits):
+    hq, hkv, L = 4, 2, 37
+    kp, ks = o.block_quantize(bits, 128, 0, -1, CASES["att_k"])
+    vp, vs = o.block_quantize(bits, 128, 0, -1, CASES["att_v"])
+    out = gpu_attend(CASES["att_q"], kp.reshape(hkv, L, -1), ks.reshape(hkv, L, -1), vp.reshape(hkv, L, -1),
+                     vs.reshape(hkv, L, -1), L, bits, 1.0 / np.sqrt(128)).cpu().numpy()
+    assert np.abs(out - CASES[f"att_out_{tag}"]).max() < TOL
+
+
+@pytest.mark.parametrize("bits", [3, 4])
+@pytest.mark.parametrize("L", [1, 2, 31, 32, 33, 511, 512, 513])
+def test_ragged_lengths(bits, L):
+    rng = np.random.default_rng(L * 10 + bits)
+    hq, hkv = 4, 2
+    ki, ks, vi, vs = make_cache(rng, hkv, L, L + 3, bits)
+    q = (rng.standard_normal((hq, 128)) / np.sqrt(128)).astype(np.float32)
+    want = o.block_attention(bits, 128, 0, -1, q, ki, ks, vi, vs, L, 0.0884, nthreads=8)
+    for parts in (0, 1, 3):
+        got = gpu_attend(q, ki, ks, vi, vs, L, bits, 0.0884, num_partitions=parts).cpu().numpy()
+        assert np.abs(got - want).max() < TOL
+
+
+@pytest.mark.parametrize("bits,hq,hkv,head_dim", [(3, 16, 8, 128), (4, 32, 8, 128), (3, 64, 8, 128), (3, 8, 8, 128),
+                                                  (4, 24, 2, 128), (3, 4, 2, 64), (4, 4, 2, 256), (3, 3, 1, 96)])
+def test_gqa_groups_and_head_dims(bits, hq, hkv, head_dim):
+    rng = np.random.default_rng(hq * 7 + head_dim)
+    L = 300
+    ki, ks, vi, vs = make_cache(rng, hkv, L, L, bits, head_dim)
+    q = (rng.standard_normal((hq, head_dim)) / np.sqrt(head_dim)).astype(np.float32)
+    scale = 1.0 / np.sqrt(head_dim)
+    want = o.block_attention(bits, head_dim, 0, -1, q, ki, ks, vi, vs, L, scale, nthreads=8)
+    got = gpu_attend(q, ki, ks, vi, vs, L, bits, scale).cpu().numpy()
+    assert np.abs(got - want).max() < TOL
+
+
+def test_sharp_softmax_and_query_dtypes():
+    # large logits: one token dominates; also bf16 / f16 queries and outputs
+    rng = np.random.default_rng(77)
+    hq, hkv, L = 8, 2, 700
+    ki, ks, vi, vs = make_cache(rng, hkv, L, L, 4)
+    q = rng.standard_normal((hq, 128)).astype(np.float32)
+    want = o.block_attention(4, 128, 0, -1, q, ki, ks, vi, vs, L, 1.0, nthreads=8)
+    got = gpu_attend(q, ki, ks, vi, vs, L, 4, 1.0).cpu().numpy()
+    assert np.abs(got - want).max() < TOL * max(1.0, np.abs(want).max())
+    for dt in (torch.bfloat16, torch.float16):
+        qh = torch.from_numpy(q / np.sqrt(128)).to(dt)
+        want = o.block_attention(4, 128, 0, -1, qh.float().numpy(), ki, ks, vi, vs, L, 0.0884, nthreads=8)
+        got = tq.decode_attention(qh.cuda(), dev(ki), dev(ks.view(np.int16)), dev(vi), dev(vs.view(np.int16)), L, 4, 0.0884)
+        assert got.dtype == dt
+        assert np.abs(got.float().cpu().numpy() - want).max() < 2e-2 * max(1.0, np.abs(want).max())  # output rounding of the half type
+
+
+@pytest.mark.parametrize("nm,ob", [(1, -1), (0, 0), (0, 2)])
+def test_other_cache_modes(nm, ob):
+    rng = np.random.default_rng(nm * 10 + ob + 5)
+    hq, hkv, L = 4, 2, 129
+    ki, ks, vi, vs = make_cache(rng, hkv, L, L, 3, nm=nm, ob=ob)
+    q = (rng.standard_normal((hq, 128)) / np.sqrt(128)).astype(np.float32)
+    want = o.block_attention(3, 128, nm, ob, q, ki, ks, vi, vs, L, 0.0884)
+    got = gpu_attend(q, ki, ks, vi, vs, L, 3, 0.0884, norm_mode=tq.QuantNormMode(nm), outlier_blocks=ob).cpu().numpy()
+    assert np.abs(got - want).max() < TOL
+
+
+def test_qjl_correction_branch():
+    # tq_attention_kernel.cu:197-231: per-key residual sign sketch over the whole head_dim
+    rng = np.random.default_rng(9)
+    hq, hkv, L, D = 4, 2, 200, 128
+    k = rng.standard_normal((hkv, L, D)).astype(np.float32)
+    ki, ks, vi, vs = make_cache(rng, hkv, L, L, 3, outliers=False, ob=0)
+    kp, ksc = o.block_quantize(3, D, 0, 0, k.reshape(-1, D))
+    ki, ks = kp.reshape(hkv, L, -1), ksc.reshape(hkv, L, -1)
+    res = k.reshape(-1, D) - o.block_dequantize(3, D, 0, 0, kp, ksc)
+    signs = np.stack([o.qjl_signs(r, D, 12345) for r in res]).reshape(hkv, L, D // 8)
+    norms = np.array([o.f32_to_f16_bits(float(np.linalg.norm(r))) for r in res], np.uint16).reshape(hkv, L)
+    q = (rng.standard_normal((hq, D)) / np.sqrt(D)).astype(np.float32)
+    rq = np.stack([o.query_projections(qh, D, 12345) for qh in q])
+    want = o.block_attention(3, D, 0, 0, q, ki, ks, vi, vs, L, 0.0884, qjl=(signs, norms, rq))
+    got = gpu_attend(q, ki, ks, vi, vs, L, 3, 0.0884, outlier_blocks=0,
+                     qjl=(dev(signs), dev(norms.view(np.int16)), dev(rq))).cpu().numpy()
+    assert np.abs(got - want).max() < TOL
+    plain = o.block_attention(3, D, 0, 0, q, ki, ks, vi, vs, L, 0.0884)
+    assert np.abs(plain - want).max() > 1e-4      # the correction is not a no-op
+
+
+def test_empty_cache_gives_zero_output():
+    q = torch.randn((4, 128), device="cuda")
+    z8 = torch.zeros((2, 4, 48), dtype=torch.uint8, device="cuda")
+    z16 = torch.zeros((2, 4, 4), dtype=torch.int16, device="cuda")
+    out = tq.decode_attention(q, z8, z16, z8, z16, 0, 3, 1.0)
+    assert torch.all(out == 0)
+    with pytest.raises(tq.RangeOutOfBounds):
+        tq.decode_attention(q, z8, z16, z8, z16, 5, 3, 1.0)
+
+
+def test_reference_fused_attention_symbol():
+    # tq_fused_attention with the reference's argument list (src/cache/cuda/ffi.rs:50-78),
+    # partition count = ceil(kv_len / 512) and caller-owned, pre-zeroed partial buffers
+    rng = np.random.default_rng(21)
+    hq, hkv, L, stride = 8, 2, 1100, 1300
+    for bits in (3, 4):
+        ki, ks, vi, vs = make_cache(rng, hkv, L, stride, bits)
+        q = (rng.standard_normal((hq, 128)) / np.sqrt(128)).astype(np.float32)
+        c, _ = o.block_codebook(bits, 0)
+        sign = (o.block_signs() * (np.float32(1) / np.sqrt(np.float32(32))) * np.sqrt(np.float32(32))).astype(np.float32)
+        parts = (L + 511) // 512
+        out = torch.zeros((hq, 128), device="cuda")
+        po = torch.zeros((hq * parts, 128), device="cuda")
+        pm = torch.zeros(hq * parts, device="cuda"); ps = torch.zeros(hq * parts, device="cuda")
+        t = [dev(q), dev(ki), dev(ks.view(np.int16)), dev(vi), dev(vs.view(np.int16)), dev(c), dev(sign)]
+        lib.tq_fused_attention(*[ptr(x) for x in t], ptr(out), ptr(po), ptr(pm), ptr(ps), None, None, None, 0, hq, hkv, 128,
+                               L, stride, 128 * bits // 8, 4, bits, 0.0884, parts, None)
+        want = o.block_attention(bits, 128, 0, -1, q, ki, ks, vi, vs, L, 0.0884, nthreads=8)
+        assert np.abs(out.cpu().numpy() - want).max() < TOL
+
+
+def test_sequence_shards_merge_to_the_unsharded_result():
+    # split the sequence into 3 ragged shards, attend per shard, merge (max, sum, out) partials
+    rng = np.random.default_rng(33)
+    hq, hkv, L = 16, 2, 1000
+    ki, ks, vi, vs = make_cache(rng, hkv, L, L, 3)
+    q = (rng.standard_normal((hq, 128)) / np.sqrt(128)).astype(np.float32)
+    want = o.block_attention(3, 128, 0, -1, q, ki, ks, vi, vs, L, 0.0884, nthreads=8)
+    outs, lses = [], []
+    for lo, hi in ((0, 400), (400, 401), (401, 1000)):
+        out, lse = gpu_attend(q, ki[:, lo:hi], ks[:, lo:hi], vi[:, lo:hi], vs[:, lo:hi], hi - lo, 3, 0.0884, return_lse=True)
+        outs.append(out); lses.append(lse)
+    got = tq.lse_combine(torch.stack(outs), torch.stack(lses)).cpu().numpy()
+    assert np.abs(got - want).max() < TOL
+    # an empty shard contributes nothing
+    e_out, e_lse = gpu_attend(q, ki[:, :4], ks[:, :4], vi[:, :4], vs[:, :4], 0, 3, 0.0884, return_lse=True)
+    got2 = tq.lse_combine(torch.stack(outs + [e_out]), torch.stack(lses + [e_lse])).cpu().numpy()
+    assert np.abs(got2 - want).max() < TOL
+
+
+def _sincos(shape, seed, fn, freq, amp, off=0):
+    i = np.arange(int(np.prod(shape)), dtype=np.float64)
+    return torch.from_numpy((fn((i + seed + off) * freq) * amp).astype(np.float32).reshape(shape))
+
+
+@pytest.mark.parametrize("bits,nm,thr", [(3, 0, 0.85), (3, 1, 0.83), (4, 0, 0.92)])
+def test_pqo_cache_follows_the_reference_tests(bits, nm, thr):
+    # tests/cache_pqo_tests.rs: first prefill returns the originals (:86-104), later calls return the
+    # whole dequantized cache (:119-149), cosine thresholds (:152-244), reset / memory / layers (:251-304)
+    cfg = tq.CacheConfig(bits=bits, head_dim=128, num_kv_heads=8, num_layers=2, norm_mode=tq.QuantNormMode(nm))
+    cache = tq.PqoCache(cfg)
+    k = _sincos((1, 8, 16, 128), 0, np.sin, 0.0137, 2.0).cuda()
+    v = _sincos((1, 8, 16, 128), 0, np.cos, 0.0213, 1.5, 1000).cuda()
+    r = cache.prefill(0, k, v)
+    assert r.k is k and r.v is v and r.logit_bias is None
+    assert cache.seq_len(0) == 16 and cache.seq_len(1) == 0
+    assert cache.capacity(0) == 16 + 128                      # src/cache/storage.rs:114-116
+    assert cache.memory_usage() == 2 * 8 * 16 * (128 * bits // 8) + 2 * 8 * 16 * 4 * 2
+    k2 = _sincos((1, 8, 4, 128), 50, np.sin, 0.0137, 2.0).cuda()
+    v2 = _sincos((1, 8, 4, 128), 50, np.cos, 0.0213, 1.5, 1000).cuda()
+    r2 = cache.prefill(0, k2, v2)
+    assert r2.k.shape == (1, 8, 20, 128)
+    full_k = torch.cat([k, k2], dim=2)
+    cos = torch.nn.functional.cosine_similarity(full_k.flatten(), r2.k.flatten(), dim=0).item()
+    assert cos > thr
+    want_k = o.block_dequantize(bits, 128, nm, -1, *o.block_quantize(bits, 128, nm, -1, full_k.cpu().numpy().reshape(-1, 128)))
+    assert np.array_equal(r2.k.cpu().numpy().reshape(-1, 128), want_k)
+    # decode: Fused output of shape [1, Hq, 1, D], equal to oracle attention over the same packed cache
+    q = (torch.randn((1, 16, 1, 128), generator=torch.Generator().manual_seed(1)) / 128 ** 0.5).cuda()
+    k3, v3 = torch.randn((1, 8, 1, 128)).cuda(), torch.randn((1, 8, 1, 128)).cuda()
+    dec = cache.decode(0, k3, v3, q, tq.AttendConfig(softmax_scale=0.0884, n_kv_groups=2))
+    assert dec.is_fused() and dec.fused.shape == (1, 16, 1, 128)
+    assert dec.fused.abs().sum().item() > 0.01                # tests/cache_pqo_tests.rs:387-406
+    allk = torch.cat([k, k2, k3], dim=2).cpu().numpy().reshape(8, 21, 128)
+    allv = torch.cat([v, v2, v3], dim=2).cpu().numpy().reshape(8, 21, 128)
+    kp, ks = o.block_quantize(bits, 128, nm, -1, allk.reshape(-1, 128))
+    vp, vs = o.block_quantize(bits, 128, nm, -1, allv.reshape(-1, 128))
+    want = o.block_attention(bits, 128, nm, -1, q.cpu().numpy().reshape(16, 128), kp.reshape(8, 21, -1), ks.reshape(8, 21, -1),
+                             vp.reshape(8, 21, -1), vs.reshape(8, 21, -1), 21, 0.0884)
+    assert np.abs(dec.fused.cpu().numpy().reshape(16, 128) - want).max() < TOL
+    cache.reset()
+    assert cache.seq_len(0) == 0 and cache.memory_usage() == 0
+    with pytest.raises(tq.LayerOutOfRange):
+        cache.seq_len(2)
+    with pytest.raises(tq.InvalidDimension):
+        tq.PqoCache(tq.CacheConfig(bits=3, head_dim=100, num_kv_heads=1, num_layers=1))   # src/cache/pqo.rs:32-39
+    with pytest.raises(tq.UnsupportedBits):
+        tq.PqoCache(tq.CacheConfig(bits=2, head_dim=128, num_kv_heads=1, num_layers=1))
+
+
+def test_pqo_cache_growth_batch_and_host_buffers():
+    # growth policy needed + max(needed/4, 128) with copy-on-grow; batch folds into heads;
+    # host-buffer mode copies k, v, q in and the output back
+    cfg = tq.CacheConfig(bits=4, head_dim=128, num_kv_heads=2, num_layers=1, batch=3)
+    cache = tq.PqoCache(cfg)
+    g = torch.Generator().manual_seed(5)
+    ks_, vs_ = [], []
+    for step, n in enumerate((100, 50, 200)):
+        k, v = torch.randn((3, 2, n, 128), generator=g).bfloat16(), torch.randn((3, 2, n, 128), generator=g).bfloat16()
+        cache.prefill(0, k.cuda(), v.cuda())
+        ks_.append(k); vs_.append(v)
+    assert cache.seq_len(0) == 350
+    assert cache.capacity(0) == 350 + 128      # 100 -> 228; 150 fits; 350 -> 350 + max(87, 128)
+    allk, allv = torch.cat(ks_, dim=2), torch.cat(vs_, dim=2)
+    dk, dv = cache.dequantize_full(0)
+    want = o.block_dequantize(4, 128, 0, -1, *o.block_quantize(4, 128, 0, -1, allk.float().numpy().reshape(-1, 128), nthreads=8))
+    assert np.array_equal(dk.cpu().numpy().reshape(-1, 128), want)      # old rows survived both regrowths
+    k1, v1 = torch.randn((3, 2, 1, 128), generator=g).bfloat16(), torch.randn((3, 2, 1, 128), generator=g).bfloat16()
+    q = (torch.randn((3, 8, 1, 128), generator=g) / 128 ** 0.5).bfloat16()
+    out_host = torch.empty_like(q).pin_memory()
+    cache.decode(0, k1.pin_memory(), v1.pin_memory(), q.pin_memory(), tq.AttendConfig(0.0884, 4), out=out_host)
+    torch.cuda.synchronize()
+    allk, allv = torch.cat([allk, k1], dim=2), torch.cat([allv, v1], dim=2)
+    kp, ksc = o.block_quantize(4, 128, 0, -1, allk.float().numpy().reshape(-1, 128), nthreads=8)
+    vp, vsc = o.block_quantize(4, 128, 0, -1, allv.float().numpy().reshape(-1, 128), nthreads=8)
+    want = o.block_attention(4, 128, 0, -1, q.float().numpy().reshape(24, 128), kp.reshape(6, 351, -1), ksc.reshape(6, 351, -1),
+                             vp.reshape(6, 351, -1), vsc.reshape(6, 351, -1), 351, 0.0884, nthreads=8)
+    assert np.abs(out_host.float().numpy().reshape(24, 128) - want).max() < 1e-2   # bf16 output rounding

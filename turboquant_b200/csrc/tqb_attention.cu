@@ -1,0 +1,506 @@
+// Fused decode attention over the packed block-32 cache: general kernel.
+//
+// Algebra (derived from src/cache/cuda/kernels/tq_dequant_kernel.cu:77-97 and
+// tq_attention_kernel.cu:161-253).  A stored block decodes to
+//     k = |s| * H32(sigma .* c[idx]) / sqrt(32)
+// and H32 is symmetric, so  <q_b, k> = |s| * < sigma .* H32(q_b)/sqrt(32), c[idx] >.
+// The kernel therefore rotates the query once (q~ = sigma .* H32(q_b)/sqrt(32)), scores
+// tokens with a plain code -> centroid lookup, accumulates  sum_t p_t |s_t| c[idx_t]  in the
+// rotated domain, and the merge kernel applies one inverse rotation per output block.
+// The reference instead runs a 32-point butterfly per key and per value.
+//
+// One CTA serves one KV head and one partition of the sequence for ALL query heads of the
+// GQA group, so packed K/V bytes are fetched from HBM once (the reference launches one CTA
+// per query head, tq_attention_kernel.cu:90-93).  Each warp owns whole tokens; there is no
+// block-wide barrier inside the token loop.
+#include <float.h>
+
+#include "tqb_common.cuh"
+
+namespace tqb {
+
+int block_cfg_check(int bits, int head_dim, int norm_mode);
+
+namespace {
+
+constexpr int kWarps = 4;
+constexpr int kThreads = kWarps * 32;
+constexpr int kHeadTile = 8;  // query heads handled per pass over the partition
+
+struct DecodeArgs {
+    const void* q;
+    const uint8_t* k_idx;
+    const uint16_t* k_sc;
+    const uint8_t* v_idx;
+    const uint16_t* v_sc;
+    float* partial_out;  // [hq, P, D]  rotated domain, un-normalised
+    float* partial_max;  // [hq, P]
+    float* partial_sum;  // [hq, P]
+    const uint8_t* qjl_signs;
+    const uint16_t* qjl_norms;
+    const float* rq;
+    const float* dev_codebook;  // reference entry point: caller's tables on the device
+    const float* dev_signs;
+    int qjl_enabled;
+    int hq, hkv, head_dim, nblk, bits, packed_dim;
+    int kv_len, kv_stride, num_partitions, part_size;
+    int outlier_mode;  // 0 all normal, 1 all outlier, 2 by sign of the scale
+    float softmax_scale;
+    float sign_mag;
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// 32-point butterfly with one element per lane.
+__device__ __forceinline__ float wht32_lane(float v, int lane) {
+#pragma unroll
+    for (int h = 1; h < 32; h <<= 1) {
+        float other = __shfl_xor_sync(0xffffffffu, v, h);
+        v = (lane & h) ? (other - v) : (v + other);
+    }
+    return v;
+}
+
+template <typename QT, int NB>
+__global__ void __launch_bounds__(kThreads)
+decode_general_kernel(DecodeArgs a, Codebook normal, Codebook outlier) {
+    extern __shared__ float smem[];
+    const int D = a.head_dim;
+    const int g = a.hq / a.hkv;
+    float* s_q = smem;                                // [kHeadTile][D]
+    float* s_rq = s_q + kHeadTile * D;                // [kHeadTile][D]
+    float* s_c = s_rq + kHeadTile * D;                // [2][16]
+    float* s_sign = s_c + 32;                         // [32]
+    float* s_m = s_sign + 32;                         // [kWarps][kHeadTile]
+    float* s_l = s_m + kWarps * kHeadTile;            // [kWarps][kHeadTile]
+    float* s_o = s_l + kWarps * kHeadTile;            // [kWarps][kHeadTile][D]
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int kvh = blockIdx.x, part = blockIdx.y;
+    const int nwords = a.packed_dim >> 2;
+    const int bits = a.bits;
+    const uint32_t cmask = (1u << bits) - 1u;
+
+    if (tid < 16) {
+        s_c[tid] = normal.c[tid];
+        s_c[16 + tid] = a.dev_codebook ? (tid < (1 << bits) ? a.dev_codebook[tid] : 0.0f) : outlier.c[tid];
+    }
+    if (tid < 32) {
+        const uint32_t neg = 0xB1A6D4B2u;  // src/cache/precomputed/rotation.rs:16-20
+        s_sign[tid] = a.dev_signs ? a.dev_signs[tid] : (((neg >> tid) & 1u) ? -a.sign_mag : a.sign_mag);
+    }
+    __syncthreads();
+
+    const int t0 = part * a.part_size;
+    const int t1 = min(t0 + a.part_size, a.kv_len);
+    const float inv_sqrt = 1.0f / sqrtf((float)kBlock);
+    const float qjl_c = 1.2533141f * (1.0f / sqrtf((float)D));  // tq_attention_kernel.cu:225
+
+    const size_t row0 = (size_t)kvh * a.kv_stride;
+    const uint32_t* kw = reinterpret_cast<const uint32_t*>(a.k_idx);
+    const uint32_t* vw = reinterpret_cast<const uint32_t*>(a.v_idx);
+
+    for (int h0 = 0; h0 < g; h0 += kHeadTile) {
+        const int gt = min(kHeadTile, g - h0);
+        __syncthreads();
+        // rotate the queries of this tile once: (head, block) pairs round-robin over warps
+        for (int u = warp; u < gt * a.nblk; u += kWarps) {
+            const int hh = u / a.nblk, b = u - hh * a.nblk;
+            const int head = kvh * g + h0 + hh;
+            float v = to_f32<QT>(reinterpret_cast<const QT*>(a.q)[(size_t)head * D + b * 32 + lane]);
+            v = wht32_lane(v, lane);
+            s_q[hh * D + b * 32 + lane] = (v * inv_sqrt) * s_sign[lane];
+            if (a.qjl_enabled) s_rq[hh * D + b * 32 + lane] = a.rq[(size_t)head * D + b * 32 + lane];
+        }
+        __syncthreads();
+
+        float m[kHeadTile], l[kHeadTile], o[kHeadTile][NB];
+#pragma unroll
+        for (int hh = 0; hh < kHeadTile; ++hh) {
+            m[hh] = -FLT_MAX;
+            l[hh] = 0.0f;
+#pragma unroll
+            for (int b = 0; b < NB; ++b) o[hh][b] = 0.0f;
+        }
+
+        for (int t = t0 + warp; t < t1; t += kWarps) {
+            const size_t row = row0 + t;
+            const uint32_t kword = lane < nwords ? __ldg(kw + row * nwords + lane) : 0u;
+            const uint32_t vword = lane < nwords ? __ldg(vw + row * nwords + lane) : 0u;
+            float ksc = 0.0f, vsc = 0.0f;
+            if (lane < a.nblk) {
+                ksc = f16_bits_to_f32(__ldg(a.k_sc + row * a.nblk + lane));
+                vsc = f16_bits_to_f32(__ldg(a.v_sc + row * a.nblk + lane));
+            }
+            float acc[kHeadTile];
+#pragma unroll
+            for (int hh = 0; hh < kHeadTile; ++hh) acc[hh] = 0.0f;
+#pragma unroll
+            for (int b = 0; b < NB; ++b) {
+                if (b < a.nblk) {
+                    const int bitoff = (b * 32 + lane) * bits;
+                    const int wi = bitoff >> 5;
+                    const uint32_t w0 = __shfl_sync(0xffffffffu, kword, wi);
+                    const uint32_t w1 = __shfl_sync(0xffffffffu, kword, min(wi + 1, 31));
+                    uint32_t code = __funnelshift_r(w0, w1, bitoff & 31) & cmask;
+                    const float sb = __shfl_sync(0xffffffffu, ksc, b);
+                    const int sel = a.outlier_mode == 2 ? (sb < 0.0f ? 1 : 0) : a.outlier_mode;
+                    if (sel == 0) code = min(code, (uint32_t)(normal.n - 1));
+                    const float kv = s_c[sel * 16 + code] * fabsf(sb);
+#pragma unroll
+                    for (int hh = 0; hh < kHeadTile; ++hh)
+                        if (hh < gt) acc[hh] = fmaf(s_q[hh * D + b * 32 + lane], kv, acc[hh]);
+                }
+            }
+            float corr[kHeadTile];
+            float qn = 0.0f;
+            if (a.qjl_enabled) {
+                // tq_attention_kernel.cu:197-231
+                const uint32_t sw = lane < a.nblk
+                    ? __ldg(reinterpret_cast<const uint32_t*>(a.qjl_signs) + row * a.nblk + lane) : 0u;
+                qn = f16_bits_to_f32(__ldg(a.qjl_norms + row));
+#pragma unroll
+                for (int hh = 0; hh < kHeadTile; ++hh) corr[hh] = 0.0f;
+#pragma unroll
+                for (int b = 0; b < NB; ++b) {
+                    if (b < a.nblk) {
+                        const uint32_t w = __shfl_sync(0xffffffffu, sw, b);
+                        const float sg = ((w >> lane) & 1u) ? 1.0f : -1.0f;
+#pragma unroll
+                        for (int hh = 0; hh < kHeadTile; ++hh)
+                            if (hh < gt) corr[hh] = fmaf(s_rq[hh * D + b * 32 + lane], sg, corr[hh]);
+                    }
+                }
+            }
+            float p[kHeadTile];
+#pragma unroll
+            for (int hh = 0; hh < kHeadTile; ++hh) {
+                if (hh < gt) {
+                    float s = warp_sum(acc[hh]) * a.softmax_scale;
+                    if (a.qjl_enabled) s += (warp_sum(corr[hh]) * (qn * qjl_c)) * a.softmax_scale;
+                    const float mn = fmaxf(m[hh], s);
+                    const float resc = expf(m[hh] - mn);
+                    p[hh] = expf(s - mn);
+                    l[hh] = l[hh] * resc + p[hh];
+                    m[hh] = mn;
+#pragma unroll
+                    for (int b = 0; b < NB; ++b) o[hh][b] *= resc;
+                }
+            }
+#pragma unroll
+            for (int b = 0; b < NB; ++b) {
+                if (b < a.nblk) {
+                    const int bitoff = (b * 32 + lane) * bits;
+                    const int wi = bitoff >> 5;
+                    const uint32_t w0 = __shfl_sync(0xffffffffu, vword, wi);
+                    const uint32_t w1 = __shfl_sync(0xffffffffu, vword, min(wi + 1, 31));
+                    uint32_t code = __funnelshift_r(w0, w1, bitoff & 31) & cmask;
+                    const float sb = __shfl_sync(0xffffffffu, vsc, b);
+                    const int sel = a.outlier_mode == 2 ? (sb < 0.0f ? 1 : 0) : a.outlier_mode;
+                    if (sel == 0) code = min(code, (uint32_t)(normal.n - 1));
+                    const float vv = s_c[sel * 16 + code] * fabsf(sb);
+#pragma unroll
+                    for (int hh = 0; hh < kHeadTile; ++hh)
+                        if (hh < gt) o[hh][b] = fmaf(p[hh], vv, o[hh][b]);
+                }
+            }
+        }
+
+        // merge the four warps' online-softmax states
+#pragma unroll
+        for (int hh = 0; hh < kHeadTile; ++hh) {
+            if (hh < gt) {
+                if (lane == 0) {
+                    s_m[warp * kHeadTile + hh] = m[hh];
+                    s_l[warp * kHeadTile + hh] = l[hh];
+                }
+#pragma unroll
+                for (int b = 0; b < NB; ++b)
+                    if (b < a.nblk) s_o[(warp * kHeadTile + hh) * D + b * 32 + lane] = o[hh][b];
+            }
+        }
+        __syncthreads();
+        for (int u = warp; u < gt * a.nblk; u += kWarps) {
+            const int hh = u / a.nblk, b = u - hh * a.nblk;
+            float M = -FLT_MAX;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) M = fmaxf(M, s_m[w * kHeadTile + hh]);
+            float L = 0.0f, O = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) {
+                const float e = expf(s_m[w * kHeadTile + hh] - M);
+                L = fmaf(s_l[w * kHeadTile + hh], e, L);
+                O = fmaf(s_o[(w * kHeadTile + hh) * D + b * 32 + lane], e, O);
+            }
+            const int head = kvh * g + h0 + hh;
+            const size_t pi = (size_t)head * a.num_partitions + part;
+            a.partial_out[pi * D + b * 32 + lane] = O;
+            if (b == 0 && lane == 0) {
+                a.partial_max[pi] = M;
+                a.partial_sum[pi] = L;
+            }
+        }
+    }
+}
+
+struct MergeArgs {
+    const float* partial_out;
+    const float* partial_max;
+    const float* partial_sum;
+    const float* dev_signs;
+    void* out;
+    float* lse_out;  // optional [hq][2]
+    int head_dim, nblk, num_partitions;
+    int rotate;      // 1: inputs are in the rotated domain (apply sigma, H32, 1/sqrt(32))
+    float sign_mag;
+};
+
+// Log-sum-exp merge of partitions (tq_attention_kernel.cu:299-332) fused with the single
+// inverse rotation of the output.  Grid: one CTA per query head; warp w handles output
+// blocks w, w+4, ...; lane = element of the block.
+template <typename OT>
+__global__ void __launch_bounds__(kThreads) decode_merge_kernel(MergeArgs a) {
+    const int head = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int D = a.head_dim, P = a.num_partitions;
+    const float* pm = a.partial_max + (size_t)head * P;
+    const float* ps = a.partial_sum + (size_t)head * P;
+    float M = -FLT_MAX;
+    for (int p = lane; p < P; p += 32) M = fmaxf(M, pm[p]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    float L = 0.0f;
+    for (int p = lane; p < P; p += 32) L += ps[p] * expf(pm[p] - M);
+    L = warp_sum(L);
+    const float inv_sqrt = 1.0f / sqrtf((float)kBlock);
+    const uint32_t neg = 0xB1A6D4B2u;
+    const float sg = a.dev_signs ? a.dev_signs[lane] : (((neg >> lane) & 1u) ? -a.sign_mag : a.sign_mag);
+    const float inv_l = L > 0.0f ? 1.0f / L : 0.0f;
+    for (int b = warp; b < a.nblk; b += kWarps) {
+        float acc = 0.0f;
+        for (int p = 0; p < P; ++p)
+            acc = fmaf(a.partial_out[((size_t)head * P + p) * D + b * 32 + lane], expf(pm[p] - M), acc);
+        if (a.rotate) acc = wht32_lane(acc * sg, lane) * inv_sqrt;
+        if (a.lse_out == nullptr) acc *= inv_l;
+        reinterpret_cast<OT*>(a.out)[(size_t)head * D + b * 32 + lane] = from_f32<OT>(acc);
+    }
+    if (a.lse_out != nullptr && threadIdx.x == 0) {
+        a.lse_out[head * 2] = M;
+        a.lse_out[head * 2 + 1] = L;
+    }
+}
+
+// Shard merge: partial_out [S, hq, D] un-normalised and already in the output domain,
+// partial_lse [S, hq, 2].
+template <typename OT>
+__global__ void lse_combine_kernel(const float* __restrict__ po, const float* __restrict__ lse, int S, int hq, int D,
+                                   OT* __restrict__ out) {
+    const int head = blockIdx.x;
+    float M = -FLT_MAX;
+    for (int s = 0; s < S; ++s) M = fmaxf(M, lse[((size_t)s * hq + head) * 2]);
+    float L = 0.0f;
+    for (int s = 0; s < S; ++s) L += lse[((size_t)s * hq + head) * 2 + 1] * expf(lse[((size_t)s * hq + head) * 2] - M);
+    const float inv_l = L > 0.0f ? 1.0f / L : 0.0f;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float acc = 0.0f;
+        for (int s = 0; s < S; ++s)
+            acc = fmaf(po[((size_t)s * hq + head) * D + d], expf(lse[((size_t)s * hq + head) * 2] - M), acc);
+        out[(size_t)head * D + d] = from_f32<OT>(acc * inv_l);
+    }
+}
+
+size_t general_smem_bytes(int D) {
+    return sizeof(float) * ((size_t)2 * kHeadTile * D + 64 + 2 * kWarps * kHeadTile + (size_t)kWarps * kHeadTile * D);
+}
+
+template <typename QT, int NB>
+int launch_general(const DecodeArgs& a, const Codebook& n, const Codebook& o, cudaStream_t s) {
+    const size_t smem = general_smem_bytes(a.head_dim);
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(decode_general_kernel<QT, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)general_smem_bytes(256));
+        if (e != cudaSuccess) { set_cuda_error(e); return TQB_ERR_CUDA; }
+        attr_done = true;
+    }
+    dim3 grid(a.hkv, a.num_partitions);
+    decode_general_kernel<QT, NB><<<grid, kThreads, smem, s>>>(a, n, o);
+    return check_launch(s);
+}
+
+template <typename QT>
+int launch_general_nb(const DecodeArgs& a, const Codebook& n, const Codebook& o, cudaStream_t s) {
+    if (a.nblk <= 2) return launch_general<QT, 2>(a, n, o, s);
+    if (a.nblk <= 4) return launch_general<QT, 4>(a, n, o, s);
+    return launch_general<QT, 8>(a, n, o, s);
+}
+
+template <typename OT>
+int launch_merge(const MergeArgs& m, int hq, cudaStream_t s) {
+    decode_merge_kernel<OT><<<hq, kThreads, 0, s>>>(m);
+    return check_launch(s);
+}
+
+inline float cpu_sign_magnitude() {
+    volatile float inv = 1.0f / sqrtf(32.0f);
+    volatile float s = sqrtf(32.0f);
+    return inv * s;
+}
+
+int run_decode(DecodeArgs& a, const Codebook& cn, const Codebook& co, int q_dtype, void* out, int out_dtype,
+               float* lse_out, cudaStream_t s) {
+    int st;
+    if (q_dtype == TQB_F32) st = launch_general_nb<float>(a, cn, co, s);
+    else if (q_dtype == TQB_F16) st = launch_general_nb<__half>(a, cn, co, s);
+    else st = launch_general_nb<__nv_bfloat16>(a, cn, co, s);
+    if (st != TQB_OK) return st;
+    MergeArgs m{};
+    m.partial_out = a.partial_out;
+    m.partial_max = a.partial_max;
+    m.partial_sum = a.partial_sum;
+    m.dev_signs = a.dev_signs;
+    m.out = out;
+    m.lse_out = lse_out;
+    m.head_dim = a.head_dim;
+    m.nblk = a.nblk;
+    m.num_partitions = a.num_partitions;
+    m.rotate = 1;
+    m.sign_mag = a.sign_mag;
+    if (out_dtype == TQB_F32) return launch_merge<float>(m, a.hq, s);
+    if (out_dtype == TQB_F16) return launch_merge<__half>(m, a.hq, s);
+    return launch_merge<__nv_bfloat16>(m, a.hq, s);
+}
+
+}  // namespace
+}  // namespace tqb
+
+using namespace tqb;
+
+extern "C" {
+
+int32_t tqb_decode_num_partitions(int32_t num_kv_heads, int32_t kv_len) {
+    if (num_kv_heads <= 0 || kv_len <= 0) return 1;
+    const int target_ctas = 148 * 8;
+    int p = (target_ctas + num_kv_heads - 1) / num_kv_heads;
+    const int max_p = (kv_len + 63) / 64;  // at least 64 tokens per partition
+    if (p > max_p) p = max_p;
+    if (p < 1) p = 1;
+    return p;
+}
+
+size_t tqb_decode_scratch_bytes(int32_t num_q_heads, int32_t head_dim, int32_t num_partitions) {
+    if (num_q_heads <= 0 || head_dim <= 0 || num_partitions <= 0) return 0;
+    return sizeof(float) * (size_t)num_q_heads * num_partitions * ((size_t)head_dim + 2);
+}
+
+int tqb_decode_attention(const tqb_decode_params* p, tqb_stream_t stream) {
+    if (!p) return TQB_ERR_NULL_POINTER;
+    int st = block_cfg_check(p->bits, p->head_dim, p->norm_mode);
+    if (st != TQB_OK) return st;
+    if (p->head_dim > 256) return TQB_ERR_UNSUPPORTED;
+    if (p->num_q_heads <= 0 || p->num_kv_heads <= 0 || p->num_q_heads % p->num_kv_heads != 0)
+        return TQB_ERR_INVALID_ARGUMENT;
+    if (p->kv_len < 0 || p->kv_len > p->kv_stride) return TQB_ERR_RANGE_OUT_OF_BOUNDS;
+    if (!p->q || !p->out || !p->scratch) return TQB_ERR_NULL_POINTER;
+    if (p->kv_len > 0 && (!p->k_indices || !p->k_scales || !p->v_indices || !p->v_scales)) return TQB_ERR_NULL_POINTER;
+    if (p->qjl_enabled && (!p->qjl_signs || !p->qjl_norms || !p->rq)) return TQB_ERR_NULL_POINTER;
+    if (p->lse_out && p->out_dtype != TQB_F32) return TQB_ERR_INVALID_ARGUMENT;
+    if (((uintptr_t)p->k_indices % 4) || ((uintptr_t)p->v_indices % 4) || ((uintptr_t)p->scratch % 16) ||
+        ((uintptr_t)p->qjl_signs % 4))
+        return TQB_ERR_MISALIGNED;
+    int P = p->num_partitions > 0 ? p->num_partitions : tqb_decode_num_partitions(p->num_kv_heads, p->kv_len);
+    if (p->scratch_bytes < tqb_decode_scratch_bytes(p->num_q_heads, p->head_dim, P)) return TQB_ERR_INVALID_ARGUMENT;
+    Codebook cn, co;
+    if (!block_codebook(p->bits - 1, p->norm_mode, cn) || !block_codebook(p->bits, p->norm_mode, co))
+        return TQB_ERR_UNSUPPORTED_BITS;
+    DecodeArgs a{};
+    a.q = p->q;
+    a.k_idx = p->k_indices; a.k_sc = p->k_scales; a.v_idx = p->v_indices; a.v_sc = p->v_scales;
+    float* sc = reinterpret_cast<float*>(p->scratch);
+    a.partial_out = sc;
+    a.partial_max = sc + (size_t)p->num_q_heads * P * p->head_dim;
+    a.partial_sum = a.partial_max + (size_t)p->num_q_heads * P;
+    a.qjl_signs = p->qjl_signs; a.qjl_norms = p->qjl_norms; a.rq = p->rq; a.qjl_enabled = p->qjl_enabled ? 1 : 0;
+    a.dev_codebook = nullptr; a.dev_signs = nullptr;
+    a.hq = p->num_q_heads; a.hkv = p->num_kv_heads; a.head_dim = p->head_dim; a.nblk = p->head_dim / kBlock;
+    a.bits = p->bits; a.packed_dim = p->head_dim * p->bits / 8;
+    a.kv_len = p->kv_len; a.kv_stride = p->kv_stride; a.num_partitions = P;
+    a.part_size = ((p->kv_len + P - 1) / P + kWarps - 1) / kWarps * kWarps;
+    if (a.part_size < kWarps) a.part_size = kWarps;
+    const int ob = p->outlier_blocks < 0 || p->outlier_blocks >= a.nblk ? a.nblk : p->outlier_blocks;
+    a.outlier_mode = ob >= a.nblk ? 1 : (ob == 0 ? 0 : 2);
+    a.softmax_scale = p->softmax_scale;
+    a.sign_mag = cpu_sign_magnitude();
+    return run_decode(a, cn, co, p->q_dtype, p->out, p->out_dtype, p->lse_out, as_stream(stream));
+}
+
+int tqb_lse_combine(const float* partial_out, const float* partial_lse, int32_t num_shards, int32_t num_q_heads,
+                    int32_t head_dim, void* out, int32_t out_dtype, tqb_stream_t stream) {
+    if (!partial_out || !partial_lse || !out) return TQB_ERR_NULL_POINTER;
+    if (num_shards <= 0 || num_q_heads <= 0 || head_dim <= 0) return TQB_ERR_INVALID_ARGUMENT;
+    cudaStream_t s = as_stream(stream);
+    if (out_dtype == TQB_F32)
+        lse_combine_kernel<float><<<num_q_heads, 128, 0, s>>>(partial_out, partial_lse, num_shards, num_q_heads, head_dim, (float*)out);
+    else if (out_dtype == TQB_F16)
+        lse_combine_kernel<__half><<<num_q_heads, 128, 0, s>>>(partial_out, partial_lse, num_shards, num_q_heads, head_dim, (__half*)out);
+    else if (out_dtype == TQB_BF16)
+        lse_combine_kernel<__nv_bfloat16><<<num_q_heads, 128, 0, s>>>(partial_out, partial_lse, num_shards, num_q_heads, head_dim, (__nv_bfloat16*)out);
+    else return TQB_ERR_INVALID_ARGUMENT;
+    return check_launch(s);
+}
+
+int tqb_fused_attention(const float* q, const uint8_t* k_indices, const uint16_t* k_scales, const uint8_t* v_indices,
+                        const uint16_t* v_scales, const float* codebook, const float* sign_pattern, float* output,
+                        float* partial_out, float* partial_max, float* partial_sum, const uint8_t* qjl_signs,
+                        const uint16_t* qjl_residual_norms, const float* rq, int32_t qjl_enabled,
+                        int32_t num_attention_heads, int32_t num_kv_heads, int32_t head_dim, int32_t kv_len,
+                        int32_t kv_stride, int32_t packed_dim, int32_t num_qblocks, int32_t bits, float softmax_scale,
+                        int32_t num_partitions, tqb_stream_t stream) {
+    if (kv_len == 0 || num_kv_heads == 0) return TQB_OK;  // tq_attention_kernel.cu:366
+    if (bits < 2 || bits > 4) return TQB_ERR_UNSUPPORTED_BITS;
+    if (head_dim <= 0 || head_dim % kBlock != 0) return TQB_ERR_INVALID_DIMENSION;
+    if (head_dim > 256) return TQB_ERR_UNSUPPORTED;  // the reference itself stops at 8 blocks (TQ_NUM_WARPS)
+    if (num_qblocks != head_dim / kBlock || packed_dim != head_dim * bits / 8) return TQB_ERR_DIMENSION_MISMATCH;
+    if (num_attention_heads <= 0 || num_kv_heads < 0 || num_attention_heads % num_kv_heads != 0 || num_partitions <= 0)
+        return TQB_ERR_INVALID_ARGUMENT;
+    if (kv_len < 0 || kv_len > kv_stride) return TQB_ERR_RANGE_OUT_OF_BOUNDS;
+    if (!q || !k_indices || !k_scales || !v_indices || !v_scales || !codebook || !sign_pattern || !output ||
+        !partial_out || !partial_max || !partial_sum)
+        return TQB_ERR_NULL_POINTER;
+    if (qjl_enabled && (!qjl_signs || !qjl_residual_norms || !rq)) return TQB_ERR_NULL_POINTER;
+    if (((uintptr_t)k_indices % 4) || ((uintptr_t)v_indices % 4) || ((uintptr_t)qjl_signs % 4)) return TQB_ERR_MISALIGNED;
+    Codebook dummy{};
+    dummy.n = 1 << bits;
+    DecodeArgs a{};
+    a.q = q;
+    a.k_idx = k_indices; a.k_sc = k_scales; a.v_idx = v_indices; a.v_sc = v_scales;
+    a.partial_out = partial_out; a.partial_max = partial_max; a.partial_sum = partial_sum;
+    a.qjl_signs = qjl_signs; a.qjl_norms = qjl_residual_norms; a.rq = rq; a.qjl_enabled = qjl_enabled ? 1 : 0;
+    a.dev_codebook = codebook; a.dev_signs = sign_pattern;
+    a.hq = num_attention_heads; a.hkv = num_kv_heads; a.head_dim = head_dim; a.nblk = num_qblocks;
+    a.bits = bits; a.packed_dim = packed_dim;
+    a.kv_len = kv_len; a.kv_stride = kv_stride; a.num_partitions = num_partitions;
+    a.part_size = ((kv_len + num_partitions - 1) / num_partitions + kWarps - 1) / kWarps * kWarps;
+    a.outlier_mode = 1;  // the caller's codebook decodes every block
+    a.softmax_scale = softmax_scale;
+    a.sign_mag = 1.0f;
+    return run_decode(a, dummy, dummy, TQB_F32, output, TQB_F32, nullptr, as_stream(stream));
+}
+
+void tq_fused_attention(const float* q, const uint8_t* k_indices, const uint16_t* k_scales, const uint8_t* v_indices,
+                        const uint16_t* v_scales, const float* codebook, const float* sign_pattern, float* output,
+                        float* partial_out, float* partial_max, float* partial_sum, const uint8_t* qjl_signs,
+                        const uint16_t* qjl_residual_norms, const float* rq, int32_t qjl_enabled,
+                        int32_t num_attention_heads, int32_t num_kv_heads, int32_t head_dim, int32_t kv_len,
+                        int32_t kv_stride, int32_t packed_dim, int32_t num_qblocks, int32_t bits, float softmax_scale,
+                        int32_t num_partitions, tqb_stream_t stream) {
+    (void)tqb_fused_attention(q, k_indices, k_scales, v_indices, v_scales, codebook, sign_pattern, output, partial_out,
+                              partial_max, partial_sum, qjl_signs, qjl_residual_norms, rq, qjl_enabled,
+                              num_attention_heads, num_kv_heads, head_dim, kv_len, kv_stride, packed_dim, num_qblocks,
+                              bits, softmax_scale, num_partitions, stream);
+}
+
+}  // extern "C"

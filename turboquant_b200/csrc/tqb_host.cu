@@ -1,0 +1,605 @@
+// Host-side cache objects above the kernels: PqoCache (src/cache/pqo.rs) over
+// CompressedStorage (src/cache/storage.rs) and QuantizedKVCache (src/attention.rs).
+// They own device memory, keep the reference's growth policy and error behaviour, and
+// enqueue the library's own entry points; there is no CPU implementation behind them.
+#include <algorithm>
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "tqb_common.cuh"
+
+namespace {
+
+using namespace tqb;
+
+int cuda_fail(cudaError_t e) {
+    set_cuda_error(e);
+    return e == cudaErrorMemoryAllocation ? TQB_ERR_OUT_OF_MEMORY : TQB_ERR_CUDA;
+}
+#define TQB_CUDA(call)                          \
+    do {                                        \
+        cudaError_t e__ = (call);               \
+        if (e__ != cudaSuccess) return cuda_fail(e__); \
+    } while (0)
+#define TQB_TRY(call)                 \
+    do {                              \
+        int st__ = (call);            \
+        if (st__ != TQB_OK) return st__; \
+    } while (0)
+
+size_t dtype_size(int dt) { return dt == TQB_F32 ? 4 : 2; }
+
+// A device buffer that only grows.
+struct DevBuf {
+    void* p = nullptr;
+    size_t bytes = 0;
+    int reserve(size_t need) {
+        if (need <= bytes) return TQB_OK;
+        if (p) TQB_CUDA(cudaFree(p));
+        p = nullptr;
+        bytes = 0;
+        TQB_CUDA(cudaMalloc(&p, need));
+        bytes = need;
+        return TQB_OK;
+    }
+    void release() {
+        if (p) cudaFree(p);
+        p = nullptr;
+        bytes = 0;
+    }
+};
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------
+// PqoCache
+// ---------------------------------------------------------------------------------------
+struct tqb_pqo_cache {
+    tqb_cache_config cfg;
+    int nblk, packed_dim, heads;  // heads = batch * num_kv_heads
+    struct Layer {
+        uint8_t *ki = nullptr, *vi = nullptr;
+        uint16_t *ks = nullptr, *vs = nullptr;
+        int64_t cap = 0, len = 0;
+        bool active = false;
+    };
+    std::vector<Layer> layers;
+    DevBuf stage_k, stage_v, stage_q, stage_out, scratch;
+
+    void free_layer(Layer& l) {
+        if (l.ki) cudaFree(l.ki);
+        if (l.vi) cudaFree(l.vi);
+        if (l.ks) cudaFree(l.ks);
+        if (l.vs) cudaFree(l.vs);
+        l = Layer{};
+    }
+
+    // CompressedStorage::ensure_capacity (src/cache/storage.rs:108-143): grow to
+    // needed + max(needed / 4, 128), zero-filled, old rows copied per head.
+    int ensure_capacity(int layer, int64_t needed, cudaStream_t s) {
+        Layer& l = layers[layer];
+        if (l.cap >= needed) return TQB_OK;
+        const int64_t grow = std::max<int64_t>(needed / 4, 128);
+        const int64_t new_cap = needed + grow;
+        Layer nl;
+        nl.cap = new_cap;
+        nl.len = l.len;
+        nl.active = l.active;
+        const size_t ib = (size_t)heads * new_cap * packed_dim;
+        const size_t sb = (size_t)heads * new_cap * nblk * sizeof(uint16_t);
+        cudaError_t e;
+        if ((e = cudaMalloc((void**)&nl.ki, ib)) != cudaSuccess || (e = cudaMalloc((void**)&nl.vi, ib)) != cudaSuccess ||
+            (e = cudaMalloc((void**)&nl.ks, sb)) != cudaSuccess || (e = cudaMalloc((void**)&nl.vs, sb)) != cudaSuccess) {
+            free_layer(nl);
+            return cuda_fail(e);
+        }
+        TQB_CUDA(cudaMemsetAsync(nl.ki, 0, ib, s));
+        TQB_CUDA(cudaMemsetAsync(nl.vi, 0, ib, s));
+        TQB_CUDA(cudaMemsetAsync(nl.ks, 0, sb, s));
+        TQB_CUDA(cudaMemsetAsync(nl.vs, 0, sb, s));
+        if (l.len > 0) {
+            const size_t iw = (size_t)l.len * packed_dim, sw = (size_t)l.len * nblk * 2;
+            TQB_CUDA(cudaMemcpy2DAsync(nl.ki, (size_t)new_cap * packed_dim, l.ki, (size_t)l.cap * packed_dim, iw, heads,
+                                       cudaMemcpyDeviceToDevice, s));
+            TQB_CUDA(cudaMemcpy2DAsync(nl.vi, (size_t)new_cap * packed_dim, l.vi, (size_t)l.cap * packed_dim, iw, heads,
+                                       cudaMemcpyDeviceToDevice, s));
+            TQB_CUDA(cudaMemcpy2DAsync(nl.ks, (size_t)new_cap * nblk * 2, l.ks, (size_t)l.cap * nblk * 2, sw, heads,
+                                       cudaMemcpyDeviceToDevice, s));
+            TQB_CUDA(cudaMemcpy2DAsync(nl.vs, (size_t)new_cap * nblk * 2, l.vs, (size_t)l.cap * nblk * 2, sw, heads,
+                                       cudaMemcpyDeviceToDevice, s));
+        }
+        if (l.ki) {
+            TQB_CUDA(cudaStreamSynchronize(s));  // the old buffers may still be read by queued work
+            free_layer(l);
+        }
+        l = nl;
+        return TQB_OK;
+    }
+
+    // quantize_and_store (src/cache/pqo.rs:64-104)
+    int quantize_and_store(int layer, const void* k_dev, const void* v_dev, int dtype, int new_tokens, cudaStream_t s) {
+        Layer& l0 = layers[layer];
+        const int64_t old_len = l0.len;
+        TQB_TRY(ensure_capacity(layer, old_len + new_tokens, s));
+        Layer& l = layers[layer];
+        const int64_t rows = (int64_t)heads * new_tokens;
+        TQB_TRY(tqb_block_quantize(cfg.bits, cfg.head_dim, cfg.norm_mode, cfg.outlier_blocks, k_dev, dtype, rows, 0, l.ki,
+                                   l.ks, new_tokens, l.cap, old_len, s));
+        TQB_TRY(tqb_block_quantize(cfg.bits, cfg.head_dim, cfg.norm_mode, cfg.outlier_blocks, v_dev, dtype, rows, 0, l.vi,
+                                   l.vs, new_tokens, l.cap, old_len, s));
+        l.len = old_len + new_tokens;
+        l.active = true;
+        return TQB_OK;
+    }
+
+    int dequantize_full(int layer, void* k_out, void* v_out, int dtype, bool host, cudaStream_t s) {
+        Layer& l = layers[layer];
+        if (l.len == 0) return TQB_OK;
+        const int64_t rows = (int64_t)heads * l.len;
+        const size_t bytes = (size_t)rows * cfg.head_dim * dtype_size(dtype);
+        void* kd = k_out;
+        void* vd = v_out;
+        if (host) {
+            TQB_TRY(stage_k.reserve(bytes));
+            TQB_TRY(stage_v.reserve(bytes));
+            kd = stage_k.p;
+            vd = stage_v.p;
+        }
+        TQB_TRY(tqb_block_dequantize(cfg.bits, cfg.head_dim, cfg.norm_mode, cfg.outlier_blocks, l.ki, l.ks, rows, l.len,
+                                     l.cap, 0, kd, dtype, s));
+        TQB_TRY(tqb_block_dequantize(cfg.bits, cfg.head_dim, cfg.norm_mode, cfg.outlier_blocks, l.vi, l.vs, rows, l.len,
+                                     l.cap, 0, vd, dtype, s));
+        if (host) {
+            TQB_CUDA(cudaMemcpyAsync(k_out, kd, bytes, cudaMemcpyDeviceToHost, s));
+            TQB_CUDA(cudaMemcpyAsync(v_out, vd, bytes, cudaMemcpyDeviceToHost, s));
+        }
+        return TQB_OK;
+    }
+
+    int attend(int layer, const void* q_dev, int dtype, int num_q_heads, float softmax_scale, void* out_dev, int out_dtype,
+               float* lse_out, cudaStream_t s) {
+        Layer& l = layers[layer];
+        tqb_decode_params p{};
+        p.q = q_dev;
+        p.k_indices = l.ki; p.k_scales = l.ks; p.v_indices = l.vi; p.v_scales = l.vs;
+        p.out = out_dev;
+        p.lse_out = lse_out;
+        p.q_dtype = dtype;
+        p.out_dtype = out_dtype;
+        p.bits = cfg.bits; p.head_dim = cfg.head_dim; p.norm_mode = cfg.norm_mode; p.outlier_blocks = cfg.outlier_blocks;
+        p.num_q_heads = cfg.batch * num_q_heads;
+        p.num_kv_heads = heads;
+        p.kv_len = (int32_t)l.len;
+        p.kv_stride = (int32_t)l.cap;
+        p.num_partitions = tqb_decode_num_partitions(heads, (int32_t)l.len);
+        p.softmax_scale = softmax_scale;
+        const size_t need = tqb_decode_scratch_bytes(p.num_q_heads, cfg.head_dim, p.num_partitions);
+        if (need > scratch.bytes) {
+            TQB_CUDA(cudaStreamSynchronize(s));
+            TQB_TRY(scratch.reserve(need + need / 4));
+        }
+        p.scratch = scratch.p;
+        p.scratch_bytes = scratch.bytes;
+        return tqb_decode_attention(&p, s);
+    }
+};
+
+extern "C" {
+
+int tqb_pqo_cache_create(const tqb_cache_config* cfg, tqb_pqo_cache** out) {
+    if (!cfg || !out) return TQB_ERR_NULL_POINTER;
+    *out = nullptr;
+    // src/cache/pqo.rs:32-39, src/cache/precomputed/mod.rs:46-51
+    if (cfg->head_dim <= 0 || cfg->head_dim % kBlock != 0) return TQB_ERR_INVALID_DIMENSION;
+    if (cfg->bits < 3 || cfg->bits > 4) return TQB_ERR_UNSUPPORTED_BITS;
+    if (cfg->head_dim > 256) return TQB_ERR_UNSUPPORTED;
+    if (cfg->num_kv_heads <= 0 || cfg->num_layers <= 0 || cfg->batch <= 0) return TQB_ERR_INVALID_ARGUMENT;
+    if (cfg->norm_mode != TQB_MAXNORM && cfg->norm_mode != TQB_L2NORM) return TQB_ERR_INVALID_ARGUMENT;
+    tqb_pqo_cache* c = new (std::nothrow) tqb_pqo_cache();
+    if (!c) return TQB_ERR_OUT_OF_MEMORY;
+    c->cfg = *cfg;
+    c->nblk = cfg->head_dim / kBlock;
+    c->packed_dim = cfg->head_dim * cfg->bits / 8;
+    c->heads = cfg->batch * cfg->num_kv_heads;
+    c->layers.resize(cfg->num_layers);
+    *out = c;
+    return TQB_OK;
+}
+
+void tqb_pqo_cache_destroy(tqb_pqo_cache* c) {
+    if (!c) return;
+    for (auto& l : c->layers) c->free_layer(l);
+    c->stage_k.release(); c->stage_v.release(); c->stage_q.release(); c->stage_out.release(); c->scratch.release();
+    delete c;
+}
+
+static int check_layer(const tqb_pqo_cache* c, int32_t layer) {
+    if (!c) return TQB_ERR_NULL_POINTER;
+    if (layer < 0 || layer >= (int32_t)c->layers.size()) return TQB_ERR_LAYER_OUT_OF_RANGE;
+    return TQB_OK;
+}
+
+int tqb_pqo_cache_prefill(tqb_pqo_cache* c, int32_t layer, const void* k, const void* v, int32_t dtype,
+                          int32_t new_tokens, void* k_out, void* v_out, int32_t host_buffers, tqb_stream_t stream) {
+    TQB_TRY(check_layer(c, layer));
+    if (new_tokens < 0) return TQB_ERR_INVALID_ARGUMENT;
+    if (dtype != TQB_F32 && dtype != TQB_F16 && dtype != TQB_BF16) return TQB_ERR_INVALID_ARGUMENT;
+    if (new_tokens == 0) return TQB_OK;
+    if (!k || !v) return TQB_ERR_NULL_POINTER;
+    cudaStream_t s = as_stream(stream);
+    const size_t bytes = (size_t)c->heads * new_tokens * c->cfg.head_dim * dtype_size(dtype);
+    const void* kd = k;
+    const void* vd = v;
+    if (host_buffers) {
+        TQB_TRY(c->stage_k.reserve(bytes));
+        TQB_TRY(c->stage_v.reserve(bytes));
+        TQB_CUDA(cudaMemcpyAsync(c->stage_k.p, k, bytes, cudaMemcpyHostToDevice, s));
+        TQB_CUDA(cudaMemcpyAsync(c->stage_v.p, v, bytes, cudaMemcpyHostToDevice, s));
+        kd = c->stage_k.p;
+        vd = c->stage_v.p;
+    }
+    const int64_t old_len = c->layers[layer].len;
+    TQB_TRY(c->quantize_and_store(layer, kd, vd, dtype, new_tokens, s));
+    // pqo.rs:194-199: the first prefill hands back the original tensors
+    if (old_len > 0 && k_out && v_out) TQB_TRY(c->dequantize_full(layer, k_out, v_out, dtype, host_buffers != 0, s));
+    return TQB_OK;
+}
+
+int tqb_pqo_cache_decode(tqb_pqo_cache* c, int32_t layer, const void* k, const void* v, const void* q, int32_t dtype,
+                         int32_t num_q_heads, float softmax_scale, void* out, int32_t host_buffers,
+                         tqb_stream_t stream) {
+    TQB_TRY(check_layer(c, layer));
+    if (!k || !v || !q || !out) return TQB_ERR_NULL_POINTER;
+    if (dtype != TQB_F32 && dtype != TQB_F16 && dtype != TQB_BF16) return TQB_ERR_INVALID_ARGUMENT;
+    if (num_q_heads <= 0 || num_q_heads % c->cfg.num_kv_heads != 0) return TQB_ERR_INVALID_ARGUMENT;
+    cudaStream_t s = as_stream(stream);
+    const size_t esz = dtype_size(dtype);
+    const size_t kv_bytes = (size_t)c->heads * c->cfg.head_dim * esz;
+    const size_t q_bytes = (size_t)c->cfg.batch * num_q_heads * c->cfg.head_dim * esz;
+    const void* kd = k;
+    const void* vd = v;
+    const void* qd = q;
+    void* od = out;
+    if (host_buffers) {
+        TQB_TRY(c->stage_k.reserve(kv_bytes));
+        TQB_TRY(c->stage_v.reserve(kv_bytes));
+        TQB_TRY(c->stage_q.reserve(q_bytes));
+        TQB_TRY(c->stage_out.reserve(q_bytes));
+        TQB_CUDA(cudaMemcpyAsync(c->stage_k.p, k, kv_bytes, cudaMemcpyHostToDevice, s));
+        TQB_CUDA(cudaMemcpyAsync(c->stage_v.p, v, kv_bytes, cudaMemcpyHostToDevice, s));
+        TQB_CUDA(cudaMemcpyAsync(c->stage_q.p, q, q_bytes, cudaMemcpyHostToDevice, s));
+        kd = c->stage_k.p; vd = c->stage_v.p; qd = c->stage_q.p; od = c->stage_out.p;
+    }
+    TQB_TRY(c->quantize_and_store(layer, kd, vd, dtype, 1, s));
+    TQB_TRY(c->attend(layer, qd, dtype, num_q_heads, softmax_scale, od, dtype, nullptr, s));
+    if (host_buffers) TQB_CUDA(cudaMemcpyAsync(out, od, q_bytes, cudaMemcpyDeviceToHost, s));
+    return TQB_OK;
+}
+
+int tqb_pqo_cache_attend_partial(tqb_pqo_cache* c, int32_t layer, const void* q, int32_t dtype, int32_t num_q_heads,
+                                 float softmax_scale, float* out_unnorm, float* lse_out, tqb_stream_t stream) {
+    TQB_TRY(check_layer(c, layer));
+    if (!q || !out_unnorm || !lse_out) return TQB_ERR_NULL_POINTER;
+    if (num_q_heads <= 0 || num_q_heads % c->cfg.num_kv_heads != 0) return TQB_ERR_INVALID_ARGUMENT;
+    return c->attend(layer, q, dtype, num_q_heads, softmax_scale, out_unnorm, TQB_F32, lse_out, as_stream(stream));
+}
+
+int tqb_pqo_cache_dequantize_full(tqb_pqo_cache* c, int32_t layer, void* k_out, void* v_out, int32_t dtype,
+                                  int32_t host_buffers, tqb_stream_t stream) {
+    TQB_TRY(check_layer(c, layer));
+    if (!k_out || !v_out) return TQB_ERR_NULL_POINTER;
+    if (dtype != TQB_F32 && dtype != TQB_F16 && dtype != TQB_BF16) return TQB_ERR_INVALID_ARGUMENT;
+    return c->dequantize_full(layer, k_out, v_out, dtype, host_buffers != 0, as_stream(stream));
+}
+
+int64_t tqb_pqo_cache_seq_len(const tqb_pqo_cache* c, int32_t layer) {
+    return check_layer(c, layer) == TQB_OK ? c->layers[layer].len : -1;
+}
+int64_t tqb_pqo_cache_capacity(const tqb_pqo_cache* c, int32_t layer) {
+    return check_layer(c, layer) == TQB_OK ? c->layers[layer].cap : -1;
+}
+
+// CompressedStorage::reset (src/cache/storage.rs:175-185): drops the buffers.
+int tqb_pqo_cache_reset(tqb_pqo_cache* c) {
+    if (!c) return TQB_ERR_NULL_POINTER;
+    TQB_CUDA(cudaDeviceSynchronize());
+    for (auto& l : c->layers) c->free_layer(l);
+    return TQB_OK;
+}
+
+// CompressedStorage::memory_usage (src/cache/storage.rs:188-202): counts stored tokens.
+size_t tqb_pqo_cache_memory_usage(const tqb_pqo_cache* c) {
+    if (!c) return 0;
+    size_t total = 0;
+    for (const auto& l : c->layers) {
+        if (l.len == 0) continue;
+        total += 2 * (size_t)c->heads * l.len * c->packed_dim;
+        total += 2 * (size_t)c->heads * l.len * c->nblk * 2;
+    }
+    return total;
+}
+
+int tqb_pqo_cache_layer_ptrs(const tqb_pqo_cache* c, int32_t layer, const uint8_t** k_indices, const uint16_t** k_scales,
+                             const uint8_t** v_indices, const uint16_t** v_scales) {
+    TQB_TRY(check_layer(c, layer));
+    const auto& l = c->layers[layer];
+    if (k_indices) *k_indices = l.ki;
+    if (k_scales) *k_scales = l.ks;
+    if (v_indices) *v_indices = l.vi;
+    if (v_scales) *v_scales = l.vs;
+    return TQB_OK;
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------------------
+// QuantizedKVCache
+// ---------------------------------------------------------------------------------------
+struct tqb_kv_cache {
+    tqb_config cfg;   // total bits
+    uint64_t qjl_seed;
+    int pb, sb;       // polar bytes and sign bytes per block
+    struct Side {
+        uint8_t* packed = nullptr;
+        uint16_t* scales = nullptr;
+        uint8_t* signs = nullptr;
+        uint16_t* rnorms = nullptr;
+        int64_t cap = 0;
+    };
+    struct Layer {
+        Side k, v;
+        int64_t nk = 0, nv = 0;
+    };
+    std::vector<Layer> layers;
+    uint32_t* rbits = nullptr;
+    DevBuf stage_a, stage_b, wv_scratch;
+
+    void free_side(Side& s) {
+        if (s.packed) cudaFree(s.packed);
+        if (s.scales) cudaFree(s.scales);
+        if (s.signs) cudaFree(s.signs);
+        if (s.rnorms) cudaFree(s.rnorms);
+        s = Side{};
+    }
+
+    int reserve(Side& s, int64_t used, int64_t needed, cudaStream_t st) {
+        if (s.cap >= needed) return TQB_OK;
+        int64_t new_cap = std::max<int64_t>(needed, std::max<int64_t>(2 * s.cap, 256));
+        Side n;
+        n.cap = new_cap;
+        cudaError_t e;
+        if ((e = cudaMalloc((void**)&n.packed, (size_t)new_cap * pb)) != cudaSuccess ||
+            (e = cudaMalloc((void**)&n.scales, (size_t)new_cap * 2)) != cudaSuccess ||
+            (e = cudaMalloc((void**)&n.signs, (size_t)new_cap * sb)) != cudaSuccess ||
+            (e = cudaMalloc((void**)&n.rnorms, (size_t)new_cap * 2)) != cudaSuccess) {
+            free_side(n);
+            return cuda_fail(e);
+        }
+        if (used > 0) {
+            TQB_CUDA(cudaMemcpyAsync(n.packed, s.packed, (size_t)used * pb, cudaMemcpyDeviceToDevice, st));
+            TQB_CUDA(cudaMemcpyAsync(n.scales, s.scales, (size_t)used * 2, cudaMemcpyDeviceToDevice, st));
+            TQB_CUDA(cudaMemcpyAsync(n.signs, s.signs, (size_t)used * sb, cudaMemcpyDeviceToDevice, st));
+            TQB_CUDA(cudaMemcpyAsync(n.rnorms, s.rnorms, (size_t)used * 2, cudaMemcpyDeviceToDevice, st));
+        }
+        TQB_CUDA(cudaStreamSynchronize(st));
+        free_side(s);
+        s = n;
+        return TQB_OK;
+    }
+};
+
+extern "C" {
+
+int tqb_kv_cache_create(const tqb_config* cfg, int32_t num_layers, uint64_t qjl_seed, tqb_kv_cache** out) {
+    if (!cfg || !out) return TQB_ERR_NULL_POINTER;
+    *out = nullptr;
+    // the QJL stage needs 3 or 4 total bits (src/qjl.rs:277-279); the config itself is
+    // validated as TurboQuantConfig::new does (src/packed/mod.rs:124-132)
+    int st = tqb_config_validate(cfg);
+    if (st != TQB_OK && st != TQB_ERR_UNSUPPORTED) return st;
+    if (cfg->bits < 3) return TQB_ERR_UNSUPPORTED_BITS;
+    tqb_config polar = *cfg;
+    polar.bits = cfg->bits - 1;
+    TQB_TRY(tqb_config_validate(&polar));
+    if (num_layers < 0) return TQB_ERR_INVALID_ARGUMENT;
+    tqb_kv_cache* c = new (std::nothrow) tqb_kv_cache();
+    if (!c) return TQB_ERR_OUT_OF_MEMORY;
+    c->cfg = *cfg;
+    c->qjl_seed = qjl_seed;
+    c->pb = (int)tqb_packed_bytes(polar.bits, cfg->dim);
+    c->sb = cfg->dim / 8;
+    c->layers.resize(num_layers);
+    std::vector<uint32_t> rb((size_t)cfg->dim * (cfg->dim / 32));
+    st = tqb_qjl_rademacher_bits(cfg->dim, qjl_seed, rb.data());
+    if (st == TQB_OK) {
+        cudaError_t e = cudaMalloc((void**)&c->rbits, rb.size() * 4);
+        if (e == cudaSuccess) e = cudaMemcpy(c->rbits, rb.data(), rb.size() * 4, cudaMemcpyHostToDevice);
+        if (e != cudaSuccess) st = cuda_fail(e);
+    }
+    if (st != TQB_OK) {
+        if (c->rbits) cudaFree(c->rbits);
+        delete c;
+        return st;
+    }
+    *out = c;
+    return TQB_OK;
+}
+
+void tqb_kv_cache_destroy(tqb_kv_cache* c) {
+    if (!c) return;
+    for (auto& l : c->layers) {
+        c->free_side(l.k);
+        c->free_side(l.v);
+    }
+    if (c->rbits) cudaFree(c->rbits);
+    c->stage_a.release(); c->stage_b.release(); c->wv_scratch.release();
+    delete c;
+}
+
+static int kv_check_layer(const tqb_kv_cache* c, int32_t layer) {
+    if (!c) return TQB_ERR_NULL_POINTER;
+    if (layer < 0 || layer >= (int32_t)c->layers.size()) return TQB_ERR_LAYER_OUT_OF_RANGE;  // attention.rs:95-100
+    return TQB_OK;
+}
+
+int tqb_kv_cache_push_batch(tqb_kv_cache* c, int32_t layer, const float* keys, const float* values, int64_t n,
+                            int64_t vec_dim, tqb_stream_t stream) {
+    TQB_TRY(kv_check_layer(c, layer));
+    if (vec_dim != c->cfg.dim) return TQB_ERR_DIMENSION_MISMATCH;  // attention.rs:241-242, :102-116
+    if (n < 0) return TQB_ERR_INVALID_ARGUMENT;
+    if (n == 0) return TQB_OK;
+    if (!keys || !values) return TQB_ERR_NULL_POINTER;
+    cudaStream_t s = as_stream(stream);
+    auto& L = c->layers[layer];
+    const size_t bytes = (size_t)n * c->cfg.dim * sizeof(float);
+    TQB_TRY(c->stage_a.reserve(bytes));
+    TQB_TRY(c->stage_b.reserve(bytes));
+    TQB_TRY(c->reserve(L.k, L.nk, L.nk + n, s));
+    TQB_TRY(c->reserve(L.v, L.nv, L.nv + n, s));
+    TQB_CUDA(cudaMemcpyAsync(c->stage_a.p, keys, bytes, cudaMemcpyHostToDevice, s));
+    TQB_CUDA(cudaMemcpyAsync(c->stage_b.p, values, bytes, cudaMemcpyHostToDevice, s));
+    TQB_TRY(tqb_qjl_quantize_batch(&c->cfg, c->rbits, (const float*)c->stage_a.p, n, L.k.packed + L.nk * c->pb,
+                                   L.k.scales + L.nk, L.k.signs + L.nk * c->sb, L.k.rnorms + L.nk, s));
+    TQB_TRY(tqb_qjl_quantize_batch(&c->cfg, c->rbits, (const float*)c->stage_b.p, n, L.v.packed + L.nv * c->pb,
+                                   L.v.scales + L.nv, L.v.signs + L.nv * c->sb, L.v.rnorms + L.nv, s));
+    TQB_CUDA(cudaStreamSynchronize(s));
+    L.nk += n;
+    L.nv += n;
+    return TQB_OK;
+}
+
+int tqb_kv_cache_attention_scores(tqb_kv_cache* c, int32_t layer, const float* query, int64_t query_len, float* scores,
+                                  tqb_stream_t stream) {
+    TQB_TRY(kv_check_layer(c, layer));
+    if (query_len != c->cfg.dim) return TQB_ERR_DIMENSION_MISMATCH;
+    auto& L = c->layers[layer];
+    if (L.nk == 0) return TQB_OK;  // attention.rs:325-327
+    if (!query || !scores) return TQB_ERR_NULL_POINTER;
+    cudaStream_t s = as_stream(stream);
+    const int d = c->cfg.dim;
+    TQB_TRY(c->stage_a.reserve(std::max<size_t>(2 * d * sizeof(float), c->stage_a.bytes)));
+    TQB_TRY(c->stage_b.reserve((size_t)L.nk * sizeof(float)));
+    float* qd = (float*)c->stage_a.p;
+    float* rq = qd + d;
+    TQB_CUDA(cudaMemcpyAsync(qd, query, d * sizeof(float), cudaMemcpyHostToDevice, s));
+    TQB_TRY(tqb_qjl_query_projections(d, c->rbits, qd, 1, rq, s));
+    TQB_TRY(tqb_qjl_attention_scores(&c->cfg, qd, rq, L.k.packed, L.k.scales, L.k.signs, L.k.rnorms, L.nk,
+                                     (float*)c->stage_b.p, s));
+    TQB_CUDA(cudaMemcpyAsync(scores, c->stage_b.p, (size_t)L.nk * sizeof(float), cudaMemcpyDeviceToHost, s));
+    TQB_CUDA(cudaStreamSynchronize(s));
+    return TQB_OK;
+}
+
+int tqb_kv_cache_weighted_values(tqb_kv_cache* c, int32_t layer, const float* weights, int64_t num_weights, float* out,
+                                 tqb_stream_t stream) {
+    TQB_TRY(kv_check_layer(c, layer));
+    auto& L = c->layers[layer];
+    if (num_weights != L.nk) return TQB_ERR_DIMENSION_MISMATCH;  // attention.rs:373
+    if (!out) return TQB_ERR_NULL_POINTER;
+    cudaStream_t s = as_stream(stream);
+    const int d = c->cfg.dim;
+    const int64_t n = std::min(L.nv, num_weights);
+    if (n == 0) {
+        std::memset(out, 0, sizeof(float) * d);
+        return TQB_OK;
+    }
+    if (!weights) return TQB_ERR_NULL_POINTER;
+    TQB_TRY(c->stage_a.reserve((size_t)n * sizeof(float)));
+    TQB_TRY(c->stage_b.reserve((size_t)d * sizeof(float)));
+    TQB_TRY(c->wv_scratch.reserve(tqb_weighted_values_scratch_bytes(d)));
+    TQB_CUDA(cudaMemcpyAsync(c->stage_a.p, weights, (size_t)n * sizeof(float), cudaMemcpyHostToDevice, s));
+    TQB_TRY(tqb_weighted_values(&c->cfg, (const float*)c->stage_a.p, L.v.packed, L.v.scales, n, (float*)c->stage_b.p,
+                                c->wv_scratch.p, c->wv_scratch.bytes, s));
+    TQB_CUDA(cudaMemcpyAsync(out, c->stage_b.p, (size_t)d * sizeof(float), cudaMemcpyDeviceToHost, s));
+    TQB_CUDA(cudaStreamSynchronize(s));
+    return TQB_OK;
+}
+
+int tqb_kv_cache_dequantize_range(tqb_kv_cache* c, int32_t layer, int64_t start, int64_t end, int32_t is_keys, float* out,
+                                  tqb_stream_t stream) {
+    TQB_TRY(kv_check_layer(c, layer));
+    auto& L = c->layers[layer];
+    const auto& S = is_keys ? L.k : L.v;
+    const int64_t count = is_keys ? L.nk : L.nv;
+    if (!(start <= end && end <= count) || start < 0) return TQB_ERR_RANGE_OUT_OF_BOUNDS;  // attention.rs:118-132
+    const int64_t n = end - start;
+    if (n == 0) return TQB_OK;
+    if (!out) return TQB_ERR_NULL_POINTER;
+    cudaStream_t s = as_stream(stream);
+    const size_t bytes = (size_t)n * c->cfg.dim * sizeof(float);
+    TQB_TRY(c->stage_a.reserve(bytes));
+    tqb_config polar = c->cfg;
+    polar.bits = c->cfg.bits - 1;
+    TQB_TRY(tqb_dequantize_batch(&polar, S.packed + start * c->pb, S.scales + start, n, (float*)c->stage_a.p, s));
+    TQB_CUDA(cudaMemcpyAsync(out, c->stage_a.p, bytes, cudaMemcpyDeviceToHost, s));
+    TQB_CUDA(cudaStreamSynchronize(s));
+    return TQB_OK;
+}
+
+int tqb_kv_cache_export_packed_range(tqb_kv_cache* c, int32_t layer, int64_t start, int64_t end, int32_t is_keys,
+                                     uint8_t* packed_bytes, uint16_t* scales, uint8_t* qjl_signs,
+                                     uint16_t* residual_norms, tqb_stream_t stream) {
+    TQB_TRY(kv_check_layer(c, layer));
+    auto& L = c->layers[layer];
+    const auto& S = is_keys ? L.k : L.v;
+    const int64_t count = is_keys ? L.nk : L.nv;
+    if (!(start <= end && end <= count) || start < 0) return TQB_ERR_RANGE_OUT_OF_BOUNDS;
+    const int64_t n = end - start;
+    if (n == 0) return TQB_OK;
+    if (!packed_bytes || !scales) return TQB_ERR_NULL_POINTER;
+    cudaStream_t s = as_stream(stream);
+    TQB_CUDA(cudaMemcpyAsync(packed_bytes, S.packed + start * c->pb, (size_t)n * c->pb, cudaMemcpyDeviceToHost, s));
+    TQB_CUDA(cudaMemcpyAsync(scales, S.scales + start, (size_t)n * 2, cudaMemcpyDeviceToHost, s));
+    if (qjl_signs) TQB_CUDA(cudaMemcpyAsync(qjl_signs, S.signs + start * c->sb, (size_t)n * c->sb, cudaMemcpyDeviceToHost, s));
+    if (residual_norms) TQB_CUDA(cudaMemcpyAsync(residual_norms, S.rnorms + start, (size_t)n * 2, cudaMemcpyDeviceToHost, s));
+    TQB_CUDA(cudaStreamSynchronize(s));
+    return TQB_OK;
+}
+
+int tqb_kv_cache_import_packed_range(tqb_kv_cache* c, int32_t layer, int32_t polar_bits, const uint8_t* packed_bytes,
+                                     const uint16_t* scales, const uint8_t* qjl_signs_flat,
+                                     const uint16_t* residual_norms, int64_t count, int64_t bytes_per_block,
+                                     int64_t signs_per_block, int32_t is_keys, tqb_stream_t stream) {
+    TQB_TRY(kv_check_layer(c, layer));
+    if (count < 0) return TQB_ERR_INVALID_ARGUMENT;
+    if (count == 0) return TQB_OK;
+    if (polar_bits != c->cfg.bits - 1) return TQB_ERR_UNSUPPORTED;  // one polar width per cache in this build
+    if (bytes_per_block != c->pb || signs_per_block != c->sb) return TQB_ERR_DIMENSION_MISMATCH;
+    if (!packed_bytes || !scales || !qjl_signs_flat || !residual_norms) return TQB_ERR_NULL_POINTER;
+    cudaStream_t s = as_stream(stream);
+    auto& L = c->layers[layer];
+    auto& S = is_keys ? L.k : L.v;
+    int64_t& used = is_keys ? L.nk : L.nv;
+    TQB_TRY(c->reserve(S, used, used + count, s));
+    TQB_CUDA(cudaMemcpyAsync(S.packed + used * c->pb, packed_bytes, (size_t)count * c->pb, cudaMemcpyHostToDevice, s));
+    TQB_CUDA(cudaMemcpyAsync(S.scales + used, scales, (size_t)count * 2, cudaMemcpyHostToDevice, s));
+    TQB_CUDA(cudaMemcpyAsync(S.signs + used * c->sb, qjl_signs_flat, (size_t)count * c->sb, cudaMemcpyHostToDevice, s));
+    TQB_CUDA(cudaMemcpyAsync(S.rnorms + used, residual_norms, (size_t)count * 2, cudaMemcpyHostToDevice, s));
+    TQB_CUDA(cudaStreamSynchronize(s));
+    used += count;
+    return TQB_OK;
+}
+
+int64_t tqb_kv_cache_entry_count(const tqb_kv_cache* c, int32_t layer) {
+    return kv_check_layer(c, layer) == TQB_OK ? c->layers[layer].nk : -1;  // attention.rs:443-445
+}
+int32_t tqb_kv_cache_num_layers(const tqb_kv_cache* c) { return c ? (int32_t)c->layers.size() : 0; }
+
+size_t tqb_kv_cache_memory_usage(const tqb_kv_cache* c) {
+    if (!c) return 0;
+    // attention.rs:76-78: polar block (2 + packed) + signs + 2 bytes residual norm
+    const size_t per = 2 + (size_t)c->pb + c->sb + 2;
+    size_t total = 0;
+    for (const auto& l : c->layers) total += per * (size_t)(l.nk + l.nv);
+    return total;
+}
+
+size_t tqb_kv_cache_fp16_equivalent_memory(const tqb_kv_cache* c) {
+    if (!c) return 0;
+    size_t entries = 0;
+    for (const auto& l : c->layers) entries += (size_t)l.nk;
+    return entries * c->cfg.dim * 2 * 2;  // attention.rs:437-440
+}
+
+}  // extern "C"

@@ -1,0 +1,572 @@
+// Whole-vector ("core crate") kernels: PolarQuant quantize / dequantize, the QJL sign
+// sketch, query projections, inner-product scores and weighted values.
+//
+// Element e of a vector of dimension d = 32*EPL lives in lane e % 32, slot e / 32.  The
+// Walsh-Hadamard stages run in the reference's order h = 1, 2, 4, ... (src/rotation.rs:22-40):
+// h < 32 through __shfl_xor, h >= 32 between the slots of a lane.  Every stage pairs the
+// same two operands as the scalar loop, so the transform is bit-identical to it.
+//
+// The two order-sensitive reductions of the reference -- the L2 norm (src/quantize.rs:51-53)
+// and each Rademacher row product (src/qjl.rs:196-208) -- are sequential f32 sums.  They are
+// kept sequential: a warp stages 32 vectors in shared memory and lane r sums vector r, so all
+// lanes stay busy while each sum keeps the reference's left-to-right order.
+#include <float.h>
+
+#include "tqb_common.cuh"
+
+namespace tqb {
+namespace {
+
+constexpr int kTile = 32;  // vectors per warp tile
+
+// src/rotation.rs:47-70: the multiplier is odd, so the hash's low bit is the parity of seed+i.
+__device__ __forceinline__ float sign_of(uint64_t seed, int e) {
+    return ((seed + (uint64_t)e) & 1ULL) ? -1.0f : 1.0f;
+}
+
+template <int EPL>
+__device__ __forceinline__ void wht_lanes(float (&v)[EPL], int lane) {
+#pragma unroll
+    for (int h = 1; h < 32; h <<= 1) {
+        const bool upper = (lane & h) != 0;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) {
+            float other = __shfl_xor_sync(0xffffffffu, v[i], h);
+            v[i] = upper ? (other - v[i]) : (v[i] + other);
+        }
+    }
+#pragma unroll
+    for (int hs = 1; hs < EPL; hs <<= 1) {
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) {
+            if ((i & hs) == 0) {
+                float x = v[i], y = v[i + hs];
+                v[i] = x + y;
+                v[i + hs] = x - y;
+            }
+        }
+    }
+}
+
+// Codes of one vector (bytes in shared memory, dim entries) -> packed bytes, eight codes
+// (= `bits` bytes) per lane pass.  src/packed/mod.rs:242-309.
+__device__ __forceinline__ void pack_codes(const uint8_t* codes, uint8_t* out, int dim, int bits, int lane) {
+    for (int g = lane; g < dim / 8; g += 32) {
+        uint32_t acc = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc |= (uint32_t)codes[g * 8 + i] << (bits * i);
+        for (int b = 0; b < bits; ++b) out[g * bits + b] = (uint8_t)(acc >> (8 * b));
+    }
+}
+
+// Code of element e from the packed words of one vector, one word per lane.
+__device__ __forceinline__ uint32_t code_at(uint32_t word, int e, int bits) {
+    const int bitoff = e * bits;
+    const int wi = bitoff >> 5;
+    const uint32_t w0 = __shfl_sync(0xffffffffu, word, wi);
+    const uint32_t w1 = __shfl_sync(0xffffffffu, word, min(wi + 1, 31));
+    return __funnelshift_r(w0, w1, bitoff & 31) & ((1u << bits) - 1u);
+}
+
+struct WholeArgs {
+    const float* x;
+    long long n;
+    uint8_t* packed;
+    uint16_t* scales;
+    uint8_t* signs;       // QJL outputs (may be null)
+    uint16_t* rnorms;
+    const uint32_t* rbits;  // [dim][dim/32]
+    int bits;             // polar bits
+    int dim;
+    int pb;               // packed bytes per vector
+    uint64_t seed;
+    float inv_sqrt_d;
+};
+
+// Sequential Rademacher row products of one vector held in shared memory.
+// Lane handles rows lane, lane+32, ...; s_rb has row stride W+1 words.
+template <int EPL>
+__device__ __forceinline__ void rademacher_rows(const float* vec, const uint32_t* s_rb, int lane, float inv_sqrt_d,
+                                                float (&proj)[EPL]) {
+    constexpr int W = EPL;
+    float s[EPL];
+#pragma unroll
+    for (int k = 0; k < EPL; ++k) s[k] = 0.0f;
+#pragma unroll 1
+    for (int cw = 0; cw < W; ++cw) {
+        uint32_t rb[EPL];
+#pragma unroll
+        for (int k = 0; k < EPL; ++k) rb[k] = s_rb[(lane + 32 * k) * (W + 1) + cw];
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+            const uint32_t val = __float_as_uint(vec[cw * 32 + c]);
+#pragma unroll
+            for (int k = 0; k < EPL; ++k)
+                s[k] = s[k] + __uint_as_float(val ^ ((rb[k] << (31 - c)) & 0x80000000u));
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < EPL; ++k) proj[k] = s[k] * inv_sqrt_d;
+}
+
+// quantize_vec (src/quantize.rs:142-192) and, with QJL outputs requested,
+// quantize_with_qjl (src/qjl.rs:355-377).  One warp per tile of 32 vectors.
+template <int EPL, bool QJL>
+__global__ void whole_quantize_kernel(WholeArgs a, Codebook cb) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    constexpr int D = 32 * EPL;
+    constexpr int W = EPL;
+    const int warps = blockDim.x >> 5;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // layout: [rbits (D*(W+1) words, QJL only)] [boundaries 16] [centroids 16] then per warp:
+    // tile [32][D+1] floats, codes [D] bytes, stage [32*pb] bytes
+    uint32_t* s_rb = reinterpret_cast<uint32_t*>(smem_raw);
+    float* s_b = reinterpret_cast<float*>(s_rb + (QJL ? D * (W + 1) : 0));
+    float* s_c = s_b + 16;
+    const size_t per_warp = sizeof(float) * kTile * (D + 1) + D + (size_t)kTile * a.pb;
+    unsigned char* wbase = reinterpret_cast<unsigned char*>(s_c + 16) + (size_t)warp * ((per_warp + 15) / 16 * 16);
+    float* tile = reinterpret_cast<float*>(wbase);
+    uint8_t* codes = reinterpret_cast<uint8_t*>(tile + kTile * (D + 1));
+    uint8_t* stage = codes + D;
+
+    if (threadIdx.x < 16) {
+        s_b[threadIdx.x] = cb.b[threadIdx.x];
+        s_c[threadIdx.x] = cb.c[threadIdx.x];
+    }
+    if (QJL)
+        for (int i = threadIdx.x; i < D * W; i += blockDim.x) s_rb[(i / W) * (W + 1) + (i % W)] = a.rbits[i];
+    __syncthreads();
+
+    const long long tiles = (a.n + kTile - 1) / kTile;
+    for (long long t = (long long)blockIdx.x * warps + warp; t < tiles; t += (long long)gridDim.x * warps) {
+        const long long v0 = t * kTile;
+        const int nv = (int)min((long long)kTile, a.n - v0);
+        // stage the tile (coalesced 128-byte rows)
+        for (int r = 0; r < nv; ++r)
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) tile[r * (D + 1) + lane + 32 * i] = a.x[(v0 + r) * D + lane + 32 * i];
+        __syncwarp();
+        // l2_norm: lane r sums vector r left to right
+        float norm = 0.0f;
+        if (lane < nv) {
+            float s = 0.0f;
+            const float* row = tile + lane * (D + 1);
+#pragma unroll 8
+            for (int c = 0; c < D; ++c) s = s + row[c] * row[c];
+            norm = __fsqrt_rn(s);
+        }
+        float rnorm_mine = 0.0f;
+        for (int r = 0; r < nv; ++r) {
+            const float nr = __shfl_sync(0xffffffffu, norm, r);
+            const bool tiny = nr < kMinNorm;
+            const float inv = __fdiv_rn(1.0f, nr);
+            float x[EPL], v[EPL];
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) {
+                x[i] = tile[r * (D + 1) + lane + 32 * i];
+                float nx = tiny ? 0.0f : x[i] * inv;                 // normalize_inplace, quantize.rs:60-72
+                v[i] = nx * sign_of(a.seed, lane + 32 * i);          // rotation.rs:139-142
+            }
+            wht_lanes<EPL>(v, lane);
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) {
+                v[i] = v[i] * a.inv_sqrt_d;
+                codes[lane + 32 * i] = (uint8_t)bucket_index_n(v[i], s_b, cb.n);
+            }
+            __syncwarp();
+            pack_codes(codes, stage + (size_t)r * a.pb, D, a.bits, lane);
+            if (QJL) {
+                // dequantize (quantize.rs:225-239) with the f16-rounded scale, residual, norm, signs
+                const float sc = f16_bits_to_f32(f32_to_f16_bits(tiny ? 0.0f : nr));
+                float y[EPL];
+#pragma unroll
+                for (int i = 0; i < EPL; ++i) y[i] = s_c[codes[lane + 32 * i]];
+                wht_lanes<EPL>(y, lane);
+#pragma unroll
+                for (int i = 0; i < EPL; ++i) {
+                    float rec = ((y[i] * a.inv_sqrt_d) * sign_of(a.seed, lane + 32 * i)) * sc;
+                    tile[r * (D + 1) + lane + 32 * i] = x[i] - rec;  // compute_residual, qjl.rs:213-219
+                }
+            }
+            __syncwarp();
+        }
+        if (QJL) {
+            if (lane < nv) {
+                float s = 0.0f;
+                const float* row = tile + lane * (D + 1);
+#pragma unroll 8
+                for (int c = 0; c < D; ++c) s = s + row[c] * row[c];
+                rnorm_mine = __fsqrt_rn(s);
+                a.rnorms[v0 + lane] = f32_to_f16_bits(rnorm_mine);
+            }
+            for (int r = 0; r < nv; ++r) {
+                float proj[EPL];
+                rademacher_rows<EPL>(tile + r * (D + 1), s_rb, lane, a.inv_sqrt_d, proj);
+#pragma unroll
+                for (int k = 0; k < EPL; ++k) {
+                    const uint32_t word = __ballot_sync(0xffffffffu, proj[k] >= 0.0f);  // qjl.rs:315
+                    if (lane == 0) reinterpret_cast<uint32_t*>(a.signs)[(v0 + r) * W + k] = word;
+                }
+            }
+        }
+        // write the tile's packed bytes and scales (contiguous in global memory)
+        const int nwords = nv * a.pb / 4;
+        uint32_t* gout = reinterpret_cast<uint32_t*>(a.packed + v0 * a.pb);
+        const uint32_t* sst = reinterpret_cast<const uint32_t*>(stage);
+        for (int i = lane; i < nwords; i += 32) gout[i] = sst[i];
+        if (lane < nv) a.scales[v0 + lane] = f32_to_f16_bits(norm < kMinNorm ? 0.0f : norm);  // select_scale
+        __syncwarp();
+    }
+}
+
+// dequantize_vec (src/quantize.rs:225-239) / dequantize_rotated (:306-316); warp per vector.
+template <int EPL>
+__global__ void whole_dequantize_kernel(const uint8_t* __restrict__ packed, const uint16_t* __restrict__ scales,
+                                        long long n, float* __restrict__ out, Codebook cb, int bits, int pb,
+                                        uint64_t seed, float inv_sqrt_d, int rotated_only) {
+    constexpr int D = 32 * EPL;
+    __shared__ float s_c[16];
+    if (threadIdx.x < 16) s_c[threadIdx.x] = cb.c[threadIdx.x];
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    const long long warp_id = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+    const int nwords = pb >> 2;
+    for (long long i = warp_id; i < n; i += nwarps) {
+        const uint32_t word = lane < nwords ? __ldg(reinterpret_cast<const uint32_t*>(packed + i * pb) + lane) : 0u;
+        const float sc = f16_bits_to_f32(__ldg(scales + i));
+        float v[EPL];
+#pragma unroll
+        for (int k = 0; k < EPL; ++k) v[k] = s_c[code_at(word, lane + 32 * k, bits)];
+        if (!rotated_only) {
+            wht_lanes<EPL>(v, lane);
+#pragma unroll
+            for (int k = 0; k < EPL; ++k) v[k] = (v[k] * inv_sqrt_d) * sign_of(seed, lane + 32 * k);
+        }
+#pragma unroll
+        for (int k = 0; k < EPL; ++k) out[i * D + lane + 32 * k] = v[k] * sc;
+    }
+}
+
+// precompute_query_projections (src/qjl.rs:488-492); one warp per query.
+template <int EPL>
+__global__ void projections_kernel(const float* __restrict__ q, long long nq, const uint32_t* __restrict__ rbits,
+                                   float* __restrict__ rq, float inv_sqrt_d) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    constexpr int D = 32 * EPL, W = EPL;
+    uint32_t* s_rb = reinterpret_cast<uint32_t*>(smem_raw);
+    float* vecs = reinterpret_cast<float*>(s_rb + D * (W + 1));
+    for (int i = threadIdx.x; i < D * W; i += blockDim.x) s_rb[(i / W) * (W + 1) + (i % W)] = rbits[i];
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    float* vec = vecs + warp * D;
+    for (long long i = (long long)blockIdx.x * warps + warp; i < nq; i += (long long)gridDim.x * warps) {
+#pragma unroll
+        for (int k = 0; k < EPL; ++k) vec[lane + 32 * k] = q[i * D + lane + 32 * k];
+        __syncwarp();
+        float proj[EPL];
+        rademacher_rows<EPL>(vec, s_rb, lane, inv_sqrt_d, proj);
+#pragma unroll
+        for (int k = 0; k < EPL; ++k) rq[i * D + lane + 32 * k] = proj[k];
+        __syncwarp();
+    }
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// attention_scores (src/attention.rs:319-353, src/qjl.rs:585-606).  The key is never
+// rotated back: <q, s * sigma .* H(c)/sqrt(d)> = s * <H(sigma .* q)/sqrt(d), c>.
+template <int EPL>
+__global__ void scores_kernel(const float* __restrict__ q, const float* __restrict__ rq,
+                              const uint8_t* __restrict__ packed, const uint16_t* __restrict__ scales,
+                              const uint8_t* __restrict__ signs, const uint16_t* __restrict__ rnorms, long long n,
+                              float* __restrict__ scores, Codebook cb, int bits, int pb, uint64_t seed,
+                              float inv_sqrt_d, float sqrt_d) {
+    constexpr int D = 32 * EPL, W = EPL;
+    __shared__ float s_c[16];
+    if (threadIdx.x < 16) s_c[threadIdx.x] = cb.c[threadIdx.x];
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    float qr[EPL], rqv[EPL];
+#pragma unroll
+    for (int k = 0; k < EPL; ++k) {
+        qr[k] = q[lane + 32 * k] * sign_of(seed, lane + 32 * k);
+        rqv[k] = rq[lane + 32 * k];
+    }
+    wht_lanes<EPL>(qr, lane);
+#pragma unroll
+    for (int k = 0; k < EPL; ++k) qr[k] = qr[k] * inv_sqrt_d;
+    const long long warp_id = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+    const int nwords = pb >> 2;
+    for (long long i = warp_id; i < n; i += nwarps) {
+        const uint32_t word = lane < nwords ? __ldg(reinterpret_cast<const uint32_t*>(packed + i * pb) + lane) : 0u;
+        const uint32_t sw = lane < W ? __ldg(reinterpret_cast<const uint32_t*>(signs + i * (D / 8)) + lane) : 0u;
+        float base = 0.0f, corr = 0.0f;
+#pragma unroll
+        for (int k = 0; k < EPL; ++k) {
+            base = fmaf(qr[k], s_c[code_at(word, lane + 32 * k, bits)], base);
+            const uint32_t w = __shfl_sync(0xffffffffu, sw, k);
+            corr = fmaf(rqv[k], ((w >> lane) & 1u) ? 1.0f : -1.0f, corr);
+        }
+        base = warp_sum(base) * f16_bits_to_f32(__ldg(scales + i));
+        corr = warp_sum(corr);
+        const float cc = (f16_bits_to_f32(__ldg(rnorms + i)) * 1.2533141f) / sqrt_d;  // qjl.rs:263-265
+        if (lane == 0) scores[i] = base + cc * corr;
+    }
+}
+
+constexpr int kWvBlocks = 296;  // two CTAs per SM
+
+// weighted_values (src/attention.rs:371-408), accumulated in the rotated domain:
+// sum_t w_t s_t sigma .* H(c_t)/sqrt(d) = sigma .* H(sum_t w_t s_t c_t)/sqrt(d).
+template <int EPL>
+__global__ void weighted_values_partial_kernel(const float* __restrict__ w, const uint8_t* __restrict__ packed,
+                                               const uint16_t* __restrict__ scales, long long n,
+                                               float* __restrict__ partial, Codebook cb, int bits, int pb) {
+    constexpr int D = 32 * EPL;
+    __shared__ float s_c[16];
+    __shared__ float s_acc[8][D];
+    if (threadIdx.x < 16) s_c[threadIdx.x] = cb.c[threadIdx.x];
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const int nwords = pb >> 2;
+    float acc[EPL];
+#pragma unroll
+    for (int k = 0; k < EPL; ++k) acc[k] = 0.0f;
+    for (long long i = (long long)blockIdx.x * warps + warp; i < n; i += (long long)gridDim.x * warps) {
+        const uint32_t word = lane < nwords ? __ldg(reinterpret_cast<const uint32_t*>(packed + i * pb) + lane) : 0u;
+        const float ws = __ldg(w + i) * f16_bits_to_f32(__ldg(scales + i));
+#pragma unroll
+        for (int k = 0; k < EPL; ++k) acc[k] = fmaf(ws, s_c[code_at(word, lane + 32 * k, bits)], acc[k]);
+    }
+#pragma unroll
+    for (int k = 0; k < EPL; ++k) s_acc[warp][lane + 32 * k] = acc[k];
+    __syncthreads();
+    for (int e = threadIdx.x; e < D; e += blockDim.x) {
+        float s = 0.0f;
+        for (int ww = 0; ww < warps; ++ww) s += s_acc[ww][e];
+        partial[(size_t)blockIdx.x * D + e] = s;
+    }
+}
+
+template <int EPL>
+__global__ void weighted_values_final_kernel(const float* __restrict__ partial, int nparts, float* __restrict__ out,
+                                             uint64_t seed, float inv_sqrt_d) {
+    constexpr int D = 32 * EPL;
+    const int lane = threadIdx.x & 31;
+    float v[EPL];
+#pragma unroll
+    for (int k = 0; k < EPL; ++k) {
+        float s = 0.0f;
+        for (int p = 0; p < nparts; ++p) s += partial[(size_t)p * D + lane + 32 * k];
+        v[k] = s;
+    }
+    wht_lanes<EPL>(v, lane);
+#pragma unroll
+    for (int k = 0; k < EPL; ++k) out[lane + 32 * k] = (v[k] * inv_sqrt_d) * sign_of(seed, lane + 32 * k);
+}
+
+size_t quant_smem(int dim, int pb, int warps, bool qjl) {
+    const int W = dim / 32;
+    size_t per_warp = sizeof(float) * kTile * (dim + 1) + dim + (size_t)kTile * pb;
+    per_warp = (per_warp + 15) / 16 * 16;
+    return (qjl ? sizeof(uint32_t) * dim * (W + 1) : 0) + 32 * sizeof(float) + per_warp * warps;
+}
+
+template <int EPL, bool QJL>
+int launch_quant(const WholeArgs& a, const Codebook& cb, cudaStream_t s) {
+    const int warps = EPL >= 8 ? 2 : 4;
+    const size_t smem = quant_smem(a.dim, a.pb, warps, QJL);
+    cudaError_t e = cudaFuncSetAttribute(whole_quantize_kernel<EPL, QJL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
+    if (e != cudaSuccess) { set_cuda_error(e); return TQB_ERR_CUDA; }
+    const long long tiles = (a.n + kTile - 1) / kTile;
+    long long grid = (tiles + warps - 1) / warps;
+    if (grid > 148 * 8) grid = 148 * 8;
+    whole_quantize_kernel<EPL, QJL><<<(int)grid, warps * 32, smem, s>>>(a, cb);
+    return check_launch(s);
+}
+
+template <bool QJL>
+int dispatch_quant(const WholeArgs& a, const Codebook& cb, cudaStream_t s) {
+    switch (a.dim) {
+        case 32: return launch_quant<1, QJL>(a, cb, s);
+        case 64: return launch_quant<2, QJL>(a, cb, s);
+        case 128: return launch_quant<4, QJL>(a, cb, s);
+        case 256: return launch_quant<8, QJL>(a, cb, s);
+        default: return TQB_ERR_UNSUPPORTED;
+    }
+}
+
+int grid_warps(long long n, int warps_per_block) {
+    long long g = (n + warps_per_block - 1) / warps_per_block;
+    if (g > 148 * 8) g = 148 * 8;
+    if (g < 1) g = 1;
+    return (int)g;
+}
+
+float host_inv_sqrt(int dim) { return 1.0f / sqrtf((float)dim); }  // rotation.rs:36
+
+}  // namespace
+}  // namespace tqb
+
+using namespace tqb;
+
+#define TQB_DISPATCH_EPL(dim, ...)                        \
+    switch (dim) {                                         \
+        case 32: { constexpr int EPL = 1; __VA_ARGS__; } break;  \
+        case 64: { constexpr int EPL = 2; __VA_ARGS__; } break;  \
+        case 128: { constexpr int EPL = 4; __VA_ARGS__; } break; \
+        case 256: { constexpr int EPL = 8; __VA_ARGS__; } break; \
+        default: return TQB_ERR_UNSUPPORTED;               \
+    }
+
+extern "C" {
+
+int tqb_quantize_batch(const tqb_config* cfg, const float* x, int64_t n, uint8_t* packed, uint16_t* scales,
+                       tqb_stream_t stream) {
+    int st = tqb_config_validate(cfg);
+    if (st != TQB_OK) return st;
+    if (n < 0) return TQB_ERR_INVALID_ARGUMENT;
+    if (n == 0) return TQB_OK;
+    if (!x || !packed || !scales) return TQB_ERR_NULL_POINTER;
+    if (((uintptr_t)packed % 4) || ((uintptr_t)x % 4)) return TQB_ERR_MISALIGNED;
+    Codebook cb;
+    if (!whole_codebook(cfg->bits, cfg->dim, cb)) return TQB_ERR_UNSUPPORTED;
+    WholeArgs a{};
+    a.x = x; a.n = n; a.packed = packed; a.scales = scales;
+    a.bits = cfg->bits; a.dim = cfg->dim; a.pb = (int)tqb_packed_bytes(cfg->bits, cfg->dim);
+    a.seed = cfg->rotation_seed; a.inv_sqrt_d = host_inv_sqrt(cfg->dim);
+    return dispatch_quant<false>(a, cb, as_stream(stream));
+}
+
+int tqb_qjl_quantize_batch(const tqb_config* cfg, const uint32_t* rbits, const float* x, int64_t n, uint8_t* packed,
+                           uint16_t* scales, uint8_t* signs, uint16_t* rnorms, tqb_stream_t stream) {
+    if (!cfg) return TQB_ERR_NULL_POINTER;
+    if (cfg->bits < 3 || cfg->bits > 4) return TQB_ERR_UNSUPPORTED_BITS;  // src/qjl.rs:277-279
+    tqb_config polar = *cfg;
+    polar.bits = cfg->bits - 1;
+    int st = tqb_config_validate(&polar);
+    if (st != TQB_OK) return st;
+    if (n < 0) return TQB_ERR_INVALID_ARGUMENT;
+    if (n == 0) return TQB_OK;
+    if (!rbits || !x || !packed || !scales || !signs || !rnorms) return TQB_ERR_NULL_POINTER;
+    if (((uintptr_t)packed % 4) || ((uintptr_t)signs % 4) || ((uintptr_t)x % 4)) return TQB_ERR_MISALIGNED;
+    Codebook cb;
+    if (!whole_codebook(polar.bits, polar.dim, cb)) return TQB_ERR_UNSUPPORTED;
+    WholeArgs a{};
+    a.x = x; a.n = n; a.packed = packed; a.scales = scales; a.signs = signs; a.rnorms = rnorms; a.rbits = rbits;
+    a.bits = polar.bits; a.dim = polar.dim; a.pb = (int)tqb_packed_bytes(polar.bits, polar.dim);
+    a.seed = cfg->rotation_seed; a.inv_sqrt_d = host_inv_sqrt(cfg->dim);
+    return dispatch_quant<true>(a, cb, as_stream(stream));
+}
+
+static int dequant_common(const tqb_config* cfg, const uint8_t* packed, const uint16_t* scales, int64_t n, float* out,
+                          int rotated_only, tqb_stream_t stream) {
+    int st = tqb_config_validate(cfg);
+    if (st != TQB_OK) return st;
+    if (n < 0) return TQB_ERR_INVALID_ARGUMENT;
+    if (n == 0) return TQB_OK;
+    if (!packed || !scales || !out) return TQB_ERR_NULL_POINTER;
+    if ((uintptr_t)packed % 4) return TQB_ERR_MISALIGNED;
+    Codebook cb;
+    if (!whole_codebook(cfg->bits, cfg->dim, cb)) return TQB_ERR_UNSUPPORTED;
+    const int pb = (int)tqb_packed_bytes(cfg->bits, cfg->dim);
+    cudaStream_t s = as_stream(stream);
+    const int grid = grid_warps(n, 8);
+    TQB_DISPATCH_EPL(cfg->dim, (whole_dequantize_kernel<EPL><<<grid, 256, 0, s>>>(
+        packed, scales, n, out, cb, cfg->bits, pb, cfg->rotation_seed, host_inv_sqrt(cfg->dim), rotated_only)));
+    return check_launch(s);
+}
+
+int tqb_dequantize_batch(const tqb_config* cfg, const uint8_t* packed, const uint16_t* scales, int64_t n, float* out,
+                         tqb_stream_t stream) {
+    return dequant_common(cfg, packed, scales, n, out, 0, stream);
+}
+
+int tqb_dequantize_rotated_batch(const tqb_config* cfg, const uint8_t* packed, const uint16_t* scales, int64_t n,
+                                 float* out, tqb_stream_t stream) {
+    return dequant_common(cfg, packed, scales, n, out, 1, stream);
+}
+
+int tqb_qjl_query_projections(int32_t dim, const uint32_t* rbits, const float* q, int64_t nq, float* rq,
+                              tqb_stream_t stream) {
+    if (dim != 32 && dim != 64 && dim != 128 && dim != 256)
+        return (dim > 0 && (dim & (dim - 1)) == 0) ? TQB_ERR_UNSUPPORTED : TQB_ERR_INVALID_DIMENSION;
+    if (nq < 0) return TQB_ERR_INVALID_ARGUMENT;
+    if (nq == 0) return TQB_OK;
+    if (!rbits || !q || !rq) return TQB_ERR_NULL_POINTER;
+    cudaStream_t s = as_stream(stream);
+    const int W = dim / 32, warps = 4;
+    const size_t smem = sizeof(uint32_t) * dim * (W + 1) + sizeof(float) * warps * dim;
+    const int grid = grid_warps(nq, warps);
+    TQB_DISPATCH_EPL(dim, {
+        cudaError_t e = cudaFuncSetAttribute(projections_kernel<EPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) { set_cuda_error(e); return TQB_ERR_CUDA; }
+        projections_kernel<EPL><<<grid, warps * 32, smem, s>>>(q, nq, rbits, rq, host_inv_sqrt(dim));
+    });
+    return check_launch(s);
+}
+
+int tqb_qjl_attention_scores(const tqb_config* cfg, const float* q, const float* rq, const uint8_t* packed,
+                             const uint16_t* scales, const uint8_t* signs, const uint16_t* rnorms, int64_t n,
+                             float* scores, tqb_stream_t stream) {
+    if (!cfg) return TQB_ERR_NULL_POINTER;
+    if (cfg->bits < 3 || cfg->bits > 4) return TQB_ERR_UNSUPPORTED_BITS;
+    tqb_config polar = *cfg;
+    polar.bits = cfg->bits - 1;
+    int st = tqb_config_validate(&polar);
+    if (st != TQB_OK) return st;
+    if (n < 0) return TQB_ERR_INVALID_ARGUMENT;
+    if (n == 0) return TQB_OK;
+    if (!q || !rq || !packed || !scales || !signs || !rnorms || !scores) return TQB_ERR_NULL_POINTER;
+    if (((uintptr_t)packed % 4) || ((uintptr_t)signs % 4)) return TQB_ERR_MISALIGNED;
+    Codebook cb;
+    if (!whole_codebook(polar.bits, polar.dim, cb)) return TQB_ERR_UNSUPPORTED;
+    const int pb = (int)tqb_packed_bytes(polar.bits, polar.dim);
+    cudaStream_t s = as_stream(stream);
+    const int grid = grid_warps(n, 8);
+    TQB_DISPATCH_EPL(cfg->dim, (scores_kernel<EPL><<<grid, 256, 0, s>>>(
+        q, rq, packed, scales, signs, rnorms, n, scores, cb, polar.bits, pb, cfg->rotation_seed,
+        host_inv_sqrt(cfg->dim), sqrtf((float)cfg->dim))));
+    return check_launch(s);
+}
+
+size_t tqb_weighted_values_scratch_bytes(int32_t dim) {
+    return dim > 0 ? sizeof(float) * (size_t)kWvBlocks * dim : 0;
+}
+
+int tqb_weighted_values(const tqb_config* cfg, const float* w, const uint8_t* packed, const uint16_t* scales, int64_t n,
+                        float* out, void* scratch, size_t scratch_bytes, tqb_stream_t stream) {
+    if (!cfg) return TQB_ERR_NULL_POINTER;
+    if (cfg->bits < 3 || cfg->bits > 4) return TQB_ERR_UNSUPPORTED_BITS;
+    tqb_config polar = *cfg;
+    polar.bits = cfg->bits - 1;
+    int st = tqb_config_validate(&polar);
+    if (st != TQB_OK) return st;
+    if (n < 0) return TQB_ERR_INVALID_ARGUMENT;
+    if (!out || !scratch) return TQB_ERR_NULL_POINTER;
+    if (n > 0 && (!w || !packed || !scales)) return TQB_ERR_NULL_POINTER;
+    if (scratch_bytes < tqb_weighted_values_scratch_bytes(cfg->dim)) return TQB_ERR_INVALID_ARGUMENT;
+    if ((uintptr_t)packed % 4) return TQB_ERR_MISALIGNED;
+    Codebook cb;
+    if (!whole_codebook(polar.bits, polar.dim, cb)) return TQB_ERR_UNSUPPORTED;
+    const int pb = (int)tqb_packed_bytes(polar.bits, polar.dim);
+    cudaStream_t s = as_stream(stream);
+    int nparts = (int)((n + 7) / 8);
+    if (nparts > kWvBlocks) nparts = kWvBlocks;
+    if (nparts < 1) nparts = 1;
+    float* partial = reinterpret_cast<float*>(scratch);
+    TQB_DISPATCH_EPL(cfg->dim, {
+        weighted_values_partial_kernel<EPL><<<nparts, 256, 0, s>>>(w, packed, scales, n, partial, cb, polar.bits, pb);
+        weighted_values_final_kernel<EPL><<<1, 32, 0, s>>>(partial, nparts, out, cfg->rotation_seed, host_inv_sqrt(cfg->dim));
+    });
+    return check_launch(s);
+}
+
+}  // extern "C"
