@@ -245,8 +245,13 @@ typedef struct tqb_decode_params {
     int32_t kv_stride;
     int32_t num_partitions;       /* 0 = let the library choose */
     float softmax_scale;
-    int32_t reserved;
+    int32_t flags;                /* TQB_DECODE_* bits */
 } tqb_decode_params;
+
+/* flags: stop after the split-K pass and leave the per-partition (max, sum, out) partials in
+ * `scratch` (layout [num_q_heads, P, head_dim] f32, then [num_q_heads, P] max, then sum);
+ * `out` is not written. */
+#define TQB_DECODE_PARTIALS_ONLY 1
 
 /* Partitions the library would use for this shape, and the scratch it then needs. */
 int32_t tqb_decode_num_partitions(int32_t num_kv_heads, int32_t kv_len);

@@ -93,17 +93,19 @@ def test_reference_ffi_symbols():
         nblocks, bpb = rot.shape[0], 32 * bits // 8
         packed = torch.zeros(nblocks * bpb, dtype=torch.uint8, device="cuda")
         scales = torch.zeros(nblocks, dtype=torch.int16, device="cuda")
-        lib.tq_quant_maxnorm_batch(ptr(dev(rot)), ptr(dev(b)), ptr(packed), ptr(scales), nblocks, 32, bits, len(b), bpb,
+        rot_d, b_d, c_d = dev(rot), dev(b), dev(c)   # keep the device copies alive across the asynchronous launches
+        lib.tq_quant_maxnorm_batch(ptr(rot_d), ptr(b_d), ptr(packed), ptr(scales), nblocks, 32, bits, len(b), bpb,
                                    float(c[-1]), -1.0, None)
         op, os_ = o.block_quantize(bits, hd, 0, -1, x)
         assert np.array_equal(packed.cpu().numpy(), op.reshape(-1)) and np.array_equal(u16(scales), os_.reshape(-1))
         out = torch.zeros(nblocks * 32, device="cuda")
         sign_dev = dev((signs * (np.float32(1) / np.sqrt(np.float32(32))) * np.sqrt(np.float32(32))).astype(np.float32))
-        lib.tq_dequant_batch(ptr(packed), ptr(scales), ptr(dev(c)), ptr(sign_dev), ptr(out), nblocks, 32, bits, bpb, None)
+        lib.tq_dequant_batch(ptr(packed), ptr(scales), ptr(c_d), ptr(sign_dev), ptr(out), nblocks, 32, bits, bpb, None)
         assert np.array_equal(out.cpu().numpy().reshape(n_vec, hd), o.block_dequantize(bits, hd, 0, -1, op, os_))
         codes = rng.integers(0, 1 << bits, size=(n_vec, hd), dtype=np.uint8)
         pk = torch.zeros(n_vec * hd * bits // 8, dtype=torch.uint8, device="cuda")
-        lib.tq_pack_indices(ptr(dev(codes)), ptr(pk), n_vec * 4, 32, bits, bpb, None)
+        codes_d = dev(codes)
+        lib.tq_pack_indices(ptr(codes_d), ptr(pk), n_vec * 4, 32, bits, bpb, None)
         assert np.array_equal(pk.cpu().numpy(), o.pack_indices(bits, codes.reshape(-1)))
         assert lib.tqb_quant_maxnorm_batch(None, None, None, None, 0, 32, bits, len(b), bpb, 1.0, 1.0, None) == 0
 

@@ -511,7 +511,8 @@ def block_dequantize(indices, scales, bits, head_dim, norm_mode=QuantNormMode.Ma
 
 
 def decode_attention(q, k_idx, k_sc, v_idx, v_sc, kv_len, bits, softmax_scale, norm_mode=QuantNormMode.MaxNorm,
-                     outlier_blocks=ALL_BLOCKS, num_partitions=0, out_dtype=None, return_lse=False, qjl=None):
+                     outlier_blocks=ALL_BLOCKS, num_partitions=0, out_dtype=None, return_lse=False, qjl=None,
+                     scratch=None, out=None, partials_only=False):
     """Fused decode attention over packed K/V.
 
     q [Hq, D]; k_idx/v_idx [Hkv, kv_stride, D*bits/8]; k_sc/v_sc [Hkv, kv_stride, D/32].
@@ -521,11 +522,13 @@ def decode_attention(q, k_idx, k_sc, v_idx, v_sc, kv_len, bits, softmax_scale, n
     hkv, stride = k_idx.shape[0], k_idx.shape[1]
     q = q.contiguous()
     out_dtype = out_dtype or (torch.float32 if return_lse else q.dtype)
-    out = torch.empty((hq, d), dtype=out_dtype, device=q.device)
+    if out is None:
+        out = torch.empty((hq, d), dtype=out_dtype, device=q.device)
     lse = torch.empty((hq, 2), dtype=torch.float32, device=q.device) if return_lse else None
     parts = num_partitions or int(lib.tqb_decode_num_partitions(hkv, kv_len))
     sbytes = int(lib.tqb_decode_scratch_bytes(hq, d, parts))
-    scratch = torch.empty((max(sbytes, 16),), dtype=torch.uint8, device=q.device)
+    if scratch is None:
+        scratch = torch.empty((max(sbytes, 16),), dtype=torch.uint8, device=q.device)
     p = TqbDecodeParams()
     p.q, p.k_indices, p.k_scales, p.v_indices, p.v_scales = (q.data_ptr(), k_idx.data_ptr(), k_sc.data_ptr(),
                                                              v_idx.data_ptr(), v_sc.data_ptr())
@@ -537,6 +540,7 @@ def decode_attention(q, k_idx, k_sc, v_idx, v_sc, kv_len, bits, softmax_scale, n
     p.bits, p.head_dim, p.norm_mode, p.outlier_blocks = bits, d, int(norm_mode), outlier_blocks
     p.num_q_heads, p.num_kv_heads, p.kv_len, p.kv_stride = hq, hkv, kv_len, stride
     p.num_partitions, p.softmax_scale = parts, softmax_scale
+    p.flags = 1 if partials_only else 0
     check(lib.tqb_decode_attention(ctypes.byref(p), _stream()))
     return (out, lse) if return_lse else out
 

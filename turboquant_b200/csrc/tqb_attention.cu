@@ -319,12 +319,10 @@ size_t general_smem_bytes(int D) {
 template <typename QT, int NB>
 int launch_general(const DecodeArgs& a, const Codebook& n, const Codebook& o, cudaStream_t s) {
     const size_t smem = general_smem_bytes(a.head_dim);
-    static bool attr_done = false;
-    if (!attr_done) {
+    if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(decode_general_kernel<QT, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)general_smem_bytes(256));
+                                             (int)smem);
         if (e != cudaSuccess) { set_cuda_error(e); return TQB_ERR_CUDA; }
-        attr_done = true;
     }
     dim3 grid(a.hkv, a.num_partitions);
     decode_general_kernel<QT, NB><<<grid, kThreads, smem, s>>>(a, n, o);
@@ -351,12 +349,12 @@ inline float cpu_sign_magnitude() {
 }
 
 int run_decode(DecodeArgs& a, const Codebook& cn, const Codebook& co, int q_dtype, void* out, int out_dtype,
-               float* lse_out, cudaStream_t s) {
+               float* lse_out, cudaStream_t s, bool partials_only = false) {
     int st;
     if (q_dtype == TQB_F32) st = launch_general_nb<float>(a, cn, co, s);
     else if (q_dtype == TQB_F16) st = launch_general_nb<__half>(a, cn, co, s);
     else st = launch_general_nb<__nv_bfloat16>(a, cn, co, s);
-    if (st != TQB_OK) return st;
+    if (st != TQB_OK || partials_only) return st;
     MergeArgs m{};
     m.partial_out = a.partial_out;
     m.partial_max = a.partial_max;
@@ -434,7 +432,8 @@ int tqb_decode_attention(const tqb_decode_params* p, tqb_stream_t stream) {
     a.outlier_mode = ob >= a.nblk ? 1 : (ob == 0 ? 0 : 2);
     a.softmax_scale = p->softmax_scale;
     a.sign_mag = cpu_sign_magnitude();
-    return run_decode(a, cn, co, p->q_dtype, p->out, p->out_dtype, p->lse_out, as_stream(stream));
+    return run_decode(a, cn, co, p->q_dtype, p->out, p->out_dtype, p->lse_out, as_stream(stream),
+                      (p->flags & TQB_DECODE_PARTIALS_ONLY) != 0);
 }
 
 int tqb_lse_combine(const float* partial_out, const float* partial_lse, int32_t num_shards, int32_t num_q_heads,
