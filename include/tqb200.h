@@ -252,6 +252,8 @@ typedef struct tqb_decode_params {
  * `scratch` (layout [num_q_heads, P, head_dim] f32, then [num_q_heads, P] max, then sum);
  * `out` is not written. */
 #define TQB_DECODE_PARTIALS_ONLY 1
+/* flags: always take the general (SIMT, any shape) kernel; used to cross-check the tensor-core kernels. */
+#define TQB_DECODE_FORCE_GENERAL 2
 
 /* Partitions the library would use for this shape, and the scratch it then needs. */
 int32_t tqb_decode_num_partitions(int32_t num_kv_heads, int32_t kv_len);

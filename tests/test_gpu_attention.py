@@ -87,6 +87,25 @@ def test_gqa_groups_and_head_dims(bits, hq, hkv, head_dim):
     assert np.abs(got - want).max() < TOL
 
 
+@pytest.mark.parametrize("bits", [4])
+@pytest.mark.parametrize("g", [1, 2, 4, 8])
+@pytest.mark.parametrize("L", [17, 1000, 4133])
+def test_tensor_core_kernel_against_oracle_and_general_kernel(bits, g, L):
+    rng = np.random.default_rng(g * 100 + L)
+    hkv = 3
+    hq = hkv * g
+    ki, ks, vi, vs = make_cache(rng, hkv, L, L + 5, bits)
+    q = (rng.standard_normal((hq, 128)) / np.sqrt(128)).astype(np.float32)
+    want = o.block_attention(bits, 128, 0, -1, q, ki, ks, vi, vs, L, 0.0884, nthreads=8)
+    fast = gpu_attend(q, ki, ks, vi, vs, L, bits, 0.0884).cpu().numpy()
+    slow = gpu_attend(q, ki, ks, vi, vs, L, bits, 0.0884, force_general=True).cpu().numpy()
+    assert np.abs(fast - want).max() < 2e-5      # exact-integer codes + hi/lo splits: f32-level agreement
+    assert np.abs(slow - want).max() < 2e-5
+    for parts in (1, 2, 7):
+        got = gpu_attend(q, ki, ks, vi, vs, L, bits, 0.0884, num_partitions=parts).cpu().numpy()
+        assert np.abs(got - want).max() < 2e-5
+
+
 def test_sharp_softmax_and_query_dtypes():
     # large logits: one token dominates; also bf16 / f16 queries and outputs
     rng = np.random.default_rng(77)

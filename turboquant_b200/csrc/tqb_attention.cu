@@ -20,6 +20,8 @@
 namespace tqb {
 
 int block_cfg_check(int bits, int head_dim, int norm_mode);
+int launch_decode_mma(const tqb_decode_params* p, int num_partitions, float* partial_out, float* partial_max,
+                      float* partial_sum, float sign_mag, cudaStream_t s);
 
 namespace {
 
@@ -348,6 +350,8 @@ inline float cpu_sign_magnitude() {
     return inv * s;
 }
 
+int run_merge(const DecodeArgs& a, void* out, int out_dtype, float* lse_out, cudaStream_t s);
+
 int run_decode(DecodeArgs& a, const Codebook& cn, const Codebook& co, int q_dtype, void* out, int out_dtype,
                float* lse_out, cudaStream_t s, bool partials_only = false) {
     int st;
@@ -355,6 +359,10 @@ int run_decode(DecodeArgs& a, const Codebook& cn, const Codebook& co, int q_dtyp
     else if (q_dtype == TQB_F16) st = launch_general_nb<__half>(a, cn, co, s);
     else st = launch_general_nb<__nv_bfloat16>(a, cn, co, s);
     if (st != TQB_OK || partials_only) return st;
+    return run_merge(a, out, out_dtype, lse_out, s);
+}
+
+int run_merge(const DecodeArgs& a, void* out, int out_dtype, float* lse_out, cudaStream_t s) {
     MergeArgs m{};
     m.partial_out = a.partial_out;
     m.partial_max = a.partial_max;
@@ -432,8 +440,17 @@ int tqb_decode_attention(const tqb_decode_params* p, tqb_stream_t stream) {
     a.outlier_mode = ob >= a.nblk ? 1 : (ob == 0 ? 0 : 2);
     a.softmax_scale = p->softmax_scale;
     a.sign_mag = cpu_sign_magnitude();
-    return run_decode(a, cn, co, p->q_dtype, p->out, p->out_dtype, p->lse_out, as_stream(stream),
-                      (p->flags & TQB_DECODE_PARTIALS_ONLY) != 0);
+    const bool partials_only = (p->flags & TQB_DECODE_PARTIALS_ONLY) != 0;
+    if (!(p->flags & TQB_DECODE_FORCE_GENERAL)) {
+        // tensor-core kernels for the shapes they cover; everything else takes the general kernel
+        st = launch_decode_mma(p, P, a.partial_out, a.partial_max, a.partial_sum, a.sign_mag, as_stream(stream));
+        if (st == TQB_OK) {
+            if (partials_only) return TQB_OK;
+            return run_merge(a, p->out, p->out_dtype, p->lse_out, as_stream(stream));
+        }
+        if (st != TQB_ERR_UNSUPPORTED) return st;
+    }
+    return run_decode(a, cn, co, p->q_dtype, p->out, p->out_dtype, p->lse_out, as_stream(stream), partials_only);
 }
 
 int tqb_lse_combine(const float* partial_out, const float* partial_lse, int32_t num_shards, int32_t num_q_heads,
