@@ -342,7 +342,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--profile-case", action="store_true",
+                    help="small case for profiler captures: 2 layers, batch 16 (151 MB of packed cache per launch, "
+                         "above the L2 size, 0.4 GB on the device); its numbers are not bench values")
     args = ap.parse_args()
+    if args.profile_case:
+        CFG.update(layers=2, batch=16)
+        args.no_cpu = True
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -104,14 +104,78 @@ __device__ __forceinline__ float wht32_lane(float v, int lane) {
     return v;
 }
 
+// ---- per-warp asynchronous staging -------------------------------------------------------
+// Each warp owns a ring of kStages stages in shared memory; one stage holds the packed bytes of
+// 16 consecutive tokens of one KV head: K indices [16][64 B], V indices [16][64 B], K scales
+// [16][8 B], V scales [16][8 B].  Lanes fill a stage with cp.async (16-byte pieces for the
+// indices, 8-byte pieces for the scales) and track completion with commit/wait groups, so no
+// thread ever spins on a flag.  The 16-byte piece c of token row t is stored at piece
+// c ^ ((t >> 1) & 3): with that XOR both access patterns below touch 32 distinct banks.
+constexpr int kStages = 4;
+constexpr int kStageBytes = 1024 + 1024 + 128 + 128;
+constexpr int kRingBytes = kStages * kStageBytes;
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async8(uint32_t dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+
+// Issues the copies of the 16 tokens starting at `gs` into the stage at shared address `st`.
+__device__ __forceinline__ void stage_fill(const MmaArgs& a, size_t row0, int gs, int last, uint32_t st, int lane) {
+    const uint8_t* kb = reinterpret_cast<const uint8_t*>(a.kw);
+    const uint8_t* vb = reinterpret_cast<const uint8_t*>(a.vw);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int c = lane + 32 * h;            // piece index 0..63
+        const int t = c >> 2, pc = c & 3;
+        const size_t row = row0 + min(gs + t, last);
+        const uint32_t dst = t * 64 + ((pc ^ ((t >> 1) & 3)) << 4);
+        cp_async16(st + dst, kb + row * 64 + pc * 16);
+        cp_async16(st + 1024 + dst, vb + row * 64 + pc * 16);
+    }
+    {
+        const int t = lane & 15;
+        const size_t row = row0 + min(gs + t, last);
+        const uint16_t* src = (lane < 16 ? a.ks : a.vs) + row * 4;
+        cp_async8(st + 2048 + (lane < 16 ? 0 : 128) + t * 8, src);
+    }
+}
+
 // 4-bit MaxNorm ("PQO4") kernel.  Grid (kv heads, partitions), 4 warps; each warp walks its
 // partition in steps of 16 tokens and keeps its own online-softmax state; the four states are
 // merged through shared memory at the end and written as one split-K partial.
-template <typename QT>
+//
+// NSPLIT = true (GQA group <= 4): the MMA columns 0..3 of O^T = V^T P' carry the f16 "hi" part of
+// P' for heads 0..3 and columns 4..7 the "lo" part, so one MMA delivers the split-precision
+// product.  NSPLIT = false (group 5..8): hi and lo take one MMA each.
+// The query is split the same way along the 16 MMA rows of S^T = Q~ K^T: rows 0..7 hold the
+// hi parts of the (up to) 8 heads, rows 8..15 the lo parts.
+template <typename QT, bool NSPLIT>
 __global__ void __launch_bounds__(kThreads, 3) decode_pqo4_mma_kernel(MmaArgs a) {
-    __shared__ float s_o[kWarps][8][kD];   // prologue: rotated queries [8][128] live in s_o[0]
-    __shared__ float s_m[kWarps][8], s_l[kWarps][8], s_z[kWarps][8][4];
+    __shared__ __align__(1024) unsigned char s_raw[kWarps * kRingBytes];
+    // epilogue / prologue views of the same memory (the rings are idle then)
+    float (*s_o)[8][kD] = reinterpret_cast<float (*)[8][kD]>(s_raw);                 // [kWarps][8][128]
+    float (*s_m)[8] = reinterpret_cast<float (*)[8]>(s_raw + kWarps * 8 * kD * 4);   // [kWarps][8]
+    float (*s_l)[8] = s_m + kWarps;
+    float (*s_z)[8][4] = reinterpret_cast<float (*)[8][4]>(s_l + kWarps);
     __shared__ float s_sign[32];
+    static_assert(kWarps * kRingBytes >= kWarps * 8 * kD * 4 + kWarps * 8 * 4 * 2 + kWarps * 8 * 4 * 4, "ring too small");
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int n = lane >> 2, j = lane & 3;     // n: MMA column / row group, j: position in the quad
@@ -136,9 +200,9 @@ __global__ void __launch_bounds__(kThreads, 3) decode_pqo4_mma_kernel(MmaArgs a)
         }
     }
     __syncthreads();
-    // A fragments (rows = heads; only rows 0..7 are populated): for block b and half m the k-slots
-    // (2j, 2j+1 | 2j+8, 2j+9) hold dims 32b + 8j + 2m + (0, 4 | 1, 5), matching nibbles_to_half2.
-    uint32_t ahi[4][2][2], alo[4][2][2];
+    // A fragments: rows 0..7 = hi(q~) of head n, rows 8..15 = lo(q~) of head n.  For block b and
+    // half m the k-slots (2j, 2j+1 | 2j+8, 2j+9) hold dims 32b + 8j + 2m + (0, 4 | 1, 5).
+    uint32_t afr[4][2][4];
     float qbar[4];
     {
         const float* s_q = &s_o[0][0][0] + n * kD;
@@ -147,17 +211,17 @@ __global__ void __launch_bounds__(kThreads, 3) decode_pqo4_mma_kernel(MmaArgs a)
 #pragma unroll
             for (int m = 0; m < 2; ++m) {
                 const int d0 = 32 * b + 8 * j + 2 * m;
-                ahi[b][m][0] = pack_hi(s_q[d0], s_q[d0 + 4]);
-                alo[b][m][0] = pack_lo(s_q[d0], s_q[d0 + 4]);
-                ahi[b][m][1] = pack_hi(s_q[d0 + 1], s_q[d0 + 5]);
-                alo[b][m][1] = pack_lo(s_q[d0 + 1], s_q[d0 + 5]);
+                afr[b][m][0] = pack_hi(s_q[d0], s_q[d0 + 4]);
+                afr[b][m][1] = pack_lo(s_q[d0], s_q[d0 + 4]);
+                afr[b][m][2] = pack_hi(s_q[d0 + 1], s_q[d0 + 5]);
+                afr[b][m][3] = pack_lo(s_q[d0 + 1], s_q[d0 + 5]);
             }
             float s = 0.0f;
             for (int i = 0; i < 32; ++i) s += s_q[32 * b + i];
             qbar[b] = 0.5f * s;   // the +0.5 of (i - 7.5) = (i - 8) + 0.5
         }
     }
-    __syncthreads();   // s_o is reused by the epilogue
+    __syncthreads();   // s_raw now belongs to the rings
 
     float m_run = kNegBig, l_run = 0.0f;
     float z[4] = {0.0f, 0.0f, 0.0f, 0.0f};
@@ -173,52 +237,65 @@ __global__ void __launch_bounds__(kThreads, 3) decode_pqo4_mma_kernel(MmaArgs a)
     const int t_end = min(t_begin + a.part_size, a.kv_len);
     const size_t row0 = (size_t)kvh * a.kv_stride;
     const int last = a.kv_len - 1;
+    const int first = t_begin + warp * kGroup;
+    const int stride = kWarps * kGroup;
+    const int ngroups = first < t_end ? (t_end - first + stride - 1) / stride : 0;
 
-    for (int gs = t_begin + warp * kGroup; gs < t_end; gs += kWarps * kGroup) {
-        // ---- loads: K words (token gs+8o+n, word j of each block), scales of tokens gs+8o+2j+e ----
-        uint32_t kwv[2][4], vwv[2][2][4];
-        uint2 ksc[2][2], vsc[2][2];
+    const uint32_t ring = (uint32_t)__cvta_generic_to_shared(s_raw) + warp * kRingBytes;
+    // per-thread shared-memory offsets inside a stage
+    uint32_t koff[4], voff[4];
 #pragma unroll
-        for (int o8 = 0; o8 < 2; ++o8) {
-            const size_t rk = (row0 + min(gs + 8 * o8 + n, last)) * 16;
+    for (int b = 0; b < 4; ++b) {
+        koff[b] = n * 64 + ((b ^ ((n >> 1) & 3)) << 4) + j * 4;                 // token n (+8o: +512), word j of block b
+        voff[b] = 1024 + (2 * j) * 64 + ((b ^ j) << 4) + (n >> 1) * 4;          // token 2j (+e: +64, +8o: +512), word n/2
+    }
+    const uint32_t scoff = 2048 + (2 * j) * 8;                                   // scales of token 2j (+e: +8, +8o: +64)
+    const uint32_t vsel = (n & 1) ? 0x7632u : 0x5410u;
+
 #pragma unroll
-            for (int b = 0; b < 4; ++b) kwv[o8][b] = __ldg(a.kw + rk + b * 4 + j);
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const size_t rt = row0 + min(gs + 8 * o8 + 2 * j + e, last);
-                ksc[o8][e] = __ldg(reinterpret_cast<const uint2*>(a.ks + rt * 4));
-                vsc[o8][e] = __ldg(reinterpret_cast<const uint2*>(a.vs + rt * 4));
-#pragma unroll
-                for (int b = 0; b < 4; ++b) vwv[o8][e][b] = __ldg(a.vw + rt * 16 + b * 4 + (n >> 1));
-            }
+    for (int i = 0; i < kStages - 1; ++i) {
+        if (i < ngroups) stage_fill(a, row0, first + i * stride, last, ring + i * kStageBytes, lane);
+        cp_async_commit();
+    }
+
+    for (int it = 0; it < ngroups; ++it) {
+        const int gs = first + it * stride;
+        {
+            const int nx = it + kStages - 1;
+            if (nx < ngroups) stage_fill(a, row0, first + nx * stride, last, ring + (nx % kStages) * kStageBytes, lane);
+            cp_async_commit();
         }
+        cp_async_wait<kStages - 1>();
+        __syncwarp();
+        const uint32_t st = ring + (it % kStages) * kStageBytes;
+
         // ---- S^T = Q~ K^T ----
         float s[2][2];
 #pragma unroll
         for (int o8 = 0; o8 < 2; ++o8) {
             s[o8][0] = 0.0f;
             s[o8][1] = 0.0f;
-            const __half2 sc01[2] = {u32_as_h2(ksc[o8][0].x), u32_as_h2(ksc[o8][1].x)};
-            const __half2 sc23[2] = {u32_as_h2(ksc[o8][0].y), u32_as_h2(ksc[o8][1].y)};
+            const uint2 sc0 = lds64(st + scoff + o8 * 64), sc1 = lds64(st + scoff + o8 * 64 + 8);
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
                 uint32_t x[4];
-                nibbles_to_half2(kwv[o8][b], x);
+                nibbles_to_half2(lds32(st + koff[b] + o8 * 512), x);
                 float acc[4] = {qbar[b], qbar[b], 0.0f, 0.0f};
-                mma16816(acc, ahi[b][0][0], 0u, ahi[b][0][1], 0u, x[0], x[1]);
-                mma16816(acc, alo[b][0][0], 0u, alo[b][0][1], 0u, x[0], x[1]);
-                mma16816(acc, ahi[b][1][0], 0u, ahi[b][1][1], 0u, x[2], x[3]);
-                mma16816(acc, alo[b][1][0], 0u, alo[b][1][1], 0u, x[2], x[3]);
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const __half2 pr = (b < 2) ? sc01[e] : sc23[e];
-                    const float sk = fabsf((b & 1) ? __high2float(pr) : __low2float(pr));
-                    s[o8][e] = fmaf(sk, acc[e], s[o8][e]);
-                }
+                mma16816(acc, afr[b][0][0], afr[b][0][1], afr[b][0][2], afr[b][0][3], x[0], x[1]);
+                mma16816(acc, afr[b][1][0], afr[b][1][1], afr[b][1][2], afr[b][1][3], x[2], x[3]);
+                const __half2 p0 = u32_as_h2(b < 2 ? sc0.x : sc0.y), p1 = u32_as_h2(b < 2 ? sc1.x : sc1.y);
+                const float k0 = fabsf((b & 1) ? __high2float(p0) : __low2float(p0));
+                const float k1 = fabsf((b & 1) ? __high2float(p1) : __low2float(p1));
+                s[o8][0] = fmaf(k0, acc[0] + acc[2], s[o8][0]);
+                s[o8][1] = fmaf(k1, acc[1] + acc[3], s[o8][1]);
             }
+        }
+        if (gs + kGroup > a.kv_len) {   // ragged tail: tokens past the end get zero weight
 #pragma unroll
-            for (int e = 0; e < 2; ++e)
-                if (gs + 8 * o8 + 2 * j + e > last) s[o8][e] = kNegBig;
+            for (int o8 = 0; o8 < 2; ++o8)
+#pragma unroll
+                for (int e = 0; e < 2; ++e)
+                    if (gs + 8 * o8 + 2 * j + e > last) s[o8][e] = kNegBig;
         }
         // ---- online softmax for head n (the quad holds its 16 tokens) ----
         float mx = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
@@ -234,8 +311,10 @@ __global__ void __launch_bounds__(kThreads, 3) decode_pqo4_mma_kernel(MmaArgs a)
             for (int e = 0; e < 2; ++e) p[o8][e] = ex2(s[o8][e] - m_new);
         l_run = l_run * resc + ((p[0][0] + p[0][1]) + (p[1][0] + p[1][1]));
         if (__any_sync(0xffffffffu, resc != 1.0f)) {
-            const float r0 = __shfl_sync(0xffffffffu, resc, 8 * j);        // head 2j
-            const float r1 = __shfl_sync(0xffffffffu, resc, 8 * j + 4);    // head 2j+1
+            // column c of O^T belongs to head c (NSPLIT: head c & 3)
+            const int h0 = NSPLIT ? ((2 * j) & 3) : 2 * j, h1 = NSPLIT ? ((2 * j + 1) & 3) : 2 * j + 1;
+            const float r0 = __shfl_sync(0xffffffffu, resc, 4 * h0);
+            const float r1 = __shfl_sync(0xffffffffu, resc, 4 * h1);
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
                 z[b] *= resc;
@@ -245,7 +324,19 @@ __global__ void __launch_bounds__(kThreads, 3) decode_pqo4_mma_kernel(MmaArgs a)
                 }
             }
         }
+        if (NSPLIT) {
+            // lanes of rows 4..7 take over the probabilities of heads 0..3 and will supply the lo parts
+#pragma unroll
+            for (int o8 = 0; o8 < 2; ++o8)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) p[o8][e] = __shfl_sync(0xffffffffu, p[o8][e], lane & 15);
+        }
         // ---- O^T += V^T P' ----
+        uint2 vs[2][2];
+#pragma unroll
+        for (int o8 = 0; o8 < 2; ++o8)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) vs[o8][e] = lds64(st + 128 + scoff + o8 * 64 + e * 8);
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
             float pf[2][2];
@@ -253,24 +344,31 @@ __global__ void __launch_bounds__(kThreads, 3) decode_pqo4_mma_kernel(MmaArgs a)
             for (int o8 = 0; o8 < 2; ++o8)
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
-                    const uint32_t w = (b < 2) ? vsc[o8][e].x : vsc[o8][e].y;
-                    const __half2 pr = u32_as_h2(w);
+                    const __half2 pr = u32_as_h2(b < 2 ? vs[o8][e].x : vs[o8][e].y);
                     pf[o8][e] = p[o8][e] * fabsf((b & 1) ? __high2float(pr) : __low2float(pr));
                 }
             z[b] += (pf[0][0] + pf[0][1]) + (pf[1][0] + pf[1][1]);
             const uint32_t b0h = pack_hi(pf[0][0], pf[0][1]), b1h = pack_hi(pf[1][0], pf[1][1]);
             const uint32_t b0l = pack_lo(pf[0][0], pf[0][1]), b1l = pack_lo(pf[1][0], pf[1][1]);
             // half-word n of block b of the four tokens, paired (token 2j, token 2j+1)
-            const uint32_t sel = (n & 1) ? 0x7632u : 0x5410u;
             uint32_t xab[4], xcd[4];
-            nibbles_to_half2(__byte_perm(vwv[0][0][b], vwv[0][1][b], sel), xab);
-            nibbles_to_half2(__byte_perm(vwv[1][0][b], vwv[1][1][b], sel), xcd);
-            mma16816(o[b][0], xab[0], xab[1], xcd[0], xcd[1], b0h, b1h);
-            mma16816(o[b][0], xab[0], xab[1], xcd[0], xcd[1], b0l, b1l);
-            mma16816(o[b][1], xab[2], xab[3], xcd[2], xcd[3], b0h, b1h);
-            mma16816(o[b][1], xab[2], xab[3], xcd[2], xcd[3], b0l, b1l);
+            nibbles_to_half2(__byte_perm(lds32(st + voff[b]), lds32(st + voff[b] + 64), vsel), xab);
+            nibbles_to_half2(__byte_perm(lds32(st + voff[b] + 512), lds32(st + voff[b] + 576), vsel), xcd);
+            if (NSPLIT) {
+                const uint32_t b0 = n < 4 ? b0h : b0l, b1 = n < 4 ? b1h : b1l;
+                mma16816(o[b][0], xab[0], xab[1], xcd[0], xcd[1], b0, b1);
+                mma16816(o[b][1], xab[2], xab[3], xcd[2], xcd[3], b0, b1);
+            } else {
+                mma16816(o[b][0], xab[0], xab[1], xcd[0], xcd[1], b0h, b1h);
+                mma16816(o[b][0], xab[0], xab[1], xcd[0], xcd[1], b0l, b1l);
+                mma16816(o[b][1], xab[2], xab[3], xcd[2], xcd[3], b0h, b1h);
+                mma16816(o[b][1], xab[2], xab[3], xcd[2], xcd[3], b0l, b1l);
+            }
         }
+        __syncwarp();   // every lane is done with this stage before it is refilled
     }
+    cp_async_wait<0>();
+    __syncthreads();    // all rings idle: the memory is reused for the merge
 
     // ---- merge the four warps (scores are in log2 units; partials are stored in natural units) ----
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
@@ -280,7 +378,7 @@ __global__ void __launch_bounds__(kThreads, 3) decode_pqo4_mma_kernel(MmaArgs a)
         z[b] += __shfl_xor_sync(0xffffffffu, z[b], 1);
         z[b] += __shfl_xor_sync(0xffffffffu, z[b], 2);
     }
-    if (j == 0) {
+    if (j == 0 && (!NSPLIT || n < 4)) {
         s_m[warp][n] = m_run;
         s_l[warp][n] = l_run;
 #pragma unroll
@@ -308,7 +406,9 @@ __global__ void __launch_bounds__(kThreads, 3) decode_pqo4_mma_kernel(MmaArgs a)
             for (int w = 0; w < kWarps; ++w) {
                 const float e = ex2(s_m[w][hh] - M);
                 L = fmaf(s_l[w][hh], e, L);
-                O = fmaf(s_o[w][hh][d] + 0.5f * s_z[w][hh][b], e, O);
+                float ov = s_o[w][hh][d];
+                if (NSPLIT) ov += s_o[w][hh + 4][d];
+                O = fmaf(ov + 0.5f * s_z[w][hh][b], e, O);
             }
             const size_t pi = (size_t)(kvh * g + hh) * a.num_partitions + part;
             a.partial_out[pi * kD + d] = O * a.v_const;
@@ -332,6 +432,7 @@ int launch_decode_mma(const tqb_decode_params* p, int num_partitions, float* par
     if (p->head_dim != kD || g > 8 || p->qjl_enabled) return TQB_ERR_UNSUPPORTED;
     if (!(p->bits == 4 && p->norm_mode == TQB_MAXNORM && all_outlier)) return TQB_ERR_UNSUPPORTED;
     if (((uintptr_t)p->k_scales % 8) || ((uintptr_t)p->v_scales % 8)) return TQB_ERR_UNSUPPORTED;
+    if (((uintptr_t)p->k_indices % 16) || ((uintptr_t)p->v_indices % 16)) return TQB_ERR_UNSUPPORTED;
     if (p->kv_len <= 0) return TQB_ERR_UNSUPPORTED;
     MmaArgs a{};
     a.q = p->q;
@@ -353,9 +454,15 @@ int launch_decode_mma(const tqb_decode_params* p, int num_partitions, float* par
     a.v_const = grid_step;
     a.sign_mag = sign_mag;
     dim3 grid(p->num_kv_heads, num_partitions);
-    if (p->q_dtype == TQB_F32) decode_pqo4_mma_kernel<float><<<grid, kThreads, 0, s>>>(a);
-    else if (p->q_dtype == TQB_F16) decode_pqo4_mma_kernel<__half><<<grid, kThreads, 0, s>>>(a);
-    else decode_pqo4_mma_kernel<__nv_bfloat16><<<grid, kThreads, 0, s>>>(a);
+#define TQB_LAUNCH_PQO4(QT)                                                              \
+    do {                                                                                 \
+        if (g <= 4) decode_pqo4_mma_kernel<QT, true><<<grid, kThreads, 0, s>>>(a);       \
+        else decode_pqo4_mma_kernel<QT, false><<<grid, kThreads, 0, s>>>(a);             \
+    } while (0)
+    if (p->q_dtype == TQB_F32) TQB_LAUNCH_PQO4(float);
+    else if (p->q_dtype == TQB_F16) TQB_LAUNCH_PQO4(__half);
+    else TQB_LAUNCH_PQO4(__nv_bfloat16);
+#undef TQB_LAUNCH_PQO4
     return check_launch(s);
 }
 
