@@ -389,12 +389,24 @@ extern "C" {
 
 int32_t tqb_decode_num_partitions(int32_t num_kv_heads, int32_t kv_len) {
     if (num_kv_heads <= 0 || kv_len <= 0) return 1;
-    const int target_ctas = 148 * 8;
-    int p = (target_ctas + num_kv_heads - 1) / num_kv_heads;
-    const int max_p = (kv_len + 63) / 64;  // at least 64 tokens per partition
+    // Measured on B200 (512 KV heads x 8192 tokens): a CTA costs a few microseconds of fixed work
+    // (query rotation, pipeline fill, merge), so partitions of 2048..4096 tokens are best once the
+    // grid covers the 148 x 3 resident CTAs; shorter sequences are split further to fill the GPU,
+    // down to 64 tokens per partition.
+    const long long resident = 148 * 3;
+    const int max_p = (kv_len + 63) / 64;
+    long long p = (kv_len + 2047) / 2048;
+    if ((long long)num_kv_heads * p < resident) p = (resident + num_kv_heads - 1) / num_kv_heads;
+    // a grid just past a whole number of waves leaves the last wave nearly empty: trim it
+    const long long ctas = (long long)num_kv_heads * p;
+    const long long waves = ctas / resident;
+    if (waves >= 1 && ctas - waves * resident < resident * 35 / 100) {
+        const long long trimmed = waves * resident / num_kv_heads;
+        if (trimmed >= 1 && (kv_len + trimmed - 1) / trimmed <= 3072) p = trimmed;
+    }
     if (p > max_p) p = max_p;
     if (p < 1) p = 1;
-    return p;
+    return (int32_t)p;
 }
 
 size_t tqb_decode_scratch_bytes(int32_t num_q_heads, int32_t head_dim, int32_t num_partitions) {

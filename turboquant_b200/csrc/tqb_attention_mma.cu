@@ -136,24 +136,51 @@ __device__ __forceinline__ uint2 lds64(uint32_t addr) {
     return v;
 }
 
-// Issues the copies of the 16 tokens starting at `gs` into the stage at shared address `st`.
-__device__ __forceinline__ void stage_fill(const MmaArgs& a, size_t row0, int gs, int last, uint32_t st, int lane) {
+// Per-lane copy plan of one stage: two 16-byte index pieces (rows t0, t0 + 8) of K and of V,
+// and one 8-byte scale row (K for lanes 0..15, V for lanes 16..31).
+struct FillPlan {
+    const uint8_t* k;     // K piece of row t0 of group 0
+    const uint8_t* v;
+    const uint16_t* sc;
+    uint32_t dst0, dst1, dsts;
+    int t0, ts;
+};
+
+__device__ __forceinline__ FillPlan make_plan(const MmaArgs& a, size_t row0, int first, int lane) {
+    FillPlan f;
+    f.t0 = lane >> 2;                // pieces lane and lane + 32 belong to rows t0 and t0 + 8
+    const int pc = lane & 3;
     const uint8_t* kb = reinterpret_cast<const uint8_t*>(a.kw);
     const uint8_t* vb = reinterpret_cast<const uint8_t*>(a.vw);
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        const int c = lane + 32 * h;            // piece index 0..63
-        const int t = c >> 2, pc = c & 3;
-        const size_t row = row0 + min(gs + t, last);
-        const uint32_t dst = t * 64 + ((pc ^ ((t >> 1) & 3)) << 4);
-        cp_async16(st + dst, kb + row * 64 + pc * 16);
-        cp_async16(st + 1024 + dst, vb + row * 64 + pc * 16);
-    }
-    {
-        const int t = lane & 15;
-        const size_t row = row0 + min(gs + t, last);
-        const uint16_t* src = (lane < 16 ? a.ks : a.vs) + row * 4;
-        cp_async8(st + 2048 + (lane < 16 ? 0 : 128) + t * 8, src);
+    f.k = kb + (row0 + first + f.t0) * 64 + pc * 16;
+    f.v = vb + (row0 + first + f.t0) * 64 + pc * 16;
+    f.dst0 = f.t0 * 64 + ((pc ^ ((f.t0 >> 1) & 3)) << 4);
+    f.dst1 = f.dst0 + 512;           // row t0 + 8 has the same (t >> 1) & 3
+    f.ts = lane & 15;
+    f.sc = (lane < 16 ? a.ks : a.vs) + (row0 + first + f.ts) * 4;
+    f.dsts = 2048 + (lane < 16 ? 0 : 128) + f.ts * 8;
+    return f;
+}
+
+// Issues the copies of the 16 tokens starting at `gs` = first + byte_off / 64 into the stage at
+// shared address `st`.  Rows past the last valid token re-read the last token (they are masked
+// later), which only happens in the final group of a sequence.
+__device__ __forceinline__ void stage_fill(const FillPlan& f, size_t byte_off, int gs, int last, uint32_t st) {
+    if (gs + 16 <= last + 1) {
+        cp_async16(st + f.dst0, f.k + byte_off);
+        cp_async16(st + f.dst1, f.k + byte_off + 512);
+        cp_async16(st + 1024 + f.dst0, f.v + byte_off);
+        cp_async16(st + 1024 + f.dst1, f.v + byte_off + 512);
+        cp_async8(st + f.dsts, f.sc + (byte_off >> 4));
+    } else {
+        const long long b0 = (long long)(min(gs + f.t0, last) - (gs + f.t0)) * 64;
+        const long long b1 = (long long)(min(gs + f.t0 + 8, last) - (gs + f.t0 + 8)) * 64;
+        const long long bs = (long long)(min(gs + f.ts, last) - (gs + f.ts)) * 4;
+        cp_async16(st + f.dst0, f.k + byte_off + b0);
+        cp_async16(st + f.dst1, f.k + byte_off + 512 + b1);
+        cp_async16(st + 1024 + f.dst0, f.v + byte_off + b0);
+        cp_async16(st + 1024 + f.dst1, f.v + byte_off + 512 + b1);
+        cp_async8(st + f.dsts, f.sc + (byte_off >> 4) + bs);
     }
 }
 
@@ -169,7 +196,8 @@ __device__ __forceinline__ void stage_fill(const MmaArgs& a, size_t row0, int gs
 template <typename QT, bool NSPLIT>
 __global__ void __launch_bounds__(kThreads, 3) decode_pqo4_mma_kernel(MmaArgs a) {
     __shared__ __align__(1024) unsigned char s_raw[kWarps * kRingBytes];
-    // epilogue / prologue views of the same memory (the rings are idle then)
+    __shared__ float s_q[8 * kD];   // rotated queries (prologue only)
+    // epilogue view of the ring memory (the rings are idle then)
     float (*s_o)[8][kD] = reinterpret_cast<float (*)[8][kD]>(s_raw);                 // [kWarps][8][128]
     float (*s_m)[8] = reinterpret_cast<float (*)[8]>(s_raw + kWarps * 8 * kD * 4);   // [kWarps][8]
     float (*s_l)[8] = s_m + kWarps;
@@ -182,47 +210,7 @@ __global__ void __launch_bounds__(kThreads, 3) decode_pqo4_mma_kernel(MmaArgs a)
     const int kvh = blockIdx.x, part = blockIdx.y;
     const int g = a.g;
 
-    if (tid < 32) {
-        const uint32_t neg = 0xB1A6D4B2u;  // src/cache/precomputed/rotation.rs:16-20
-        s_sign[tid] = a.dev_signs ? a.dev_signs[tid] : (((neg >> tid) & 1u) ? -a.sign_mag : a.sign_mag);
-    }
-    __syncthreads();
-    // ---- rotate the g queries of this KV head once: q~ = sigma .* H32(q_b) / sqrt(32), constants folded ----
-    {
-        float* s_q = &s_o[0][0][0];
-        const float inv_sqrt = 1.0f / sqrtf(32.0f);
-        for (int u = warp; u < 8 * 4; u += kWarps) {
-            const int hh = u >> 2, b = u & 3;
-            float v = 0.0f;
-            if (hh < g) v = to_f32<QT>(reinterpret_cast<const QT*>(a.q)[(size_t)(kvh * g + hh) * kD + b * 32 + lane]);
-            v = wht32_lane(v, lane);
-            s_q[hh * kD + b * 32 + lane] = ((v * inv_sqrt) * s_sign[lane]) * a.qk_const;
-        }
-    }
-    __syncthreads();
-    // A fragments: rows 0..7 = hi(q~) of head n, rows 8..15 = lo(q~) of head n.  For block b and
-    // half m the k-slots (2j, 2j+1 | 2j+8, 2j+9) hold dims 32b + 8j + 2m + (0, 4 | 1, 5).
-    uint32_t afr[4][2][4];
-    float qbar[4];
-    {
-        const float* s_q = &s_o[0][0][0] + n * kD;
-#pragma unroll
-        for (int b = 0; b < 4; ++b) {
-#pragma unroll
-            for (int m = 0; m < 2; ++m) {
-                const int d0 = 32 * b + 8 * j + 2 * m;
-                afr[b][m][0] = pack_hi(s_q[d0], s_q[d0 + 4]);
-                afr[b][m][1] = pack_lo(s_q[d0], s_q[d0 + 4]);
-                afr[b][m][2] = pack_hi(s_q[d0 + 1], s_q[d0 + 5]);
-                afr[b][m][3] = pack_lo(s_q[d0 + 1], s_q[d0 + 5]);
-            }
-            float s = 0.0f;
-            for (int i = 0; i < 32; ++i) s += s_q[32 * b + i];
-            qbar[b] = 0.5f * s;   // the +0.5 of (i - 7.5) = (i - 8) + 0.5
-        }
-    }
-    __syncthreads();   // s_raw now belongs to the rings
-
+    // ---- start streaming the first stages before anything else: the copies do not depend on q ----
     float m_run = kNegBig, l_run = 0.0f;
     float z[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     float o[4][2][4];
@@ -252,22 +240,68 @@ __global__ void __launch_bounds__(kThreads, 3) decode_pqo4_mma_kernel(MmaArgs a)
     const uint32_t scoff = 2048 + (2 * j) * 8;                                   // scales of token 2j (+e: +8, +8o: +64)
     const uint32_t vsel = (n & 1) ? 0x7632u : 0x5410u;
 
+    const FillPlan plan = make_plan(a, row0, first, lane);
+    const size_t group_bytes = (size_t)stride * 64;   // K/V index bytes between consecutive groups of this warp
 #pragma unroll
     for (int i = 0; i < kStages - 1; ++i) {
-        if (i < ngroups) stage_fill(a, row0, first + i * stride, last, ring + i * kStageBytes, lane);
+        if (i < ngroups) stage_fill(plan, i * group_bytes, first + i * stride, last, ring + i * kStageBytes);
         cp_async_commit();
+    }
+    uint32_t st = ring;                                        // stage being consumed
+    uint32_t st_fill = ring + (kStages - 1) * kStageBytes;     // stage being refilled
+    size_t fill_off = (kStages - 1) * group_bytes;
+
+
+    if (tid < 32) {
+        const uint32_t neg = 0xB1A6D4B2u;  // src/cache/precomputed/rotation.rs:16-20
+        s_sign[tid] = a.dev_signs ? a.dev_signs[tid] : (((neg >> tid) & 1u) ? -a.sign_mag : a.sign_mag);
+    }
+    __syncthreads();
+    // ---- rotate the g queries of this KV head once: q~ = sigma .* H32(q_b) / sqrt(32), constants folded ----
+    {
+        const float inv_sqrt = 1.0f / sqrtf(32.0f);
+        for (int u = warp; u < 8 * 4; u += kWarps) {
+            const int hh = u >> 2, b = u & 3;
+            float v = 0.0f;
+            if (hh < g) v = to_f32<QT>(reinterpret_cast<const QT*>(a.q)[(size_t)(kvh * g + hh) * kD + b * 32 + lane]);
+            v = wht32_lane(v, lane);
+            s_q[hh * kD + b * 32 + lane] = ((v * inv_sqrt) * s_sign[lane]) * a.qk_const;
+        }
+    }
+    __syncthreads();
+    // A fragments: rows 0..7 = hi(q~) of head n, rows 8..15 = lo(q~) of head n.  For block b and
+    // half m the k-slots (2j, 2j+1 | 2j+8, 2j+9) hold dims 32b + 8j + 2m + (0, 4 | 1, 5).
+    uint32_t afr[4][2][4];
+    float qbar[4];
+    {
+        const float* sq = s_q + n * kD;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            float s = 0.0f;
+#pragma unroll
+            for (int m = 0; m < 2; ++m) {
+                const int d0 = 32 * b + 8 * j + 2 * m;
+                const float q0 = sq[d0], q4 = sq[d0 + 4], q1 = sq[d0 + 1], q5 = sq[d0 + 5];
+                afr[b][m][0] = pack_hi(q0, q4);
+                afr[b][m][1] = pack_lo(q0, q4);
+                afr[b][m][2] = pack_hi(q1, q5);
+                afr[b][m][3] = pack_lo(q1, q5);
+                s += (q0 + q4) + (q1 + q5);
+            }
+            s += __shfl_xor_sync(0xffffffffu, s, 1);
+            s += __shfl_xor_sync(0xffffffffu, s, 2);
+            qbar[b] = 0.5f * s;   // the +0.5 of (i - 7.5) = (i - 8) + 0.5, summed over the block
+        }
     }
 
     for (int it = 0; it < ngroups; ++it) {
         const int gs = first + it * stride;
-        {
-            const int nx = it + kStages - 1;
-            if (nx < ngroups) stage_fill(a, row0, first + nx * stride, last, ring + (nx % kStages) * kStageBytes, lane);
-            cp_async_commit();
-        }
+        if (it + kStages - 1 < ngroups) stage_fill(plan, fill_off, gs + (kStages - 1) * stride, last, st_fill);
+        cp_async_commit();
+        fill_off += group_bytes;
+        st_fill = (st_fill + kStageBytes == ring + kRingBytes) ? ring : st_fill + kStageBytes;
         cp_async_wait<kStages - 1>();
         __syncwarp();
-        const uint32_t st = ring + (it % kStages) * kStageBytes;
 
         // ---- S^T = Q~ K^T ----
         float s[2][2];
@@ -366,6 +400,7 @@ __global__ void __launch_bounds__(kThreads, 3) decode_pqo4_mma_kernel(MmaArgs a)
             }
         }
         __syncwarp();   // every lane is done with this stage before it is refilled
+        st = (st + kStageBytes == ring + kRingBytes) ? ring : st + kStageBytes;
     }
     cp_async_wait<0>();
     __syncthreads();    // all rings idle: the memory is reused for the merge
