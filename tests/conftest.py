@@ -8,8 +8,22 @@ sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 
+def _build_library_if_stale():
+    """Build the CUDA library when the toolchain is present and the .so is stale.  The build script is
+    loaded by path because importing the package needs the library."""
+    import importlib.util
+    import shutil
+    if not (shutil.which("nvcc") or os.path.exists("/usr/local/cuda/bin/nvcc")):
+        return
+    spec = importlib.util.spec_from_file_location("tqb200_build", os.path.join(ROOT, "turboquant_b200", "build.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    mod.build()
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
+    _build_library_if_stale()
 
 
 def pytest_collection_modifyitems(config, items):
@@ -20,13 +34,3 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
-
-
-@pytest.fixture(scope="session", autouse=True)
-def _built_library():
-    """Build the CUDA library when the toolchain is present and the .so is stale."""
-    import shutil
-    if shutil.which("nvcc") or os.path.exists("/usr/local/cuda/bin/nvcc"):
-        from turboquant_b200 import build as _build  # noqa: F401  (module, not the package import)
-        _build.build()
-    yield

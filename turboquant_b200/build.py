@@ -1,6 +1,6 @@
 """Builds libtqb200.so (hand-written CUDA for sm_100a) in-tree with nvcc.
 
-`python -m turboquant_b200.build` compiles every .cu file under csrc/ into one shared
+`python turboquant_b200/build.py` compiles every .cu file under csrc/ into one shared
 library next to this file.  nvcc cross-compiles without a GPU present.
 """
 import os
