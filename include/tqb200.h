@@ -260,6 +260,23 @@ int32_t tqb_decode_num_partitions(int32_t num_kv_heads, int32_t kv_len);
 size_t tqb_decode_scratch_bytes(int32_t num_q_heads, int32_t head_dim, int32_t num_partitions);
 int tqb_decode_attention(const tqb_decode_params *p, tqb_stream_t stream);
 
+/* tqb_decode_attention for callers that cannot allocate device memory.  No counterpart in the
+ * reference (there the caller always allocates the partial buffers, src/cache/cuda/attention.rs:65-77).
+ * Meant for hosts that have given all free device memory to their own pool at start-up, or that must
+ * not take the device-wide synchronisation of cudaMalloc / cudaFree in their serving loop: the split-K
+ * partials go into a fixed 8 MiB array inside the library image (held by every GPU that loads the
+ * library, until exit), and the call performs no allocation of any kind.
+ *   - p->scratch and p->scratch_bytes are ignored; inputs and outputs are still the caller's.
+ *   - Shapes whose partials need more than tqb_decode_static_scratch_capacity() bytes
+ *     (tqb_decode_scratch_bytes(num_q_heads, head_dim, partitions)) are refused with TQB_ERR_TOO_LARGE.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress with
+ *     that device current); make that first call before starting any stream capture.
+ *   - All calls on a device share the one array and it keeps the previous call's contents; the kernels
+ *     overwrite every slot they later read, so nothing needs clearing, but two calls that overlap on
+ *     the GPU (different streams, no ordering) race on it.  Order them on one stream or with events. */
+size_t tqb_decode_static_scratch_capacity(void);
+int tqb_decode_attention_static(const tqb_decode_params *p, tqb_stream_t stream);
+
 /* Log-sum-exp merge of `num_shards` shard-local results (the algebra of
  * tq_fused_attention_reduce, tq_attention_kernel.cu:299-332, one level up):
  *   partial_out [num_shards, num_q_heads, head_dim] f32 un-normalised,

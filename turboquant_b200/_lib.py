@@ -85,6 +85,8 @@ def _declare(lib):
         "tqb_decode_num_partitions": (I, [I, I]),
         "tqb_decode_scratch_bytes": (S, [I, I, I]),
         "tqb_decode_attention": (c_int, [P, P]),
+        "tqb_decode_attention_static": (c_int, [P, P]),
+        "tqb_decode_static_scratch_capacity": (S, []),
         "tqb_lse_combine": (c_int, [P, P, I, I, I, P, I, P]),
         "tqb_pqo_cache_create": (c_int, [P, P]),
         "tqb_pqo_cache_destroy": (None, [P]),
@@ -120,7 +122,7 @@ def _declare(lib):
 def load():
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m turboquant_b200.build` "
+            f"{LIB_PATH} is missing: build it with `python turboquant_b200/build.py` "
             "(nvcc, sm_100a). There is no CPU fallback.")
     lib = ctypes.CDLL(LIB_PATH)
     lib._signatures = _declare(lib)

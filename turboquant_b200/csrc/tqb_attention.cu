@@ -15,6 +15,8 @@
 // block-wide barrier inside the token loop.
 #include <float.h>
 
+#include <mutex>
+
 #include "tqb_common.cuh"
 
 namespace tqb {
@@ -529,6 +531,69 @@ void tq_fused_attention(const float* q, const uint8_t* k_indices, const uint16_t
                               partial_max, partial_sum, qjl_signs, qjl_residual_norms, rq, qjl_enabled,
                               num_attention_heads, num_kv_heads, head_dim, kv_len, kv_stride, packed_dim, num_qblocks,
                               bits, softmax_scale, num_partitions, stream);
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Decode attention with library-resident scratch (no allocation by anybody).
+//
+// The split-K partials of decode attention normally live in a buffer the caller allocates.  Some
+// callers cannot do that: an inference engine that has handed every free byte of device memory to
+// its own pool at start-up (a later cudaMalloc fails), or a serving loop that must not take the
+// device-wide synchronisation that cudaMalloc / cudaFree imply.  For them the partials go into the
+// fixed array below, which every GPU that loads this library holds from load until exit.
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kStaticScratchBytes = 8u << 20;   // 8 MiB: e.g. 2048 query heads x 8 partitions at head_dim 128
+static __device__ __align__(256) unsigned char g_decode_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_scratch_mutex;
+void* g_scratch_addr[kMaxDevices] = {};   // device address of g_decode_scratch, per device
+
+// The array's name is only a host-side handle; the address a kernel can use is obtained once per
+// device (with that device current) through cudaGetSymbolAddress.
+int static_scratch_address(void** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) { tqb::set_cuda_error(e); return TQB_ERR_CUDA; }
+    if (dev < 0 || dev >= kMaxDevices) return TQB_ERR_UNSUPPORTED;
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    if (g_scratch_addr[dev] == nullptr) {
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_decode_scratch);
+        if (e != cudaSuccess || ptr == nullptr) { tqb::set_cuda_error(e); return TQB_ERR_CUDA; }
+        g_scratch_addr[dev] = ptr;
+    }
+    *out = g_scratch_addr[dev];
+    return TQB_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t tqb_decode_static_scratch_capacity(void) { return kStaticScratchBytes; }
+
+int tqb_decode_attention_static(const tqb_decode_params* p, tqb_stream_t stream) {
+    if (!p) return TQB_ERR_NULL_POINTER;
+    if (p->num_q_heads <= 0 || p->num_kv_heads <= 0 || p->head_dim <= 0) return TQB_ERR_INVALID_ARGUMENT;
+    const int P = p->num_partitions > 0 ? p->num_partitions : tqb_decode_num_partitions(p->num_kv_heads, p->kv_len);
+    const size_t need = tqb_decode_scratch_bytes(p->num_q_heads, p->head_dim, P);
+    if (need == 0 || need > kStaticScratchBytes) return TQB_ERR_TOO_LARGE;   // refuse, never spill past the array
+    void* scratch = nullptr;
+    int st = static_scratch_address(&scratch);
+    if (st != TQB_OK) return st;
+    tqb_decode_params q = *p;
+    q.scratch = scratch;
+    q.scratch_bytes = kStaticScratchBytes;
+    q.num_partitions = P;
+    // Every (head, partition) slot that the merge reads is written by the split-K pass of the same
+    // call, so nothing in the array has to start at zero and stale contents of an earlier call are
+    // never read.
+    return tqb_decode_attention(&q, stream);
 }
 
 }  // extern "C"
