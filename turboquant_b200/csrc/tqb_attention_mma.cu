@@ -9,20 +9,28 @@
 // unpacked codes straight from registers.
 //
 // Layout of one warp step (16 tokens t0..t0+15, lane = 4*n + j):
-//   S^T = Q~ K^T :  M = query heads (rows 0..7 used), N = 8 tokens, K = 16 dims of ONE 32-block.
-//       Lane (n, j) supplies, for token t0+8o+n and block b, the eight codes of word j of the
-//       block; two MMAs per (octet o, block b).  Because each MMA stays inside one block, the
-//       per-block scale |s| is applied to the f32 accumulator (2 FMAs), not to the elements.
-//   O^T = V^T P  :  M = 16 dims of ONE block, N = 8 heads, K = 16 tokens.  The accumulator
+//   S^T = Q~ K^T :  M = query heads (rows 0..7: f16 hi part of q~, rows 8..15: its lo part),
+//       N = 8 tokens, K = 16 dims of ONE 32-block.  Lane (n, j) supplies, for token t0+8o+n and
+//       block b, the eight codes j*8..j*8+7 of the block; two MMAs per (octet o, block b).
+//       Because each MMA stays inside one block, the per-block scale |s| is applied to the f32
+//       accumulator (2 FMAs), not to the elements.
+//   O^T = V^T P' :  M = 16 dims of ONE block, N = 8 heads, K = 16 tokens.  The accumulator
 //       fragment of S^T (head n, tokens 2j, 2j+1) is exactly the B fragment of this MMA, so the
 //       probabilities never leave registers; the V scale is folded into them (P' = p |s_v|).
 //
-// Exactness (4-bit MaxNorm grid, codebooks.rs:63-73): centroid i = (2R/15)(i - 7.5).  Codes are
-// converted to the exact f16 integers i - 8 (magic-number trick: (w & 0x000f000f) | 0x64006400
-// is the half2 (1024 + i, 1024 + i')), the 0.5 offset is carried separately in f32, and both
-// the rotated query and P' are split into f16 hi + lo parts, so every product entering the
-// f32 accumulators is exact: the result matches an f32 evaluation to rounding noise.
+// Code -> f16:
+//   4-bit MaxNorm grid (codebooks.rs:63-73): centroid i = (2R/15)(i - 7.5).  Codes become the exact
+//   f16 integers i - 8 by the magic-number trick ((w & 0x000f000f) | 0x64006400 is the half2
+//   (1024 + i, 1024 + i')); the 0.5 offset is carried separately in f32.
+//   3-bit (any codebook of 8 entries, or 4 entries stored at 3-bit width): a 64-entry half2 table
+//   indexed by two codes, replicated once per bank (entry e of lane l at word 32*e + l) so that
+//   every lookup is conflict-free.  The table holds centroid / kappa, where the f32 factor kappa
+//   is chosen so that all table values are (almost) exactly representable in f16.
+// Both the rotated query and P' are split into f16 hi + lo parts, so every product entering the
+// f32 accumulators is exact up to the (tiny) table error of the 3-bit path.
 #include <float.h>
+
+#include <mutex>
 
 #include "tqb_common.cuh"
 
@@ -34,21 +42,22 @@ constexpr int kThreads = kWarps * 32;
 constexpr int kD = 128;
 constexpr int kGroup = 16;             // tokens per warp step
 constexpr float kNegBig = -1.0e30f;    // finite stand-in for -inf (keeps exp2 arguments NaN-free)
+constexpr int kStages = 4;
 
 struct MmaArgs {
     const void* q;
-    const uint32_t* kw;   // K indices as words, [hkv, kv_stride, 16]
+    const uint8_t* kb;    // K indices, [hkv, kv_stride, 16*BITS]
     const uint16_t* ks;   // [hkv, kv_stride, 4]
-    const uint32_t* vw;
+    const uint8_t* vb;
     const uint16_t* vs;
     float* partial_out;
     float* partial_max;
     float* partial_sum;
-    const float* dev_signs;
     int hq, hkv, g, kv_len, kv_stride, num_partitions, part_size;
-    float qk_const;   // softmax_scale * log2(e) * (2R/15)
-    float v_const;    // 2R/15
+    float qk_const;   // softmax_scale * log2(e) * (grid step | kappa)
+    float v_const;    // grid step | kappa
     float sign_mag;
+    float lut[8];     // 3-bit path: centroid / kappa
 };
 
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -63,6 +72,9 @@ __device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t b, uint32_t
     uint32_t d;
     asm("lop3.b32 %0, %1, %2, %3, 0xEA;\n" : "=r"(d) : "r"(a), "r"(b), "r"(c));  // (a & b) | c
     return d;
+}
+__device__ __forceinline__ uint32_t bit_select(uint32_t a, uint32_t b, uint32_t mask) {
+    return (a & mask) | (b & ~mask);   // one LOP3
 }
 
 __device__ __forceinline__ float ex2(float x) {
@@ -106,15 +118,14 @@ __device__ __forceinline__ float wht32_lane(float v, int lane) {
 
 // ---- per-warp asynchronous staging -------------------------------------------------------
 // Each warp owns a ring of kStages stages in shared memory; one stage holds the packed bytes of
-// 16 consecutive tokens of one KV head: K indices [16][64 B], V indices [16][64 B], K scales
-// [16][8 B], V scales [16][8 B].  Lanes fill a stage with cp.async (16-byte pieces for the
-// indices, 8-byte pieces for the scales) and track completion with commit/wait groups, so no
-// thread ever spins on a flag.  The 16-byte piece c of token row t is stored at piece
-// c ^ ((t >> 1) & 3): with that XOR both access patterns below touch 32 distinct banks.
-constexpr int kStages = 4;
-constexpr int kStageBytes = 1024 + 1024 + 128 + 128;
-constexpr int kRingBytes = kStages * kStageBytes;
-
+// 16 consecutive tokens of one KV head: K indices [16][ROWB], V indices [16][ROWB], K scales
+// [16][8 B], V scales [16][8 B] (ROWB = 64 for 4-bit, 48 for 3-bit).  Lanes fill a stage with
+// cp.async (16-byte pieces for the indices, 8-byte pieces for the scales) and track completion
+// with commit/wait groups, so no thread ever spins on a flag.
+// 4-bit: the 16-byte piece c of token row t is stored at piece c ^ ((t >> 1) & 3); with that XOR
+// the K pattern (8 tokens x word j) and the V pattern (4 tokens x half-word n) both touch 32
+// distinct banks.  3-bit rows are 12 words long, which already spreads both patterns over the
+// banks, so they are stored densely.
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
 }
@@ -136,74 +147,97 @@ __device__ __forceinline__ uint2 lds64(uint32_t addr) {
     return v;
 }
 
-// Per-lane copy plan of one stage: two 16-byte index pieces (rows t0, t0 + 8) of K and of V,
-// and one 8-byte scale row (K for lanes 0..15, V for lanes 16..31).
-struct FillPlan {
-    const uint8_t* k;     // K piece of row t0 of group 0
-    const uint8_t* v;
-    const uint16_t* sc;
-    uint32_t dst0, dst1, dsts;
-    int t0, ts;
+template <int BITS>
+struct Geo {
+    static constexpr int kRowB = 16 * BITS;            // packed bytes per token row
+    static constexpr int kIdxB = kGroup * kRowB;       // one index array of a stage
+    static constexpr int kStageB = 2 * kIdxB + 256;    // + K and V scales
+    static constexpr int kRingB = kStages * kStageB;
+    static constexpr int kPieces = kIdxB / 16;         // 16-byte pieces per index array (64 | 48)
 };
 
+// Per-lane copy plan of one stage: up to two 16-byte index pieces of K and of V, and one 8-byte
+// scale row (K for lanes 0..15, V for lanes 16..31).
+struct FillPlan {
+    const uint8_t* k0;    // piece 0 of group 0
+    const uint8_t* v0;
+    const uint16_t* sc;
+    uint32_t dst0, dst1, dsts;
+    int src1_delta;       // byte distance from piece 0 to piece 1 in global memory
+    int t0, t1, ts;       // token rows (inside the group) of the two pieces and of the scale row
+    bool has1;
+};
+
+template <int BITS>
 __device__ __forceinline__ FillPlan make_plan(const MmaArgs& a, size_t row0, int first, int lane) {
+    using G = Geo<BITS>;
     FillPlan f;
-    f.t0 = lane >> 2;                // pieces lane and lane + 32 belong to rows t0 and t0 + 8
-    const int pc = lane & 3;
-    const uint8_t* kb = reinterpret_cast<const uint8_t*>(a.kw);
-    const uint8_t* vb = reinterpret_cast<const uint8_t*>(a.vw);
-    f.k = kb + (row0 + first + f.t0) * 64 + pc * 16;
-    f.v = vb + (row0 + first + f.t0) * 64 + pc * 16;
-    f.dst0 = f.t0 * 64 + ((pc ^ ((f.t0 >> 1) & 3)) << 4);
-    f.dst1 = f.dst0 + 512;           // row t0 + 8 has the same (t >> 1) & 3
+    constexpr int ppr = G::kRowB / 16;       // pieces per row: 4 | 3
+    const int c0 = lane, c1 = lane + 32;
+    f.t0 = c0 / ppr;
+    f.t1 = c1 / ppr;
+    const int pc0 = c0 - f.t0 * ppr, pc1 = c1 - f.t1 * ppr;
+    f.has1 = c1 < G::kPieces;
+    f.k0 = a.kb + (row0 + first + f.t0) * G::kRowB + pc0 * 16;
+    f.v0 = a.vb + (row0 + first + f.t0) * G::kRowB + pc0 * 16;
+    f.src1_delta = (f.t1 - f.t0) * G::kRowB + (pc1 - pc0) * 16;
+    if (BITS == 4) {
+        f.dst0 = f.t0 * 64 + ((pc0 ^ ((f.t0 >> 1) & 3)) << 4);
+        f.dst1 = f.t1 * 64 + ((pc1 ^ ((f.t1 >> 1) & 3)) << 4);
+    } else {
+        f.dst0 = c0 * 16;
+        f.dst1 = c1 * 16;
+    }
     f.ts = lane & 15;
     f.sc = (lane < 16 ? a.ks : a.vs) + (row0 + first + f.ts) * 4;
-    f.dsts = 2048 + (lane < 16 ? 0 : 128) + f.ts * 8;
+    f.dsts = 2 * G::kIdxB + (lane < 16 ? 0 : 128) + f.ts * 8;
     return f;
 }
 
-// Issues the copies of the 16 tokens starting at `gs` = first + byte_off / 64 into the stage at
+// Issues the copies of the 16 tokens starting at `gs` (= first + row_off rows) into the stage at
 // shared address `st`.  Rows past the last valid token re-read the last token (they are masked
 // later), which only happens in the final group of a sequence.
-__device__ __forceinline__ void stage_fill(const FillPlan& f, size_t byte_off, int gs, int last, uint32_t st) {
-    if (gs + 16 <= last + 1) {
-        cp_async16(st + f.dst0, f.k + byte_off);
-        cp_async16(st + f.dst1, f.k + byte_off + 512);
-        cp_async16(st + 1024 + f.dst0, f.v + byte_off);
-        cp_async16(st + 1024 + f.dst1, f.v + byte_off + 512);
-        cp_async8(st + f.dsts, f.sc + (byte_off >> 4));
-    } else {
-        const long long b0 = (long long)(min(gs + f.t0, last) - (gs + f.t0)) * 64;
-        const long long b1 = (long long)(min(gs + f.t0 + 8, last) - (gs + f.t0 + 8)) * 64;
-        const long long bs = (long long)(min(gs + f.ts, last) - (gs + f.ts)) * 4;
-        cp_async16(st + f.dst0, f.k + byte_off + b0);
-        cp_async16(st + f.dst1, f.k + byte_off + 512 + b1);
-        cp_async16(st + 1024 + f.dst0, f.v + byte_off + b0);
-        cp_async16(st + 1024 + f.dst1, f.v + byte_off + 512 + b1);
-        cp_async8(st + f.dsts, f.sc + (byte_off >> 4) + bs);
+template <int BITS>
+__device__ __forceinline__ void stage_fill(const FillPlan& f, size_t row_off, int gs, int last, uint32_t st) {
+    using G = Geo<BITS>;
+    const size_t boff = row_off * G::kRowB;
+    long long b0 = 0, b1 = 0, bs = 0;
+    if (gs + kGroup > last + 1) {
+        b0 = (long long)(min(gs + f.t0, last) - (gs + f.t0)) * G::kRowB;
+        b1 = (long long)(min(gs + f.t1, last) - (gs + f.t1)) * G::kRowB;
+        bs = (long long)(min(gs + f.ts, last) - (gs + f.ts)) * 4;
     }
+    cp_async16(st + f.dst0, f.k0 + boff + b0);
+    cp_async16(st + G::kIdxB + f.dst0, f.v0 + boff + b0);
+    if (f.has1) {
+        cp_async16(st + f.dst1, f.k0 + boff + f.src1_delta + b1);
+        cp_async16(st + G::kIdxB + f.dst1, f.v0 + boff + f.src1_delta + b1);
+    }
+    cp_async8(st + f.dsts, f.sc + row_off * 4 + bs);
 }
 
-// 4-bit MaxNorm ("PQO4") kernel.  Grid (kv heads, partitions), 4 warps; each warp walks its
-// partition in steps of 16 tokens and keeps its own online-softmax state; the four states are
-// merged through shared memory at the end and written as one split-K partial.
+// Grid (kv heads, partitions), 4 warps; each warp walks its partition in steps of 16 tokens and
+// keeps its own online-softmax state; the four states are merged through shared memory at the
+// end and written as one split-K partial.
 //
 // NSPLIT = true (GQA group <= 4): the MMA columns 0..3 of O^T = V^T P' carry the f16 "hi" part of
 // P' for heads 0..3 and columns 4..7 the "lo" part, so one MMA delivers the split-precision
 // product.  NSPLIT = false (group 5..8): hi and lo take one MMA each.
-// The query is split the same way along the 16 MMA rows of S^T = Q~ K^T: rows 0..7 hold the
-// hi parts of the (up to) 8 heads, rows 8..15 the lo parts.
-template <typename QT, bool NSPLIT>
-__global__ void __launch_bounds__(kThreads, 3) decode_pqo4_mma_kernel(MmaArgs a) {
-    __shared__ __align__(1024) unsigned char s_raw[kWarps * kRingBytes];
+template <typename QT, int BITS, bool NSPLIT>
+__global__ void __launch_bounds__(kThreads, 3) decode_mma_kernel(MmaArgs a) {
+    using G = Geo<BITS>;
+    __shared__ __align__(1024) unsigned char s_raw[kWarps * G::kRingB];
+    // 3-bit: the lookup table lives in dynamic shared memory at an 8 KB-aligned address, so that a
+    // table address is formed by OR-ing (index << 7) into the lane's base with one LOP3.
+    extern __shared__ unsigned char s_dyn[];
     __shared__ float s_q[8 * kD];   // rotated queries (prologue only)
+    __shared__ float s_sign[32];
     // epilogue view of the ring memory (the rings are idle then)
     float (*s_o)[8][kD] = reinterpret_cast<float (*)[8][kD]>(s_raw);                 // [kWarps][8][128]
     float (*s_m)[8] = reinterpret_cast<float (*)[8]>(s_raw + kWarps * 8 * kD * 4);   // [kWarps][8]
     float (*s_l)[8] = s_m + kWarps;
     float (*s_z)[8][4] = reinterpret_cast<float (*)[8][4]>(s_l + kWarps);
-    __shared__ float s_sign[32];
-    static_assert(kWarps * kRingBytes >= kWarps * 8 * kD * 4 + kWarps * 8 * 4 * 2 + kWarps * 8 * 4 * 4, "ring too small");
+    static_assert(kWarps * G::kRingB >= kWarps * 8 * kD * 4 + kWarps * 8 * 4 * 2 + kWarps * 8 * 4 * 4, "ring too small");
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int n = lane >> 2, j = lane & 3;     // n: MMA column / row group, j: position in the quad
@@ -211,16 +245,6 @@ __global__ void __launch_bounds__(kThreads, 3) decode_pqo4_mma_kernel(MmaArgs a)
     const int g = a.g;
 
     // ---- start streaming the first stages before anything else: the copies do not depend on q ----
-    float m_run = kNegBig, l_run = 0.0f;
-    float z[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    float o[4][2][4];
-#pragma unroll
-    for (int b = 0; b < 4; ++b)
-#pragma unroll
-        for (int m = 0; m < 2; ++m)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) o[b][m][i] = 0.0f;
-
     const int t_begin = part * a.part_size;
     const int t_end = min(t_begin + a.part_size, a.kv_len);
     const size_t row0 = (size_t)kvh * a.kv_stride;
@@ -228,33 +252,58 @@ __global__ void __launch_bounds__(kThreads, 3) decode_pqo4_mma_kernel(MmaArgs a)
     const int first = t_begin + warp * kGroup;
     const int stride = kWarps * kGroup;
     const int ngroups = first < t_end ? (t_end - first + stride - 1) / stride : 0;
-
-    const uint32_t ring = (uint32_t)__cvta_generic_to_shared(s_raw) + warp * kRingBytes;
-    // per-thread shared-memory offsets inside a stage
-    uint32_t koff[4], voff[4];
-#pragma unroll
-    for (int b = 0; b < 4; ++b) {
-        koff[b] = n * 64 + ((b ^ ((n >> 1) & 3)) << 4) + j * 4;                 // token n (+8o: +512), word j of block b
-        voff[b] = 1024 + (2 * j) * 64 + ((b ^ j) << 4) + (n >> 1) * 4;          // token 2j (+e: +64, +8o: +512), word n/2
-    }
-    const uint32_t scoff = 2048 + (2 * j) * 8;                                   // scales of token 2j (+e: +8, +8o: +64)
-    const uint32_t vsel = (n & 1) ? 0x7632u : 0x5410u;
-
-    const FillPlan plan = make_plan(a, row0, first, lane);
-    const size_t group_bytes = (size_t)stride * 64;   // K/V index bytes between consecutive groups of this warp
+    const uint32_t ring = (uint32_t)__cvta_generic_to_shared(s_raw) + warp * G::kRingB;
+    const FillPlan plan = make_plan<BITS>(a, row0, first, lane);
 #pragma unroll
     for (int i = 0; i < kStages - 1; ++i) {
-        if (i < ngroups) stage_fill(plan, i * group_bytes, first + i * stride, last, ring + i * kStageBytes);
+        if (i < ngroups) stage_fill<BITS>(plan, (size_t)i * stride, first + i * stride, last, ring + i * G::kStageB);
         cp_async_commit();
     }
     uint32_t st = ring;                                        // stage being consumed
-    uint32_t st_fill = ring + (kStages - 1) * kStageBytes;     // stage being refilled
-    size_t fill_off = (kStages - 1) * group_bytes;
+    uint32_t st_fill = ring + (kStages - 1) * G::kStageB;      // stage being refilled
+    size_t fill_row = (size_t)(kStages - 1) * stride;
 
+    // per-thread shared-memory offsets inside a stage
+    uint32_t koff[4], voff[4];
+    uint32_t khi = 0, vhi = 0, ksh = 0, vsh = 0;   // 3-bit: distance to the second word, funnel shifts
+    if (BITS == 4) {
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            koff[b] = n * 64 + ((b ^ ((n >> 1) & 3)) << 4) + j * 4;             // token n (+8o: +512), word j of block b
+            voff[b] = G::kIdxB + (2 * j) * 64 + ((b ^ j) << 4) + (n >> 1) * 4;  // token 2j (+e: +64, +8o: +512), word n/2
+        }
+    } else {
+        // K: the 24 bits at byte 3j of block b;  V: the 12 bits at bit 12n of block b
+        const int kw0 = (3 * j) >> 2;
+        const int vw0 = (12 * n) >> 5;
+        khi = (kw0 < 2) ? 4 : 0;
+        ksh = ((3 * j) & 3) * 8;
+        vsh = (12 * n) & 31;
+        vhi = (vsh + 12 > 32) ? 4 : 0;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            koff[b] = n * 48 + 12 * b + 4 * kw0;                                // token n (+8o: +384)
+            voff[b] = G::kIdxB + (2 * j) * 48 + 12 * b + 4 * vw0;               // token 2j (+e: +48, +8o: +384)
+        }
+    }
+    constexpr uint32_t kOct = 8 * G::kRowB;                                     // 8 token rows
+    constexpr uint32_t kRow = G::kRowB;
+    const uint32_t scoff = 2 * G::kIdxB + (2 * j) * 8;                          // scales of token 2j (+e: +8, +8o: +64)
+    const uint32_t vsel = (n & 1) ? 0x7632u : 0x5410u;
+    const uint32_t lut_base = BITS == 3 ? (((uint32_t)__cvta_generic_to_shared(s_dyn) + 8191u) & ~8191u) : 0u;
+    const uint32_t lut = lut_base + lane * 4;
 
     if (tid < 32) {
         const uint32_t neg = 0xB1A6D4B2u;  // src/cache/precomputed/rotation.rs:16-20
-        s_sign[tid] = a.dev_signs ? a.dev_signs[tid] : (((neg >> tid) & 1u) ? -a.sign_mag : a.sign_mag);
+        s_sign[tid] = ((neg >> tid) & 1u) ? -a.sign_mag : a.sign_mag;
+    }
+    if (BITS == 3) {
+        // entry e = c0 | c1 << 3 -> half2(lut[c0], lut[c1]), one copy per bank
+        for (int i = tid; i < 64 * 32; i += kThreads) {
+            const int e = i >> 5;
+            const uint32_t v = pack_hi(a.lut[e & 7], a.lut[e >> 3]);
+            asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(lut_base + i * 4), "r"(v) : "memory");
+        }
     }
     __syncthreads();
     // ---- rotate the g queries of this KV head once: q~ = sigma .* H32(q_b) / sqrt(32), constants folded ----
@@ -270,7 +319,8 @@ __global__ void __launch_bounds__(kThreads, 3) decode_pqo4_mma_kernel(MmaArgs a)
     }
     __syncthreads();
     // A fragments: rows 0..7 = hi(q~) of head n, rows 8..15 = lo(q~) of head n.  For block b and
-    // half m the k-slots (2j, 2j+1 | 2j+8, 2j+9) hold dims 32b + 8j + 2m + (0, 4 | 1, 5).
+    // half m the k-slots (2j, 2j+1 | 2j+8, 2j+9) hold the dims that the code unpackers deliver:
+    //   4-bit: 32b + 8j + 2m + (0, 4 | 1, 5)      3-bit: 32b + 8j + 4m + (0, 1 | 2, 3)
     uint32_t afr[4][2][4];
     float qbar[4];
     {
@@ -280,26 +330,37 @@ __global__ void __launch_bounds__(kThreads, 3) decode_pqo4_mma_kernel(MmaArgs a)
             float s = 0.0f;
 #pragma unroll
             for (int m = 0; m < 2; ++m) {
-                const int d0 = 32 * b + 8 * j + 2 * m;
-                const float q0 = sq[d0], q4 = sq[d0 + 4], q1 = sq[d0 + 1], q5 = sq[d0 + 5];
-                afr[b][m][0] = pack_hi(q0, q4);
-                afr[b][m][1] = pack_lo(q0, q4);
-                afr[b][m][2] = pack_hi(q1, q5);
-                afr[b][m][3] = pack_lo(q1, q5);
-                s += (q0 + q4) + (q1 + q5);
+                const int d0 = 32 * b + 8 * j + (BITS == 4 ? 2 * m : 4 * m);
+                const float qa = sq[d0], qb = sq[d0 + (BITS == 4 ? 4 : 1)];
+                const float qc = sq[d0 + (BITS == 4 ? 1 : 2)], qd = sq[d0 + (BITS == 4 ? 5 : 3)];
+                afr[b][m][0] = pack_hi(qa, qb);
+                afr[b][m][1] = pack_lo(qa, qb);
+                afr[b][m][2] = pack_hi(qc, qd);
+                afr[b][m][3] = pack_lo(qc, qd);
+                s += (qa + qb) + (qc + qd);
             }
             s += __shfl_xor_sync(0xffffffffu, s, 1);
             s += __shfl_xor_sync(0xffffffffu, s, 2);
-            qbar[b] = 0.5f * s;   // the +0.5 of (i - 7.5) = (i - 8) + 0.5, summed over the block
+            qbar[b] = BITS == 4 ? 0.5f * s : 0.0f;   // 4-bit: the +0.5 of (i - 7.5) = (i - 8) + 0.5, summed over the block
         }
     }
 
+    float m_run = kNegBig, l_run = 0.0f;
+    float z[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    float o[4][2][4];
+#pragma unroll
+    for (int b = 0; b < 4; ++b)
+#pragma unroll
+        for (int m = 0; m < 2; ++m)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) o[b][m][i] = 0.0f;
+
     for (int it = 0; it < ngroups; ++it) {
         const int gs = first + it * stride;
-        if (it + kStages - 1 < ngroups) stage_fill(plan, fill_off, gs + (kStages - 1) * stride, last, st_fill);
+        if (it + kStages - 1 < ngroups) stage_fill<BITS>(plan, fill_row, gs + (kStages - 1) * stride, last, st_fill);
         cp_async_commit();
-        fill_off += group_bytes;
-        st_fill = (st_fill + kStageBytes == ring + kRingBytes) ? ring : st_fill + kStageBytes;
+        fill_row += stride;
+        st_fill = (st_fill + G::kStageB == ring + G::kRingB) ? ring : st_fill + G::kStageB;
         cp_async_wait<kStages - 1>();
         __syncwarp();
 
@@ -313,7 +374,16 @@ __global__ void __launch_bounds__(kThreads, 3) decode_pqo4_mma_kernel(MmaArgs a)
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
                 uint32_t x[4];
-                nibbles_to_half2(lds32(st + koff[b] + o8 * 512), x);
+                if (BITS == 4) {
+                    nibbles_to_half2(lds32(st + koff[b] + o8 * kOct), x);
+                } else {
+                    const uint32_t lo = lds32(st + koff[b] + o8 * kOct), hi = lds32(st + koff[b] + o8 * kOct + khi);
+                    const uint32_t w = __funnelshift_r(lo, hi, ksh);          // codes 8j..8j+7 in bits 0..23
+                    x[0] = lds32(lop3_and_or(w << 7, 0x1F80u, lut));
+                    x[1] = lds32(lop3_and_or(w << 1, 0x1F80u, lut));
+                    x[2] = lds32(lop3_and_or(w >> 5, 0x1F80u, lut));
+                    x[3] = lds32(lop3_and_or(w >> 11, 0x1F80u, lut));
+                }
                 float acc[4] = {qbar[b], qbar[b], 0.0f, 0.0f};
                 mma16816(acc, afr[b][0][0], afr[b][0][1], afr[b][0][2], afr[b][0][3], x[0], x[1]);
                 mma16816(acc, afr[b][1][0], afr[b][1][1], afr[b][1][2], afr[b][1][3], x[2], x[3]);
@@ -381,13 +451,30 @@ __global__ void __launch_bounds__(kThreads, 3) decode_pqo4_mma_kernel(MmaArgs a)
                     const __half2 pr = u32_as_h2(b < 2 ? vs[o8][e].x : vs[o8][e].y);
                     pf[o8][e] = p[o8][e] * fabsf((b & 1) ? __high2float(pr) : __low2float(pr));
                 }
-            z[b] += (pf[0][0] + pf[0][1]) + (pf[1][0] + pf[1][1]);
+            if (BITS == 4) z[b] += (pf[0][0] + pf[0][1]) + (pf[1][0] + pf[1][1]);
             const uint32_t b0h = pack_hi(pf[0][0], pf[0][1]), b1h = pack_hi(pf[1][0], pf[1][1]);
             const uint32_t b0l = pack_lo(pf[0][0], pf[0][1]), b1l = pack_lo(pf[1][0], pf[1][1]);
-            // half-word n of block b of the four tokens, paired (token 2j, token 2j+1)
+            // codes 4n..4n+3 of block b of the four tokens, paired (token 2j, token 2j+1)
             uint32_t xab[4], xcd[4];
-            nibbles_to_half2(__byte_perm(lds32(st + voff[b]), lds32(st + voff[b] + 64), vsel), xab);
-            nibbles_to_half2(__byte_perm(lds32(st + voff[b] + 512), lds32(st + voff[b] + 576), vsel), xcd);
+            if (BITS == 4) {
+                nibbles_to_half2(__byte_perm(lds32(st + voff[b]), lds32(st + voff[b] + kRow), vsel), xab);
+                nibbles_to_half2(__byte_perm(lds32(st + voff[b] + kOct), lds32(st + voff[b] + kOct + kRow), vsel), xcd);
+            } else {
+#pragma unroll
+                for (int o8 = 0; o8 < 2; ++o8) {
+                    const uint32_t base = st + voff[b] + o8 * kOct;
+                    const uint32_t xa = __funnelshift_r(lds32(base), lds32(base + vhi), vsh);                // token 2j
+                    const uint32_t xb = __funnelshift_r(lds32(base + kRow), lds32(base + kRow + vhi), vsh);  // token 2j+1
+                    // 6-bit fields (code of token 2j | code of token 2j+1 << 3): codes 0, 2 in z0, codes 1, 3 in z1
+                    const uint32_t z0 = bit_select(xa, xb << 3, 0x1C7u);
+                    const uint32_t z1 = bit_select(xa >> 3, xb, 0x1C7u);
+                    uint32_t* xo = o8 == 0 ? xab : xcd;
+                    xo[0] = lds32(lop3_and_or(z0 << 7, 0x1F80u, lut));
+                    xo[2] = lds32(lop3_and_or(z0 << 1, 0x1F80u, lut));
+                    xo[1] = lds32(lop3_and_or(z1 << 7, 0x1F80u, lut));
+                    xo[3] = lds32(lop3_and_or(z1 << 1, 0x1F80u, lut));
+                }
+            }
             if (NSPLIT) {
                 const uint32_t b0 = n < 4 ? b0h : b0l, b1 = n < 4 ? b1h : b1l;
                 mma16816(o[b][0], xab[0], xab[1], xcd[0], xcd[1], b0, b1);
@@ -400,7 +487,7 @@ __global__ void __launch_bounds__(kThreads, 3) decode_pqo4_mma_kernel(MmaArgs a)
             }
         }
         __syncwarp();   // every lane is done with this stage before it is refilled
-        st = (st + kStageBytes == ring + kRingBytes) ? ring : st + kStageBytes;
+        st = (st + G::kStageB == ring + G::kRingB) ? ring : st + G::kStageB;
     }
     cp_async_wait<0>();
     __syncthreads();    // all rings idle: the memory is reused for the merge
@@ -455,6 +542,53 @@ __global__ void __launch_bounds__(kThreads, 3) decode_pqo4_mma_kernel(MmaArgs a)
     }
 }
 
+// kappa in [1, 2) such that every centroid / kappa is as close as possible to an f16 value.
+float best_kappa(const float* c, int n) {
+    float best = 1.0f;
+    double best_err = 1e9;
+    for (int i = 0; i < (1 << 18); ++i) {
+        const float kappa = 1.0f + (float)i / (float)(1 << 18);
+        double err = 0.0;
+        for (int k = 0; k < n; ++k) {
+            if (c[k] == 0.0f) continue;
+            const float v = c[k] / kappa;
+            const float r = __half2float(__float2half_rn(v));
+            err = fmax(err, fabs((double)r * kappa - c[k]) / fabs((double)c[k]));
+        }
+        if (err < best_err) { best_err = err; best = kappa; }
+    }
+    return best;
+}
+
+struct LutCache {
+    bool valid = false;
+    float kappa = 1.0f;
+    float lut[8];
+};
+std::mutex g_lut_mutex;
+LutCache g_lut_cache[2][2];   // [norm_mode][all_outlier]
+
+template <int BITS>
+int launch(const MmaArgs& a, int g, int q_dtype, dim3 grid, cudaStream_t s) {
+    const size_t dyn = BITS == 3 ? 16384 : 0;   // 8 KB table + slack for its 8 KB alignment
+#define TQB_LAUNCH_MMA(QT)                                                                  \
+    do {                                                                                    \
+        if (dyn) {  /* static + dynamic shared memory passes 48 KB: opt in */               \
+            cudaError_t e = g <= 4                                                          \
+                ? cudaFuncSetAttribute(decode_mma_kernel<QT, BITS, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn)  \
+                : cudaFuncSetAttribute(decode_mma_kernel<QT, BITS, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn); \
+            if (e != cudaSuccess) { set_cuda_error(e); return TQB_ERR_CUDA; }               \
+        }                                                                                   \
+        if (g <= 4) decode_mma_kernel<QT, BITS, true><<<grid, kThreads, dyn, s>>>(a);       \
+        else decode_mma_kernel<QT, BITS, false><<<grid, kThreads, dyn, s>>>(a);             \
+    } while (0)
+    if (q_dtype == TQB_F32) TQB_LAUNCH_MMA(float);
+    else if (q_dtype == TQB_F16) TQB_LAUNCH_MMA(__half);
+    else TQB_LAUNCH_MMA(__nv_bfloat16);
+#undef TQB_LAUNCH_MMA
+    return check_launch(s);
+}
+
 }  // namespace
 
 // Returns TQB_ERR_UNSUPPORTED when the shape is outside what the tensor-core kernels cover;
@@ -464,41 +598,53 @@ int launch_decode_mma(const tqb_decode_params* p, int num_partitions, float* par
     const int g = p->num_q_heads / p->num_kv_heads;
     const int nblk = p->head_dim / kBlock;
     const bool all_outlier = p->outlier_blocks < 0 || p->outlier_blocks >= nblk;
-    if (p->head_dim != kD || g > 8 || p->qjl_enabled) return TQB_ERR_UNSUPPORTED;
-    if (!(p->bits == 4 && p->norm_mode == TQB_MAXNORM && all_outlier)) return TQB_ERR_UNSUPPORTED;
+    const bool all_normal = p->outlier_blocks == 0;
+    if (p->head_dim != kD || g > 8 || p->qjl_enabled || p->kv_len <= 0) return TQB_ERR_UNSUPPORTED;
+    const bool pqo4 = p->bits == 4 && p->norm_mode == TQB_MAXNORM && all_outlier;
+    const bool lut3 = p->bits == 3 && (all_outlier || all_normal);
+    if (!pqo4 && !lut3) return TQB_ERR_UNSUPPORTED;
     if (((uintptr_t)p->k_scales % 8) || ((uintptr_t)p->v_scales % 8)) return TQB_ERR_UNSUPPORTED;
     if (((uintptr_t)p->k_indices % 16) || ((uintptr_t)p->v_indices % 16)) return TQB_ERR_UNSUPPORTED;
-    if (p->kv_len <= 0) return TQB_ERR_UNSUPPORTED;
     MmaArgs a{};
     a.q = p->q;
-    a.kw = reinterpret_cast<const uint32_t*>(p->k_indices);
+    a.kb = p->k_indices;
     a.ks = p->k_scales;
-    a.vw = reinterpret_cast<const uint32_t*>(p->v_indices);
+    a.vb = p->v_indices;
     a.vs = p->v_scales;
     a.partial_out = partial_out;
     a.partial_max = partial_max;
     a.partial_sum = partial_sum;
-    a.dev_signs = nullptr;
     a.hq = p->num_q_heads; a.hkv = p->num_kv_heads; a.g = g;
     a.kv_len = p->kv_len; a.kv_stride = p->kv_stride; a.num_partitions = num_partitions;
     const int step = kWarps * kGroup;
     a.part_size = ((p->kv_len + num_partitions - 1) / num_partitions + step - 1) / step * step;
-    const float R = 2.1573f;
-    const float grid_step = (2.0f * R) / 15.0f;   // codebooks.rs:64-67
-    a.qk_const = p->softmax_scale * 1.4426950408889634f * grid_step;
-    a.v_const = grid_step;
     a.sign_mag = sign_mag;
     dim3 grid(p->num_kv_heads, num_partitions);
-#define TQB_LAUNCH_PQO4(QT)                                                              \
-    do {                                                                                 \
-        if (g <= 4) decode_pqo4_mma_kernel<QT, true><<<grid, kThreads, 0, s>>>(a);       \
-        else decode_pqo4_mma_kernel<QT, false><<<grid, kThreads, 0, s>>>(a);             \
-    } while (0)
-    if (p->q_dtype == TQB_F32) TQB_LAUNCH_PQO4(float);
-    else if (p->q_dtype == TQB_F16) TQB_LAUNCH_PQO4(__half);
-    else TQB_LAUNCH_PQO4(__nv_bfloat16);
-#undef TQB_LAUNCH_PQO4
-    return check_launch(s);
+    const float log2e = 1.4426950408889634f;
+    if (pqo4) {
+        const float R = 2.1573f;
+        const float grid_step = (2.0f * R) / 15.0f;   // codebooks.rs:64-67
+        a.qk_const = p->softmax_scale * log2e * grid_step;
+        a.v_const = grid_step;
+        return launch<4>(a, g, p->q_dtype, grid, s);
+    }
+    {
+        std::lock_guard<std::mutex> lock(g_lut_mutex);
+        LutCache& lc = g_lut_cache[p->norm_mode == TQB_L2NORM ? 1 : 0][all_outlier ? 1 : 0];
+        if (!lc.valid) {
+            Codebook cb;
+            if (!block_codebook(all_outlier ? 3 : 2, p->norm_mode, cb)) return TQB_ERR_UNSUPPORTED;
+            float c[8];
+            for (int i = 0; i < 8; ++i) c[i] = cb.c[i < cb.n ? i : cb.n - 1];   // codes past a 4-entry book clamp (quantize_tensor.rs:245)
+            lc.kappa = best_kappa(c, 8);
+            for (int i = 0; i < 8; ++i) lc.lut[i] = c[i] / lc.kappa;
+            lc.valid = true;
+        }
+        a.qk_const = p->softmax_scale * log2e * lc.kappa;
+        a.v_const = lc.kappa;
+        for (int i = 0; i < 8; ++i) a.lut[i] = lc.lut[i];
+    }
+    return launch<3>(a, g, p->q_dtype, grid, s);
 }
 
 }  // namespace tqb
