@@ -322,6 +322,47 @@ int tqb_pqo_cache_attend_partial(tqb_pqo_cache *c, int32_t layer, const void *q,
                                  int32_t num_q_heads, float softmax_scale, float *out_unnorm, float *lse_out,
                                  tqb_stream_t stream);
 
+/* compute_qjl_signs_and_norms (src/cache/tq.rs:380-411) as a kernel: residual = original - dequantized
+ * for n vectors of `dim` (32, 64, 128 or 256), its L2 norm as f16 bits and the dim-wide sign sketch,
+ * written at storage rows (same row mapping as tqb_block_quantize).  rbits: device bit matrix of
+ * tqb_qjl_rademacher_bits.  original: device [n, dim] of `dtype`; dequantized: device [n, dim] f32. */
+int tqb_residual_sketch(int32_t dim, const uint32_t *rbits, const void *original, int32_t dtype,
+                        const float *dequantized, int64_t n, uint8_t *signs, uint16_t *norms,
+                        int64_t rows_per_group, int64_t out_group_stride, int64_t out_row_offset,
+                        tqb_stream_t stream);
+/* compute_logit_bias (src/cache/tq.rs:185-253): bias[h, i, t] = (sum_d rq[h, i, d] * sign_td) * norm_t *
+ * sqrt(pi/2) / sqrt(head_dim).  rq: device [num_q_heads, q_len, head_dim] f32 (tqb_qjl_query_projections);
+ * signs [num_kv_heads, kv_stride, head_dim/8]; norms [num_kv_heads, kv_stride];
+ * bias: device [num_q_heads, q_len, kv_len] of bias_dtype. */
+int tqb_qjl_logit_bias(int32_t head_dim, const float *rq, const uint8_t *signs, const uint16_t *norms, void *bias,
+                       int32_t bias_dtype, int32_t num_q_heads, int32_t num_kv_heads, int32_t q_len,
+                       int32_t kv_len, int32_t kv_stride, tqb_stream_t stream);
+
+/* TqCache (src/cache/tq.rs:21-412): polar codes (outlier_blocks = 0: the bits-1 codebook stored at
+ * `bits` width) plus a QJL sign sketch of the key residual.  All pointers are DEVICE pointers.
+ * k, v: [batch, num_kv_heads, new_tokens, head_dim]; q: [batch, num_q_heads, q_len, head_dim];
+ * logit_bias: [batch, num_q_heads, q_len, seq_len] of `dtype` (DequantResult::logit_bias). */
+typedef struct tqb_tq_cache tqb_tq_cache;
+int tqb_tq_cache_create(const tqb_cache_config *cfg, tqb_tq_cache **out);
+void tqb_tq_cache_destroy(tqb_tq_cache *c);
+/* prefill (tq.rs:263-288): k_out/v_out receive the full dequantized cache when the layer already held tokens. */
+int tqb_tq_cache_prefill(tqb_tq_cache *c, int32_t layer, const void *k, const void *v, const void *q, int32_t dtype,
+                         int32_t new_tokens, int32_t num_q_heads, int32_t q_len, void *k_out, void *v_out,
+                         void *logit_bias, tqb_stream_t stream);
+/* decode (tq.rs:290-311): DecodeOutput::Dequantized { k, v, logit_bias } over all seq_len tokens. */
+int tqb_tq_cache_decode(tqb_tq_cache *c, int32_t layer, const void *k, const void *v, const void *q, int32_t dtype,
+                        int32_t num_q_heads, void *k_out, void *v_out, void *logit_bias, tqb_stream_t stream);
+/* Fused alternative that the reference's kernel offers but never calls (tq_attention_kernel.cu:197-231):
+ * append, then attention with the QJL correction added inside the kernel; out [batch, num_q_heads, 1, head_dim]. */
+int tqb_tq_cache_decode_fused(tqb_tq_cache *c, int32_t layer, const void *k, const void *v, const void *q,
+                              int32_t dtype, int32_t num_q_heads, float softmax_scale, void *out,
+                              tqb_stream_t stream);
+int64_t tqb_tq_cache_seq_len(const tqb_tq_cache *c, int32_t layer);
+int tqb_tq_cache_reset(tqb_tq_cache *c);
+size_t tqb_tq_cache_memory_usage(const tqb_tq_cache *c);
+int tqb_tq_cache_qjl_ptrs(const tqb_tq_cache *c, int32_t layer, const uint8_t **signs, const uint16_t **norms,
+                          int64_t *capacity);
+
 /* QuantizedKVCache (src/attention.rs:45-694): whole-vector polar + QJL blocks for keys
  * and values, one growable device array set per layer.  Vectors are HOST pointers unless
  * the name says otherwise; these calls synchronise the stream before returning. */

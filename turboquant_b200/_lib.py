@@ -99,6 +99,17 @@ def _declare(lib):
         "tqb_pqo_cache_memory_usage": (S, [P]),
         "tqb_pqo_cache_layer_ptrs": (c_int, [P, I, P, P, P, P]),
         "tqb_pqo_cache_attend_partial": (c_int, [P, I, P, I, I, F, P, P, P]),
+        "tqb_residual_sketch": (c_int, [I, P, P, I, P, L, P, P, L, L, L, P]),
+        "tqb_qjl_logit_bias": (c_int, [I, P, P, P, P, I, I, I, I, I, I, P]),
+        "tqb_tq_cache_create": (c_int, [P, P]),
+        "tqb_tq_cache_destroy": (None, [P]),
+        "tqb_tq_cache_prefill": (c_int, [P, I, P, P, P, I, I, I, I, P, P, P, P]),
+        "tqb_tq_cache_decode": (c_int, [P, I, P, P, P, I, I, P, P, P, P]),
+        "tqb_tq_cache_decode_fused": (c_int, [P, I, P, P, P, I, I, F, P, P]),
+        "tqb_tq_cache_seq_len": (L, [P, I]),
+        "tqb_tq_cache_reset": (c_int, [P]),
+        "tqb_tq_cache_memory_usage": (S, [P]),
+        "tqb_tq_cache_qjl_ptrs": (c_int, [P, I, P, P, P]),
         "tqb_kv_cache_create": (c_int, [P, I, U, P]),
         "tqb_kv_cache_destroy": (None, [P]),
         "tqb_kv_cache_push_batch": (c_int, [P, I, P, P, L, L, P]),

@@ -662,3 +662,69 @@ class PqoCache:
         ptrs = [ctypes.c_void_p() for _ in range(4)]
         check(lib.tqb_pqo_cache_layer_ptrs(self._h, layer, *[ctypes.byref(p) for p in ptrs]))
         return [p.value for p in ptrs]
+
+
+class TqCache:
+    """src/cache/tq.rs:21-412: polar codes (outlier_blocks = 0) plus a QJL sign sketch of the key
+    residual.  CUDA tensors only.  k, v: [batch, Hkv, seq, head_dim]; q: [batch, Hq, q_len, head_dim]."""
+
+    def __init__(self, config):
+        self.config = config
+        self._h = ctypes.c_void_p()
+        c = config._c()
+        check(lib.tqb_tq_cache_create(ctypes.byref(c), ctypes.byref(self._h)))
+
+    def __del__(self):
+        h = getattr(self, "_h", None)
+        if h:
+            lib.tqb_tq_cache_destroy(h)
+            self._h = None
+
+    def seq_len(self, layer):
+        n = int(lib.tqb_tq_cache_seq_len(self._h, layer))
+        if n < 0:
+            raise LayerOutOfRange(f"layer index {layer} out of range (num_layers = {self.config.num_layers})")
+        return n
+
+    def prefill(self, layer, k, v, q):
+        """tq.rs:263-288: DequantResult with the originals (first call) or the dequantized cache, and logit_bias."""
+        k, v, q = k.contiguous(), v.contiguous(), q.contiguous()
+        new_tokens, hq, q_len = k.shape[2], q.shape[1], q.shape[2]
+        old = self.seq_len(layer)
+        total = old + new_tokens
+        cfg = self.config
+        k_out = v_out = None
+        if old > 0:
+            k_out = torch.empty((cfg.batch, cfg.num_kv_heads, total, cfg.head_dim), dtype=k.dtype, device=k.device)
+            v_out = torch.empty_like(k_out)
+        bias = torch.empty((cfg.batch, hq, q_len, total), dtype=q.dtype, device=q.device)
+        check(lib.tqb_tq_cache_prefill(self._h, layer, _ptr(k), _ptr(v), _ptr(q), _dtype_code(k.dtype), new_tokens, hq, q_len,
+                                       _ptr(k_out), _ptr(v_out), _ptr(bias), _stream()))
+        return DequantResult(k if old == 0 else k_out, v if old == 0 else v_out, bias)
+
+    def decode(self, layer, k, v, q, config=None):
+        """tq.rs:290-311: DecodeOutput::Dequantized(k, v, logit_bias) over every stored token."""
+        k, v, q = k.contiguous(), v.contiguous(), q.contiguous()
+        hq = q.shape[1]
+        total = self.seq_len(layer) + 1
+        cfg = self.config
+        k_out = torch.empty((cfg.batch, cfg.num_kv_heads, total, cfg.head_dim), dtype=k.dtype, device=k.device)
+        v_out = torch.empty_like(k_out)
+        bias = torch.empty((cfg.batch, hq, 1, total), dtype=q.dtype, device=q.device)
+        check(lib.tqb_tq_cache_decode(self._h, layer, _ptr(k), _ptr(v), _ptr(q), _dtype_code(k.dtype), hq, _ptr(k_out),
+                                      _ptr(v_out), _ptr(bias), _stream()))
+        return DecodeOutput(dequantized=DequantResult(k_out, v_out, bias))
+
+    def decode_fused(self, layer, k, v, q, config):
+        """Append, then fused attention with the in-kernel QJL correction (tq_attention_kernel.cu:197-231)."""
+        k, v, q = k.contiguous(), v.contiguous(), q.contiguous()
+        out = torch.empty_like(q)
+        check(lib.tqb_tq_cache_decode_fused(self._h, layer, _ptr(k), _ptr(v), _ptr(q), _dtype_code(k.dtype), q.shape[1],
+                                            config.softmax_scale, _ptr(out), _stream()))
+        return DecodeOutput(fused=out)
+
+    def reset(self):
+        check(lib.tqb_tq_cache_reset(self._h))
+
+    def memory_usage(self):
+        return int(lib.tqb_tq_cache_memory_usage(self._h))

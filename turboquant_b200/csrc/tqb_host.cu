@@ -603,3 +603,243 @@ size_t tqb_kv_cache_fp16_equivalent_memory(const tqb_kv_cache* c) {
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------
+// TqCache: block-32 polar codes (bits-1 codebook stored at `bits` width when outlier_blocks = 0)
+// plus a head_dim-wide QJL sign sketch of the key residual (src/cache/tq.rs:21-412).
+// The reference computes the sketch on the CPU after a device->host copy (tq.rs:396-410);
+// here it is a kernel and nothing leaves the device.
+// ---------------------------------------------------------------------------------------
+namespace {
+
+template <typename T>
+__global__ void to_f32_kernel(const T* __restrict__ in, float* __restrict__ out, long long n) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        out[i] = tqb::to_f32<T>(in[i]);
+}
+
+int convert_to_f32(const void* in, int dtype, float* out, long long n, cudaStream_t s) {
+    const int grid = (int)std::min<long long>((n + 255) / 256, 148 * 8);
+    if (dtype == TQB_F32) to_f32_kernel<float><<<grid, 256, 0, s>>>((const float*)in, out, n);
+    else if (dtype == TQB_F16) to_f32_kernel<__half><<<grid, 256, 0, s>>>((const __half*)in, out, n);
+    else to_f32_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)in, out, n);
+    return tqb::check_launch(s);
+}
+
+}  // namespace
+
+struct tqb_tq_cache {
+    tqb_pqo_cache* base = nullptr;
+    struct Q {
+        uint8_t* signs = nullptr;
+        uint16_t* norms = nullptr;
+        int64_t cap = 0;
+    };
+    std::vector<Q> qjl;
+    uint32_t* rbits = nullptr;
+    DevBuf deq, qf32, rq;
+
+    int sb() const { return base->cfg.head_dim / 8; }
+
+    void free_q(Q& q) {
+        if (q.signs) cudaFree(q.signs);
+        if (q.norms) cudaFree(q.norms);
+        q = Q{};
+    }
+
+    // ensure_qjl_capacity (src/cache/tq.rs:64-97)
+    int ensure_qjl_capacity(int layer, int64_t needed, int64_t old_len, cudaStream_t s) {
+        Q& q = qjl[layer];
+        if (q.cap >= needed) return TQB_OK;
+        const int64_t new_cap = needed + std::max<int64_t>(needed / 4, 128);
+        Q n;
+        n.cap = new_cap;
+        const int heads = base->heads;
+        cudaError_t e;
+        if ((e = cudaMalloc((void**)&n.signs, (size_t)heads * new_cap * sb())) != cudaSuccess ||
+            (e = cudaMalloc((void**)&n.norms, (size_t)heads * new_cap * 2)) != cudaSuccess) {
+            free_q(n);
+            return cuda_fail(e);
+        }
+        TQB_CUDA(cudaMemsetAsync(n.signs, 0, (size_t)heads * new_cap * sb(), s));
+        TQB_CUDA(cudaMemsetAsync(n.norms, 0, (size_t)heads * new_cap * 2, s));
+        if (old_len > 0 && q.signs) {
+            TQB_CUDA(cudaMemcpy2DAsync(n.signs, (size_t)new_cap * sb(), q.signs, (size_t)q.cap * sb(), (size_t)old_len * sb(),
+                                       heads, cudaMemcpyDeviceToDevice, s));
+            TQB_CUDA(cudaMemcpy2DAsync(n.norms, (size_t)new_cap * 2, q.norms, (size_t)q.cap * 2, (size_t)old_len * 2, heads,
+                                       cudaMemcpyDeviceToDevice, s));
+        }
+        if (q.signs) {
+            TQB_CUDA(cudaStreamSynchronize(s));
+            free_q(q);
+        }
+        q = n;
+        return TQB_OK;
+    }
+
+    // quantize_and_store + compute_and_store_qjl (src/cache/tq.rs:99-183)
+    int store(int layer, const void* k, const void* v, int dtype, int new_tokens, cudaStream_t s) {
+        const int64_t old_len = base->layers[layer].len;
+        TQB_TRY(base->quantize_and_store(layer, k, v, dtype, new_tokens, s));
+        TQB_TRY(ensure_qjl_capacity(layer, old_len + new_tokens, old_len, s));
+        auto& L = base->layers[layer];
+        const auto& cfg = base->cfg;
+        const int64_t rows = (int64_t)base->heads * new_tokens;
+        TQB_TRY(deq.reserve((size_t)rows * cfg.head_dim * sizeof(float)));
+        TQB_TRY(tqb_block_dequantize(cfg.bits, cfg.head_dim, cfg.norm_mode, cfg.outlier_blocks, L.ki, L.ks, rows, new_tokens,
+                                     L.cap, old_len, deq.p, TQB_F32, s));
+        return tqb_residual_sketch(cfg.head_dim, rbits, k, dtype, (const float*)deq.p, rows, qjl[layer].signs,
+                                   qjl[layer].norms, new_tokens, qjl[layer].cap, old_len, s);
+    }
+
+    // compute_logit_bias (src/cache/tq.rs:185-253)
+    int project(const void* q, int dtype, int num_q_heads, int q_len, cudaStream_t s) {
+        const long long nq = (long long)base->cfg.batch * num_q_heads * q_len;
+        const size_t bytes = (size_t)nq * base->cfg.head_dim * sizeof(float);
+        TQB_TRY(qf32.reserve(bytes));
+        TQB_TRY(rq.reserve(bytes));
+        TQB_TRY(convert_to_f32(q, dtype, (float*)qf32.p, nq * base->cfg.head_dim, s));
+        return tqb_qjl_query_projections(base->cfg.head_dim, rbits, (const float*)qf32.p, nq, (float*)rq.p, s);
+    }
+
+    int logit_bias(int layer, const void* q, int dtype, int num_q_heads, int q_len, void* bias, cudaStream_t s) {
+        auto& L = base->layers[layer];
+        if (L.len == 0) return TQB_OK;
+        TQB_TRY(project(q, dtype, num_q_heads, q_len, s));
+        return tqb_qjl_logit_bias(base->cfg.head_dim, (const float*)rq.p, qjl[layer].signs, qjl[layer].norms, bias, dtype,
+                                  base->cfg.batch * num_q_heads, base->heads, q_len, (int32_t)L.len, (int32_t)qjl[layer].cap, s);
+    }
+};
+
+extern "C" {
+
+int tqb_tq_cache_create(const tqb_cache_config* cfg, tqb_tq_cache** out) {
+    if (!cfg || !out) return TQB_ERR_NULL_POINTER;
+    *out = nullptr;
+    // the sign sketch spans the whole head_dim and needs a power of two of at least 32 here
+    if (cfg->head_dim != 32 && cfg->head_dim != 64 && cfg->head_dim != 128 && cfg->head_dim != 256)
+        return (cfg->head_dim > 0 && cfg->head_dim % kBlock == 0) ? TQB_ERR_UNSUPPORTED : TQB_ERR_INVALID_DIMENSION;
+    tqb_pqo_cache* base = nullptr;
+    TQB_TRY(tqb_pqo_cache_create(cfg, &base));
+    tqb_tq_cache* c = new (std::nothrow) tqb_tq_cache();
+    if (!c) { tqb_pqo_cache_destroy(base); return TQB_ERR_OUT_OF_MEMORY; }
+    c->base = base;
+    c->qjl.resize(cfg->num_layers);
+    std::vector<uint32_t> rb((size_t)cfg->head_dim * (cfg->head_dim / 32));
+    int st = tqb_qjl_rademacher_bits(cfg->head_dim, cfg->qjl_seed, rb.data());
+    if (st == TQB_OK) {
+        cudaError_t e = cudaMalloc((void**)&c->rbits, rb.size() * 4);
+        if (e == cudaSuccess) e = cudaMemcpy(c->rbits, rb.data(), rb.size() * 4, cudaMemcpyHostToDevice);
+        if (e != cudaSuccess) st = cuda_fail(e);
+    }
+    if (st != TQB_OK) { tqb_tq_cache_destroy(c); return st; }
+    *out = c;
+    return TQB_OK;
+}
+
+void tqb_tq_cache_destroy(tqb_tq_cache* c) {
+    if (!c) return;
+    for (auto& q : c->qjl) c->free_q(q);
+    if (c->rbits) cudaFree(c->rbits);
+    c->deq.release(); c->qf32.release(); c->rq.release();
+    tqb_pqo_cache_destroy(c->base);
+    delete c;
+}
+
+static int tq_check(const tqb_tq_cache* c, int32_t layer) {
+    if (!c) return TQB_ERR_NULL_POINTER;
+    return check_layer(c->base, layer);
+}
+
+int tqb_tq_cache_prefill(tqb_tq_cache* c, int32_t layer, const void* k, const void* v, const void* q, int32_t dtype,
+                         int32_t new_tokens, int32_t num_q_heads, int32_t q_len, void* k_out, void* v_out,
+                         void* logit_bias, tqb_stream_t stream) {
+    TQB_TRY(tq_check(c, layer));
+    if (new_tokens < 0 || q_len <= 0 || num_q_heads <= 0 || num_q_heads % c->base->cfg.num_kv_heads != 0)
+        return TQB_ERR_INVALID_ARGUMENT;
+    if (dtype != TQB_F32 && dtype != TQB_F16 && dtype != TQB_BF16) return TQB_ERR_INVALID_ARGUMENT;
+    if (!k || !v || !q || !logit_bias) return TQB_ERR_NULL_POINTER;
+    cudaStream_t s = as_stream(stream);
+    const int64_t old_len = c->base->layers[layer].len;
+    if (new_tokens > 0) TQB_TRY(c->store(layer, k, v, dtype, new_tokens, s));
+    // tq.rs:272-276: originals on the first call, else the dequantized cache
+    if (old_len > 0 && k_out && v_out) TQB_TRY(c->base->dequantize_full(layer, k_out, v_out, dtype, false, s));
+    return c->logit_bias(layer, q, dtype, num_q_heads, q_len, logit_bias, s);
+}
+
+int tqb_tq_cache_decode(tqb_tq_cache* c, int32_t layer, const void* k, const void* v, const void* q, int32_t dtype,
+                        int32_t num_q_heads, void* k_out, void* v_out, void* logit_bias, tqb_stream_t stream) {
+    TQB_TRY(tq_check(c, layer));
+    if (num_q_heads <= 0 || num_q_heads % c->base->cfg.num_kv_heads != 0) return TQB_ERR_INVALID_ARGUMENT;
+    if (dtype != TQB_F32 && dtype != TQB_F16 && dtype != TQB_BF16) return TQB_ERR_INVALID_ARGUMENT;
+    if (!k || !v || !q || !k_out || !v_out || !logit_bias) return TQB_ERR_NULL_POINTER;
+    cudaStream_t s = as_stream(stream);
+    TQB_TRY(c->store(layer, k, v, dtype, 1, s));
+    TQB_TRY(c->base->dequantize_full(layer, k_out, v_out, dtype, false, s));   // tq.rs:300-302
+    return c->logit_bias(layer, q, dtype, num_q_heads, 1, logit_bias, s);
+}
+
+int tqb_tq_cache_decode_fused(tqb_tq_cache* c, int32_t layer, const void* k, const void* v, const void* q, int32_t dtype,
+                              int32_t num_q_heads, float softmax_scale, void* out, tqb_stream_t stream) {
+    TQB_TRY(tq_check(c, layer));
+    if (num_q_heads <= 0 || num_q_heads % c->base->cfg.num_kv_heads != 0) return TQB_ERR_INVALID_ARGUMENT;
+    if (dtype != TQB_F32 && dtype != TQB_F16 && dtype != TQB_BF16) return TQB_ERR_INVALID_ARGUMENT;
+    if (!k || !v || !q || !out) return TQB_ERR_NULL_POINTER;
+    cudaStream_t s = as_stream(stream);
+    TQB_TRY(c->store(layer, k, v, dtype, 1, s));
+    TQB_TRY(c->project(q, dtype, num_q_heads, 1, s));
+    auto* b = c->base;
+    auto& L = b->layers[layer];
+    tqb_decode_params p{};
+    p.q = q;
+    p.k_indices = L.ki; p.k_scales = L.ks; p.v_indices = L.vi; p.v_scales = L.vs;
+    p.out = out;
+    p.qjl_signs = c->qjl[layer].signs; p.qjl_norms = c->qjl[layer].norms; p.rq = (const float*)c->rq.p;
+    p.qjl_enabled = 1;
+    p.q_dtype = dtype; p.out_dtype = dtype;
+    p.bits = b->cfg.bits; p.head_dim = b->cfg.head_dim; p.norm_mode = b->cfg.norm_mode; p.outlier_blocks = b->cfg.outlier_blocks;
+    p.num_q_heads = b->cfg.batch * num_q_heads;
+    p.num_kv_heads = b->heads;
+    p.kv_len = (int32_t)L.len;
+    p.kv_stride = (int32_t)L.cap;
+    if (c->qjl[layer].cap != L.cap) return TQB_ERR_UNSUPPORTED;   // both grow by the same rule; the kernel shares one stride
+    p.num_partitions = tqb_decode_num_partitions(b->heads, (int32_t)L.len);
+    p.softmax_scale = softmax_scale;
+    const size_t need = tqb_decode_scratch_bytes(p.num_q_heads, b->cfg.head_dim, p.num_partitions);
+    if (need > b->scratch.bytes) {
+        TQB_CUDA(cudaStreamSynchronize(s));
+        TQB_TRY(b->scratch.reserve(need + need / 4));
+    }
+    p.scratch = b->scratch.p;
+    p.scratch_bytes = b->scratch.bytes;
+    return tqb_decode_attention(&p, s);
+}
+
+int64_t tqb_tq_cache_seq_len(const tqb_tq_cache* c, int32_t layer) { return c ? tqb_pqo_cache_seq_len(c->base, layer) : -1; }
+
+int tqb_tq_cache_reset(tqb_tq_cache* c) {
+    if (!c) return TQB_ERR_NULL_POINTER;
+    TQB_TRY(tqb_pqo_cache_reset(c->base));
+    for (auto& q : c->qjl) c->free_q(q);   // tq.rs:316-324
+    return TQB_OK;
+}
+
+// tq.rs:322-331: stored tokens of the polar part plus the ALLOCATED sketch tensors
+size_t tqb_tq_cache_memory_usage(const tqb_tq_cache* c) {
+    if (!c) return 0;
+    size_t total = tqb_pqo_cache_memory_usage(c->base);
+    for (const auto& q : c->qjl)
+        if (q.signs) total += (size_t)c->base->heads * q.cap * (c->sb() + 2);
+    return total;
+}
+
+int tqb_tq_cache_qjl_ptrs(const tqb_tq_cache* c, int32_t layer, const uint8_t** signs, const uint16_t** norms,
+                          int64_t* capacity) {
+    TQB_TRY(tq_check(c, layer));
+    if (signs) *signs = c->qjl[layer].signs;
+    if (norms) *norms = c->qjl[layer].norms;
+    if (capacity) *capacity = c->qjl[layer].cap;
+    return TQB_OK;
+}
+
+}  // extern "C"

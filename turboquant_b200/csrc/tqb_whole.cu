@@ -371,6 +371,90 @@ __global__ void weighted_values_final_kernel(const float* __restrict__ partial, 
     for (int k = 0; k < EPL; ++k) out[lane + 32 * k] = (v[k] * inv_sqrt_d) * sign_of(seed, lane + 32 * k);
 }
 
+// compute_qjl_signs_and_norms of the block-32 TQ cache (src/cache/tq.rs:380-411): residual =
+// original - dequantized, its L2 norm (f16) and the head_dim-wide sign sketch, written at the
+// storage rows of CompressedStorage (row i -> (i / rows_per_group) * group_stride + row_offset
+// + i % rows_per_group).  One warp per tile of 32 vectors; sums are sequential as in the core crate.
+template <int EPL, typename T>
+__global__ void residual_sketch_kernel(const T* __restrict__ x, const float* __restrict__ xhat, long long n,
+                                       const uint32_t* __restrict__ rbits, uint8_t* __restrict__ signs,
+                                       uint16_t* __restrict__ norms, long long rows_per_group, long long group_stride,
+                                       long long row_offset, float inv_sqrt_d) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    constexpr int D = 32 * EPL, W = EPL;
+    uint32_t* s_rb = reinterpret_cast<uint32_t*>(smem_raw);
+    const int warps = blockDim.x >> 5, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float* tile = reinterpret_cast<float*>(s_rb + D * (W + 1)) + (size_t)warp * kTile * (D + 1);
+    for (int i = threadIdx.x; i < D * W; i += blockDim.x) s_rb[(i / W) * (W + 1) + (i % W)] = rbits[i];
+    __syncthreads();
+    const long long tiles = (n + kTile - 1) / kTile;
+    for (long long t = (long long)blockIdx.x * warps + warp; t < tiles; t += (long long)gridDim.x * warps) {
+        const long long v0 = t * kTile;
+        const int nv = (int)min((long long)kTile, n - v0);
+        for (int r = 0; r < nv; ++r)
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) {
+                const long long e = (v0 + r) * D + lane + 32 * i;
+                tile[r * (D + 1) + lane + 32 * i] = to_f32<T>(x[e]) - xhat[e];
+            }
+        __syncwarp();
+        long long orow = 0;
+        if (lane < nv) {
+            float s = 0.0f;
+            const float* row = tile + lane * (D + 1);
+#pragma unroll 8
+            for (int c = 0; c < D; ++c) s = s + row[c] * row[c];
+            const long long i = v0 + lane;
+            orow = i;
+            if (rows_per_group != 0) {
+                const long long g = i / rows_per_group;
+                orow = g * group_stride + row_offset + (i - g * rows_per_group);
+            }
+            norms[orow] = f32_to_f16_bits(__fsqrt_rn(s));
+        }
+        for (int r = 0; r < nv; ++r) {
+            float proj[EPL];
+            rademacher_rows<EPL>(tile + r * (D + 1), s_rb, lane, inv_sqrt_d, proj);
+            const long long dst = __shfl_sync(0xffffffffu, orow, r);
+#pragma unroll
+            for (int k = 0; k < EPL; ++k) {
+                const uint32_t word = __ballot_sync(0xffffffffu, proj[k] >= 0.0f);
+                if (lane == 0) reinterpret_cast<uint32_t*>(signs)[dst * W + k] = word;
+            }
+        }
+        __syncwarp();
+    }
+}
+
+// compute_logit_bias (src/cache/tq.rs:185-253): bias[h, i, t] = (sum_d rq[h, i, d] * (+-1)) * c_t with
+// c_t = norm_t * sqrt(pi/2) / sqrt(D).  One thread per token, the group's projected queries in shared memory.
+// rq: [hq, q_len, D]; signs: [hkv, stride, D/8]; norms: [hkv, stride]; bias: [hq, q_len, kv_len] of type OT.
+template <typename OT>
+__global__ void logit_bias_kernel(const float* __restrict__ rq, const uint8_t* __restrict__ signs,
+                                  const uint16_t* __restrict__ norms, OT* __restrict__ bias, int hq, int hkv, int q_len,
+                                  int D, int kv_len, int kv_stride, float scale_factor) {
+    extern __shared__ float s_rq[];   // [g * q_len][D]
+    const int kvh = blockIdx.y, g = hq / hkv;
+    const int rows = g * q_len;
+    for (int i = threadIdx.x; i < rows * D; i += blockDim.x) s_rq[i] = rq[(size_t)kvh * rows * D + i];
+    __syncthreads();
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= kv_len) return;
+    const size_t row = (size_t)kvh * kv_stride + t;
+    const uint32_t* sw = reinterpret_cast<const uint32_t*>(signs + row * (D / 8));
+    const float c = f16_bits_to_f32(norms[row]) * scale_factor;
+    for (int r = 0; r < rows; ++r) {
+        float acc = 0.0f;
+        for (int w = 0; w < D / 32; ++w) {
+            const uint32_t bits = sw[w];
+#pragma unroll 8
+            for (int b = 0; b < 32; ++b) acc = fmaf(s_rq[r * D + w * 32 + b], ((bits >> b) & 1u) ? 1.0f : -1.0f, acc);
+        }
+        const int head = kvh * g + r / q_len, qi = r % q_len;
+        bias[((size_t)head * q_len + qi) * kv_len + t] = from_f32<OT>(acc * c);
+    }
+}
+
 size_t quant_smem(int dim, int pb, int warps, bool qjl) {
     const int W = dim / 32;
     size_t per_warp = sizeof(float) * kTile * (dim + 1) + dim + (size_t)kTile * pb;
@@ -566,6 +650,74 @@ int tqb_weighted_values(const tqb_config* cfg, const float* w, const uint8_t* pa
         weighted_values_partial_kernel<EPL><<<nparts, 256, 0, s>>>(w, packed, scales, n, partial, cb, polar.bits, pb);
         weighted_values_final_kernel<EPL><<<1, 32, 0, s>>>(partial, nparts, out, cfg->rotation_seed, host_inv_sqrt(cfg->dim));
     });
+    return check_launch(s);
+}
+
+}  // extern "C"
+
+extern "C" {
+
+int tqb_residual_sketch(int32_t dim, const uint32_t* rbits, const void* original, int32_t dtype,
+                        const float* dequantized, int64_t n, uint8_t* signs, uint16_t* norms, int64_t rows_per_group,
+                        int64_t out_group_stride, int64_t out_row_offset, tqb_stream_t stream) {
+    if (dim != 32 && dim != 64 && dim != 128 && dim != 256)
+        return (dim > 0 && dim % 32 == 0) ? TQB_ERR_UNSUPPORTED : TQB_ERR_INVALID_DIMENSION;
+    if (n < 0 || rows_per_group < 0) return TQB_ERR_INVALID_ARGUMENT;
+    if (n == 0) return TQB_OK;
+    if (!rbits || !original || !dequantized || !signs || !norms) return TQB_ERR_NULL_POINTER;
+    if ((uintptr_t)signs % 4) return TQB_ERR_MISALIGNED;
+    if (dtype != TQB_F32 && dtype != TQB_F16 && dtype != TQB_BF16) return TQB_ERR_INVALID_ARGUMENT;
+    cudaStream_t s = as_stream(stream);
+    const int W = dim / 32, warps = dim >= 256 ? 2 : 4;
+    const size_t smem = sizeof(uint32_t) * dim * (W + 1) + sizeof(float) * warps * kTile * (dim + 1);
+    const long long tiles = (n + kTile - 1) / kTile;
+    long long grid = (tiles + warps - 1) / warps;
+    if (grid > 148 * 8) grid = 148 * 8;
+    const float inv = host_inv_sqrt(dim);
+#define TQB_SKETCH(T)                                                                                            \
+    do { TQB_DISPATCH_EPL(dim, {                                                                                 \
+        cudaError_t e = cudaFuncSetAttribute(residual_sketch_kernel<EPL, T>,                                      \
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);            \
+        if (e != cudaSuccess) { set_cuda_error(e); return TQB_ERR_CUDA; }                                        \
+        residual_sketch_kernel<EPL, T><<<(int)grid, warps * 32, smem, s>>>(                                       \
+            (const T*)original, dequantized, n, rbits, signs, norms, rows_per_group, out_group_stride,           \
+            out_row_offset, inv);                                                                                \
+    }) } while (0)
+    if (dtype == TQB_F32) TQB_SKETCH(float);
+    else if (dtype == TQB_F16) TQB_SKETCH(__half);
+    else TQB_SKETCH(__nv_bfloat16);
+#undef TQB_SKETCH
+    return check_launch(s);
+}
+
+int tqb_qjl_logit_bias(int32_t head_dim, const float* rq, const uint8_t* signs, const uint16_t* norms, void* bias,
+                       int32_t bias_dtype, int32_t num_q_heads, int32_t num_kv_heads, int32_t q_len, int32_t kv_len,
+                       int32_t kv_stride, tqb_stream_t stream) {
+    if (head_dim <= 0 || head_dim % 32 != 0) return TQB_ERR_INVALID_DIMENSION;
+    if (num_q_heads <= 0 || num_kv_heads <= 0 || num_q_heads % num_kv_heads != 0 || q_len <= 0) return TQB_ERR_INVALID_ARGUMENT;
+    if (kv_len < 0 || kv_len > kv_stride) return TQB_ERR_RANGE_OUT_OF_BOUNDS;
+    if (kv_len == 0) return TQB_OK;
+    if (!rq || !signs || !norms || !bias) return TQB_ERR_NULL_POINTER;
+    if ((uintptr_t)signs % 4) return TQB_ERR_MISALIGNED;
+    const int g = num_q_heads / num_kv_heads;
+    const size_t smem = sizeof(float) * (size_t)g * q_len * head_dim;
+    if (smem > 200 * 1024) return TQB_ERR_TOO_LARGE;
+    // src/cache/tq.rs:215-216: sqrt(pi/2) as f32 divided by sqrt(head_dim) in f32
+    const float scale_factor = (float)sqrt(1.5707963267948966) / sqrtf((float)head_dim);
+    cudaStream_t s = as_stream(stream);
+    dim3 grid((kv_len + 127) / 128, num_kv_heads);
+#define TQB_BIAS(OT)                                                                                                   \
+    do {                                                                                                               \
+        cudaError_t e = cudaFuncSetAttribute(logit_bias_kernel<OT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        if (e != cudaSuccess) { set_cuda_error(e); return TQB_ERR_CUDA; }                                              \
+        logit_bias_kernel<OT><<<grid, 128, smem, s>>>(rq, signs, norms, (OT*)bias, num_q_heads, num_kv_heads, q_len,   \
+                                                      head_dim, kv_len, kv_stride, scale_factor);                      \
+    } while (0)
+    if (bias_dtype == TQB_F32) TQB_BIAS(float);
+    else if (bias_dtype == TQB_F16) TQB_BIAS(__half);
+    else if (bias_dtype == TQB_BF16) TQB_BIAS(__nv_bfloat16);
+    else return TQB_ERR_INVALID_ARGUMENT;
+#undef TQB_BIAS
     return check_launch(s);
 }
 
