@@ -175,7 +175,7 @@ def run_ours(args):
     def step_host(i):
         for layer in range(L):
             cache.decode(layer, hk[i % 4], hv[i % 4], hq_[(i + layer) % 4], att, out=hout[layer])
-        torch.cuda.current_stream().synchronize()   # the step's result is on the host
+        cache.host_sync()   # the step's results are on the host
 
     for i in range(args.warmup):
         step_host(i)
@@ -189,8 +189,8 @@ def run_ours(args):
     barrier()
     e2e_ms = f0.elapsed_time(f1)
     e2e_bytes = bytes_of_steps(len1, args.steps)
-    h2d = L * (2 * B * HKV * D + B * HQ * D) * 2
-    d2h = L * B * HQ * D * 2
+    h2d = world * L * (2 * B * HKV * D + B * HQ * D) * 2    # whole job, like the value
+    d2h = world * L * B * HQ * D * 2
 
     # ---- roofline: the decode kernel alone, one event pair per launch ----
     kv_len = cache.seq_len(0)

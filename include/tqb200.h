@@ -307,6 +307,10 @@ int tqb_pqo_cache_prefill(tqb_pqo_cache *c, int32_t layer, const void *k, const 
 int tqb_pqo_cache_decode(tqb_pqo_cache *c, int32_t layer, const void *k, const void *v, const void *q,
                          int32_t dtype, int32_t num_q_heads, float softmax_scale, void *out,
                          int32_t host_buffers, tqb_stream_t stream);
+/* With host_buffers != 0, tqb_pqo_cache_decode moves data on an internal copy stream so that copies overlap
+ * kernels of neighbouring calls; the host `out` buffers are complete once this call returns (it blocks the
+ * calling thread on the last outstanding result copy). */
+int tqb_pqo_cache_host_sync(tqb_pqo_cache *c);
 /* dequantize_full (pqo.rs:176-180): [batch, num_kv_heads, seq_len, head_dim] of `dtype`. */
 int tqb_pqo_cache_dequantize_full(tqb_pqo_cache *c, int32_t layer, void *k_out, void *v_out, int32_t dtype,
                                   int32_t host_buffers, tqb_stream_t stream);

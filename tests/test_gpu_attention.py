@@ -295,7 +295,7 @@ def test_pqo_cache_growth_batch_and_host_buffers():
     q = (torch.randn((3, 8, 1, 128), generator=g) / 128 ** 0.5).bfloat16()
     out_host = torch.empty_like(q).pin_memory()
     cache.decode(0, k1.pin_memory(), v1.pin_memory(), q.pin_memory(), tq.AttendConfig(0.0884, 4), out=out_host)
-    torch.cuda.synchronize()
+    cache.host_sync()
     allk, allv = torch.cat([allk, k1], dim=2), torch.cat([allv, v1], dim=2)
     kp, ksc = o.block_quantize(4, 128, 0, -1, allk.float().numpy().reshape(-1, 128), nthreads=8)
     vp, vsc = o.block_quantize(4, 128, 0, -1, allv.float().numpy().reshape(-1, 128), nthreads=8)

@@ -624,6 +624,10 @@ class PqoCache:
                                        config.softmax_scale, _ptr(out), self._host(k), _stream()))
         return DecodeOutput(fused=out)
 
+    def host_sync(self):
+        """Blocks until the results of earlier decode() calls with host tensors have reached the host."""
+        check(lib.tqb_pqo_cache_host_sync(self._h))
+
     def attend_partial(self, layer, q, softmax_scale):
         """Shard-local result for sequence-parallel decode: (un-normalised out [B*Hq, D] f32, lse [B*Hq, 2])."""
         q = q.contiguous()

@@ -66,6 +66,40 @@ struct tqb_pqo_cache {
     };
     std::vector<Layer> layers;
     DevBuf stage_k, stage_v, stage_q, stage_out, scratch;
+    // Host-buffer decode: two staging slots and a copy stream, so that the host->device copies of
+    // one call and the device->host copy of the previous call overlap with kernels.
+    struct Slot {
+        DevBuf k, v, q, out;
+        cudaEvent_t in_ready = nullptr, compute_done = nullptr, out_done = nullptr;
+    };
+    Slot slots[2];
+    int next_slot = 0;
+    cudaStream_t copy_stream = nullptr;   // host -> device
+    cudaStream_t down_stream = nullptr;   // device -> host
+    cudaEvent_t last_out = nullptr;   // completion of the most recent device->host output copy
+
+    int ensure_pipeline() {
+        if (copy_stream) return TQB_OK;
+        TQB_CUDA(cudaStreamCreateWithFlags(&copy_stream, cudaStreamNonBlocking));
+        TQB_CUDA(cudaStreamCreateWithFlags(&down_stream, cudaStreamNonBlocking));
+        for (auto& sl : slots) {
+            TQB_CUDA(cudaEventCreateWithFlags(&sl.in_ready, cudaEventDisableTiming));
+            TQB_CUDA(cudaEventCreateWithFlags(&sl.compute_done, cudaEventDisableTiming));
+            TQB_CUDA(cudaEventCreateWithFlags(&sl.out_done, cudaEventDisableTiming));
+        }
+        return TQB_OK;
+    }
+    void destroy_pipeline() {
+        for (auto& sl : slots) {
+            sl.k.release(); sl.v.release(); sl.q.release(); sl.out.release();
+            if (sl.in_ready) cudaEventDestroy(sl.in_ready);
+            if (sl.compute_done) cudaEventDestroy(sl.compute_done);
+            if (sl.out_done) cudaEventDestroy(sl.out_done);
+        }
+        if (copy_stream) cudaStreamDestroy(copy_stream);
+        if (down_stream) cudaStreamDestroy(down_stream);
+        copy_stream = down_stream = nullptr;
+    }
 
     void free_layer(Layer& l) {
         if (l.ki) cudaFree(l.ki);
@@ -211,6 +245,7 @@ void tqb_pqo_cache_destroy(tqb_pqo_cache* c) {
     if (!c) return;
     for (auto& l : c->layers) c->free_layer(l);
     c->stage_k.release(); c->stage_v.release(); c->stage_q.release(); c->stage_out.release(); c->scratch.release();
+    c->destroy_pipeline();
     delete c;
 }
 
@@ -257,23 +292,45 @@ int tqb_pqo_cache_decode(tqb_pqo_cache* c, int32_t layer, const void* k, const v
     const size_t esz = dtype_size(dtype);
     const size_t kv_bytes = (size_t)c->heads * c->cfg.head_dim * esz;
     const size_t q_bytes = (size_t)c->cfg.batch * num_q_heads * c->cfg.head_dim * esz;
-    const void* kd = k;
-    const void* vd = v;
-    const void* qd = q;
-    void* od = out;
-    if (host_buffers) {
-        TQB_TRY(c->stage_k.reserve(kv_bytes));
-        TQB_TRY(c->stage_v.reserve(kv_bytes));
-        TQB_TRY(c->stage_q.reserve(q_bytes));
-        TQB_TRY(c->stage_out.reserve(q_bytes));
-        TQB_CUDA(cudaMemcpyAsync(c->stage_k.p, k, kv_bytes, cudaMemcpyHostToDevice, s));
-        TQB_CUDA(cudaMemcpyAsync(c->stage_v.p, v, kv_bytes, cudaMemcpyHostToDevice, s));
-        TQB_CUDA(cudaMemcpyAsync(c->stage_q.p, q, q_bytes, cudaMemcpyHostToDevice, s));
-        kd = c->stage_k.p; vd = c->stage_v.p; qd = c->stage_q.p; od = c->stage_out.p;
+    if (!host_buffers) {
+        TQB_TRY(c->quantize_and_store(layer, k, v, dtype, 1, s));
+        return c->attend(layer, q, dtype, num_q_heads, softmax_scale, out, dtype, nullptr, s);
     }
-    TQB_TRY(c->quantize_and_store(layer, kd, vd, dtype, 1, s));
-    TQB_TRY(c->attend(layer, qd, dtype, num_q_heads, softmax_scale, od, dtype, nullptr, s));
-    if (host_buffers) TQB_CUDA(cudaMemcpyAsync(out, od, q_bytes, cudaMemcpyDeviceToHost, s));
+    // Host buffers: inputs go up on one copy stream into one of two staging slots, the kernels run on
+    // the caller's stream once the slot is filled, and the result goes down on a second copy stream
+    // once they are done, so the next call's inputs travel while this call's kernels run.  A slot is
+    // refilled only after the kernels that read it are done, and its output is overwritten only after
+    // the previous result has left it.  tqb_pqo_cache_host_sync() waits for the outstanding results.
+    TQB_TRY(c->ensure_pipeline());
+    tqb_pqo_cache::Slot& sl = c->slots[c->next_slot];
+    c->next_slot ^= 1;
+    const bool used = sl.k.p != nullptr;
+    TQB_TRY(sl.k.reserve(kv_bytes));
+    TQB_TRY(sl.v.reserve(kv_bytes));
+    TQB_TRY(sl.q.reserve(q_bytes));
+    TQB_TRY(sl.out.reserve(q_bytes));
+    if (used) {
+        TQB_CUDA(cudaStreamWaitEvent(c->copy_stream, sl.compute_done, 0));
+        TQB_CUDA(cudaStreamWaitEvent(s, sl.out_done, 0));
+    }
+    TQB_CUDA(cudaMemcpyAsync(sl.k.p, k, kv_bytes, cudaMemcpyHostToDevice, c->copy_stream));
+    TQB_CUDA(cudaMemcpyAsync(sl.v.p, v, kv_bytes, cudaMemcpyHostToDevice, c->copy_stream));
+    TQB_CUDA(cudaMemcpyAsync(sl.q.p, q, q_bytes, cudaMemcpyHostToDevice, c->copy_stream));
+    TQB_CUDA(cudaEventRecord(sl.in_ready, c->copy_stream));
+    TQB_CUDA(cudaStreamWaitEvent(s, sl.in_ready, 0));
+    TQB_TRY(c->quantize_and_store(layer, sl.k.p, sl.v.p, dtype, 1, s));
+    TQB_TRY(c->attend(layer, sl.q.p, dtype, num_q_heads, softmax_scale, sl.out.p, dtype, nullptr, s));
+    TQB_CUDA(cudaEventRecord(sl.compute_done, s));
+    TQB_CUDA(cudaStreamWaitEvent(c->down_stream, sl.compute_done, 0));
+    TQB_CUDA(cudaMemcpyAsync(out, sl.out.p, q_bytes, cudaMemcpyDeviceToHost, c->down_stream));
+    TQB_CUDA(cudaEventRecord(sl.out_done, c->down_stream));
+    c->last_out = sl.out_done;
+    return TQB_OK;
+}
+
+int tqb_pqo_cache_host_sync(tqb_pqo_cache* c) {
+    if (!c) return TQB_ERR_NULL_POINTER;
+    if (c->last_out) TQB_CUDA(cudaEventSynchronize(c->last_out));
     return TQB_OK;
 }
 
