@@ -87,18 +87,21 @@ __device__ __forceinline__ float ex2(float x) {
 __device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
 __device__ __forceinline__ __half2 u32_as_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
 
-// Eight 4-bit codes of one word -> four half2 registers holding the exact integers code - 8:
+// Eight 4-bit codes of one word -> four half2 registers holding the exact values code - 7.5:
 //   x[0] = (c0, c4), x[1] = (c1, c5), x[2] = (c2, c6), x[3] = (c3, c7).
+// A nibble moved to mantissa bits 1..4 of 0x6400 reads 1024 + 2c, at bits 5..8 it reads 1024 + 32c;
+// one HFMA2 with constants that f16 holds exactly (0.5, -519.5 | 1/32, -39.5) turns either into c - 7.5.
 __device__ __forceinline__ void nibbles_to_half2(uint32_t w, uint32_t (&x)[4]) {
     const uint32_t kMagic = 0x64006400u;                       // half2(1024, 1024)
-    const __half2 k1032 = u32_as_h2(0x64086408u);              // 1024 + 8
-    const __half2 kSixteenth = u32_as_h2(0x2C002C00u);         // 1/16
-    const __half2 kM72 = u32_as_h2(0xD480D480u);               // -(1024/16 + 8)
-    const uint32_t w8 = w >> 8;
-    x[0] = h2_as_u32(__hsub2(u32_as_h2(lop3_and_or(w, 0x000f000fu, kMagic)), k1032));
-    x[1] = h2_as_u32(__hfma2(u32_as_h2(lop3_and_or(w, 0x00f000f0u, kMagic)), kSixteenth, kM72));
-    x[2] = h2_as_u32(__hsub2(u32_as_h2(lop3_and_or(w8, 0x000f000fu, kMagic)), k1032));
-    x[3] = h2_as_u32(__hfma2(u32_as_h2(lop3_and_or(w8, 0x00f000f0u, kMagic)), kSixteenth, kM72));
+    const __half2 kHalf = u32_as_h2(0x38003800u);              // 0.5
+    const __half2 kM519 = u32_as_h2(0xE00FE00Fu);              // -519.5
+    const __half2 k32nd = u32_as_h2(0x28002800u);              // 1/32
+    const __half2 kM39 = u32_as_h2(0xD0F0D0F0u);               // -39.5
+    const uint32_t w1 = w << 1, w7 = w >> 7;
+    x[0] = h2_as_u32(__hfma2(u32_as_h2(lop3_and_or(w1, 0x001e001eu, kMagic)), kHalf, kM519));
+    x[1] = h2_as_u32(__hfma2(u32_as_h2(lop3_and_or(w1, 0x01e001e0u, kMagic)), k32nd, kM39));
+    x[2] = h2_as_u32(__hfma2(u32_as_h2(lop3_and_or(w7, 0x001e001eu, kMagic)), kHalf, kM519));
+    x[3] = h2_as_u32(__hfma2(u32_as_h2(lop3_and_or(w7, 0x01e001e0u, kMagic)), k32nd, kM39));
 }
 
 __device__ __forceinline__ uint32_t pack_hi(float a, float b) { return h2_as_u32(__floats2half2_rn(a, b)); }
@@ -146,6 +149,18 @@ __device__ __forceinline__ uint2 lds64(uint32_t addr) {
     uint2 v;
     asm("ld.shared.v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(addr) : "memory");
     return v;
+}
+
+// Four 8x8 matrices of 16-bit elements; lane l supplies the address of row l & 7 of matrix l >> 3.
+// Plain: lane (n, j) receives elements 2j, 2j+1 of row n (one 32-bit word).  Transposed: it receives
+// element n of rows 2j and 2j+1.
+__device__ __forceinline__ void ldsm4(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr) : "memory");
+}
+__device__ __forceinline__ void ldsm4t(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr) : "memory");
 }
 
 template <int BITS>
@@ -237,7 +252,6 @@ __global__ void __launch_bounds__(kThreads, 3) decode_mma_kernel(MmaArgs a) {
     float (*s_o)[8][kD] = reinterpret_cast<float (*)[8][kD]>(s_raw);                 // [kWarps][8][128]
     float (*s_m)[8] = reinterpret_cast<float (*)[8]>(s_raw + kWarps * 8 * kD * 4);   // [kWarps][8]
     float (*s_l)[8] = s_m + kWarps;
-    float (*s_z)[8][4] = reinterpret_cast<float (*)[8][4]>(s_l + kWarps);
     static_assert(kWarps * G::kRingB >= kWarps * 8 * kD * 4 + kWarps * 8 * 4 * 2 + kWarps * 8 * 4 * 4, "ring too small");
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -268,11 +282,14 @@ __global__ void __launch_bounds__(kThreads, 3) decode_mma_kernel(MmaArgs a) {
     uint32_t koff[4], voff[4];
     uint32_t khi = 0, vhi = 0, ksh = 0, vsh = 0;   // 3-bit: distance to the second word, funnel shifts
     if (BITS == 4) {
-#pragma unroll
-        for (int b = 0; b < 4; ++b) {
-            koff[b] = n * 64 + ((b ^ ((n >> 1) & 3)) << 4) + j * 4;             // token n (+8o: +512), word j of block b
-            voff[b] = G::kIdxB + (2 * j) * 64 + ((b ^ j) << 4) + (n >> 1) * 4;  // token 2j (+e: +64, +8o: +512), word n/2
-        }
+        // ldmatrix row addresses: lane l supplies row l & 7 of matrix l >> 3.  Matrix m covers the token
+        // octet m & 1 and the block 2 * pair + (m >> 1); a row is the 16-byte piece of one token.
+        const int tok = 8 * ((lane >> 3) & 1) + (lane & 7), blk = lane >> 4;
+        koff[0] = tok * 64 + ((blk ^ ((tok >> 1) & 3)) << 4);
+        koff[1] = koff[0] ^ 32;                      // blocks 2, 3: piece index ^ 2
+        voff[0] = G::kIdxB + koff[0];
+        voff[1] = G::kIdxB + koff[1];
+        koff[2] = koff[3] = voff[2] = voff[3] = 0;
     } else {
         // K: the 24 bits at byte 3j of block b;  V: the 12 bits at bit 12n of block b
         const int kw0 = (3 * j) >> 2;
@@ -290,7 +307,6 @@ __global__ void __launch_bounds__(kThreads, 3) decode_mma_kernel(MmaArgs a) {
     constexpr uint32_t kOct = 8 * G::kRowB;                                     // 8 token rows
     constexpr uint32_t kRow = G::kRowB;
     const uint32_t scoff = 2 * G::kIdxB + (2 * j) * 8;                          // scales of token 2j (+e: +8, +8o: +64)
-    const uint32_t vsel = (n & 1) ? 0x7632u : 0x5410u;
     const uint32_t lut_base = BITS == 3 ? (((uint32_t)__cvta_generic_to_shared(s_dyn) + 8191u) & ~8191u) : 0u;
     const uint32_t lut = lut_base + lane * 4;
 
@@ -319,16 +335,15 @@ __global__ void __launch_bounds__(kThreads, 3) decode_mma_kernel(MmaArgs a) {
         }
     }
     __syncthreads();
-    // A fragments: rows 0..7 = hi(q~) of head n, rows 8..15 = lo(q~) of head n.  For block b and
-    // half m the k-slots (2j, 2j+1 | 2j+8, 2j+9) hold the dims that the code unpackers deliver:
+    // A fragments: rows 0..7 = hi(q~) of head n, rows 8..15 = lo(q~) of head n (NSPLIT: head n & 3, so
+    // lanes n and n + 4 compute the same scores and need no exchange later).  For block b and half m
+    // the k-slots (2j, 2j+1 | 2j+8, 2j+9) hold the dims that the code unpackers deliver:
     //   4-bit: 32b + 8j + 2m + (0, 4 | 1, 5)      3-bit: 32b + 8j + 4m + (0, 1 | 2, 3)
     uint32_t afr[4][2][4];
-    float qbar[4];
     {
-        const float* sq = s_q + n * kD;
+        const float* sq = s_q + (NSPLIT ? (n & 3) : n) * kD;
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
-            float s = 0.0f;
 #pragma unroll
             for (int m = 0; m < 2; ++m) {
                 const int d0 = 32 * b + 8 * j + (BITS == 4 ? 2 * m : 4 * m);
@@ -338,16 +353,12 @@ __global__ void __launch_bounds__(kThreads, 3) decode_mma_kernel(MmaArgs a) {
                 afr[b][m][1] = pack_lo(qa, qb);
                 afr[b][m][2] = pack_hi(qc, qd);
                 afr[b][m][3] = pack_lo(qc, qd);
-                s += (qa + qb) + (qc + qd);
             }
-            s += __shfl_xor_sync(0xffffffffu, s, 1);
-            s += __shfl_xor_sync(0xffffffffu, s, 2);
-            qbar[b] = BITS == 4 ? 0.5f * s : 0.0f;   // 4-bit: the +0.5 of (i - 7.5) = (i - 8) + 0.5, summed over the block
         }
     }
+    const bool lo_lane = NSPLIT && n >= 4;   // NSPLIT: this lane's MMA column carries the lo part of P'
 
     float m_run = kNegBig, l_run = 0.0f;
-    float z[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     float o[4][2][4];
 #pragma unroll
     for (int b = 0; b < 4; ++b)
@@ -366,6 +377,11 @@ __global__ void __launch_bounds__(kThreads, 3) decode_mma_kernel(MmaArgs a) {
         __syncwarp();
 
         // ---- S^T = Q~ K^T ----
+        uint32_t kw[2][4];   // 4-bit: [block pair][octet | block parity << 1] -> word j of token n of the octet
+        if (BITS == 4) {
+            ldsm4(st + koff[0], kw[0]);
+            ldsm4(st + koff[1], kw[1]);
+        }
         float s[2][2];
 #pragma unroll
         for (int o8 = 0; o8 < 2; ++o8) {
@@ -376,7 +392,7 @@ __global__ void __launch_bounds__(kThreads, 3) decode_mma_kernel(MmaArgs a) {
             for (int b = 0; b < 4; ++b) {
                 uint32_t x[4];
                 if (BITS == 4) {
-                    nibbles_to_half2(lds32(st + koff[b] + o8 * kOct), x);
+                    nibbles_to_half2(kw[b >> 1][o8 + 2 * (b & 1)], x);
                 } else {
                     const uint32_t lo = lds32(st + koff[b] + o8 * kOct), hi = lds32(st + koff[b] + o8 * kOct + khi);
                     const uint32_t w = __funnelshift_r(lo, hi, ksh);          // codes 8j..8j+7 in bits 0..23
@@ -385,7 +401,7 @@ __global__ void __launch_bounds__(kThreads, 3) decode_mma_kernel(MmaArgs a) {
                     x[2] = lds32(lop3_and_or(w >> 5, 0x1F80u, lut));
                     x[3] = lds32(lop3_and_or(w >> 11, 0x1F80u, lut));
                 }
-                float acc[4] = {qbar[b], qbar[b], 0.0f, 0.0f};
+                float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
                 mma16816(acc, afr[b][0][0], afr[b][0][1], afr[b][0][2], afr[b][0][3], x[0], x[1]);
                 mma16816(acc, afr[b][1][0], afr[b][1][1], afr[b][1][2], afr[b][1][3], x[2], x[3]);
                 const __half2 p0 = u32_as_h2(b < 2 ? sc0.x : sc0.y), p1 = u32_as_h2(b < 2 ? sc1.x : sc1.y);
@@ -421,45 +437,52 @@ __global__ void __launch_bounds__(kThreads, 3) decode_mma_kernel(MmaArgs a) {
             const float r0 = __shfl_sync(0xffffffffu, resc, 4 * h0);
             const float r1 = __shfl_sync(0xffffffffu, resc, 4 * h1);
 #pragma unroll
-            for (int b = 0; b < 4; ++b) {
-                z[b] *= resc;
+            for (int b = 0; b < 4; ++b)
 #pragma unroll
                 for (int m = 0; m < 2; ++m) {
                     o[b][m][0] *= r0; o[b][m][1] *= r1; o[b][m][2] *= r0; o[b][m][3] *= r1;
                 }
-            }
         }
-        if (NSPLIT) {
-            // lanes of rows 4..7 take over the probabilities of heads 0..3 and will supply the lo parts
+        // ---- P' = p |s_v| as an exact f16 pair, in half2 arithmetic ----
+        // p = ph + pl (f16 each).  hi = rn(ph s) and ph s - hi are both f16 values (the product of two
+        // 11-bit significands has 22 bits), so hi + lo with lo = fma(pl, s, fma(ph, s, -hi)) equals p s
+        // up to 2^-22 relative.
+        __half2 ph[2], pl[2];
 #pragma unroll
-            for (int o8 = 0; o8 < 2; ++o8)
+        for (int o8 = 0; o8 < 2; ++o8) {
+            ph[o8] = u32_as_h2(pack_hi(p[o8][0], p[o8][1]));
+            pl[o8] = u32_as_h2(pack_lo(p[o8][0], p[o8][1]));
+        }
+        __half2 sv[2][4];   // |scale| of (token 2j, token 2j+1) of the octet, per block
 #pragma unroll
-                for (int e = 0; e < 2; ++e) p[o8][e] = __shfl_sync(0xffffffffu, p[o8][e], lane & 15);
+        for (int o8 = 0; o8 < 2; ++o8) {
+            const uint2 va = lds64(st + 128 + scoff + o8 * 64), vb = lds64(st + 128 + scoff + o8 * 64 + 8);
+            sv[o8][0] = u32_as_h2(__byte_perm(va.x, vb.x, 0x5410) & 0x7FFF7FFFu);
+            sv[o8][1] = u32_as_h2(__byte_perm(va.x, vb.x, 0x7632) & 0x7FFF7FFFu);
+            sv[o8][2] = u32_as_h2(__byte_perm(va.y, vb.y, 0x5410) & 0x7FFF7FFFu);
+            sv[o8][3] = u32_as_h2(__byte_perm(va.y, vb.y, 0x7632) & 0x7FFF7FFFu);
         }
         // ---- O^T += V^T P' ----
-        uint2 vs[2][2];
-#pragma unroll
-        for (int o8 = 0; o8 < 2; ++o8)
-#pragma unroll
-            for (int e = 0; e < 2; ++e) vs[o8][e] = lds64(st + 128 + scoff + o8 * 64 + e * 8);
+        uint32_t vw[2][4];   // 4-bit: codes 4n..4n+3 of (token 2j | token 2j+1 << 16), indexed like kw
+        if (BITS == 4) {
+            ldsm4t(st + voff[0], vw[0]);
+            ldsm4t(st + voff[1], vw[1]);
+        }
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
-            float pf[2][2];
+            uint32_t bh[2], bl[2];
 #pragma unroll
-            for (int o8 = 0; o8 < 2; ++o8)
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const __half2 pr = u32_as_h2(b < 2 ? vs[o8][e].x : vs[o8][e].y);
-                    pf[o8][e] = p[o8][e] * fabsf((b & 1) ? __high2float(pr) : __low2float(pr));
-                }
-            if (BITS == 4) z[b] += (pf[0][0] + pf[0][1]) + (pf[1][0] + pf[1][1]);
-            const uint32_t b0h = pack_hi(pf[0][0], pf[0][1]), b1h = pack_hi(pf[1][0], pf[1][1]);
-            const uint32_t b0l = pack_lo(pf[0][0], pf[0][1]), b1l = pack_lo(pf[1][0], pf[1][1]);
+            for (int o8 = 0; o8 < 2; ++o8) {
+                const __half2 hi = __hmul2(ph[o8], sv[o8][b]);
+                const __half2 lo = __hfma2(pl[o8], sv[o8][b], __hfma2(ph[o8], sv[o8][b], __hneg2(hi)));
+                bh[o8] = h2_as_u32(hi);
+                bl[o8] = h2_as_u32(lo);
+            }
             // codes 4n..4n+3 of block b of the four tokens, paired (token 2j, token 2j+1)
             uint32_t xab[4], xcd[4];
             if (BITS == 4) {
-                nibbles_to_half2(__byte_perm(lds32(st + voff[b]), lds32(st + voff[b] + kRow), vsel), xab);
-                nibbles_to_half2(__byte_perm(lds32(st + voff[b] + kOct), lds32(st + voff[b] + kOct + kRow), vsel), xcd);
+                nibbles_to_half2(vw[b >> 1][2 * (b & 1)], xab);
+                nibbles_to_half2(vw[b >> 1][2 * (b & 1) + 1], xcd);
             } else {
 #pragma unroll
                 for (int o8 = 0; o8 < 2; ++o8) {
@@ -477,14 +500,14 @@ __global__ void __launch_bounds__(kThreads, 3) decode_mma_kernel(MmaArgs a) {
                 }
             }
             if (NSPLIT) {
-                const uint32_t b0 = n < 4 ? b0h : b0l, b1 = n < 4 ? b1h : b1l;
+                const uint32_t b0 = lo_lane ? bl[0] : bh[0], b1 = lo_lane ? bl[1] : bh[1];
                 mma16816(o[b][0], xab[0], xab[1], xcd[0], xcd[1], b0, b1);
                 mma16816(o[b][1], xab[2], xab[3], xcd[2], xcd[3], b0, b1);
             } else {
-                mma16816(o[b][0], xab[0], xab[1], xcd[0], xcd[1], b0h, b1h);
-                mma16816(o[b][0], xab[0], xab[1], xcd[0], xcd[1], b0l, b1l);
-                mma16816(o[b][1], xab[2], xab[3], xcd[2], xcd[3], b0h, b1h);
-                mma16816(o[b][1], xab[2], xab[3], xcd[2], xcd[3], b0l, b1l);
+                mma16816(o[b][0], xab[0], xab[1], xcd[0], xcd[1], bh[0], bh[1]);
+                mma16816(o[b][0], xab[0], xab[1], xcd[0], xcd[1], bl[0], bl[1]);
+                mma16816(o[b][1], xab[2], xab[3], xcd[2], xcd[3], bh[0], bh[1]);
+                mma16816(o[b][1], xab[2], xab[3], xcd[2], xcd[3], bl[0], bl[1]);
             }
         }
         __syncwarp();   // every lane is done with this stage before it is refilled
@@ -496,16 +519,9 @@ __global__ void __launch_bounds__(kThreads, 3) decode_mma_kernel(MmaArgs a) {
     // ---- merge the four warps (scores are in log2 units; partials are stored in natural units) ----
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
-#pragma unroll
-    for (int b = 0; b < 4; ++b) {
-        z[b] += __shfl_xor_sync(0xffffffffu, z[b], 1);
-        z[b] += __shfl_xor_sync(0xffffffffu, z[b], 2);
-    }
     if (j == 0 && (!NSPLIT || n < 4)) {
         s_m[warp][n] = m_run;
         s_l[warp][n] = l_run;
-#pragma unroll
-        for (int b = 0; b < 4; ++b) s_z[warp][n][b] = z[b];
     }
 #pragma unroll
     for (int b = 0; b < 4; ++b)
@@ -519,7 +535,7 @@ __global__ void __launch_bounds__(kThreads, 3) decode_mma_kernel(MmaArgs a) {
         }
     __syncthreads();
     {
-        const int d = tid, b = d >> 5;
+        const int d = tid;
         for (int hh = 0; hh < g; ++hh) {
             float M = kNegBig;
 #pragma unroll
@@ -531,7 +547,7 @@ __global__ void __launch_bounds__(kThreads, 3) decode_mma_kernel(MmaArgs a) {
                 L = fmaf(s_l[w][hh], e, L);
                 float ov = s_o[w][hh][d];
                 if (NSPLIT) ov += s_o[w][hh + 4][d];
-                O = fmaf(ov + 0.5f * s_z[w][hh][b], e, O);
+                O = fmaf(ov, e, O);
             }
             const size_t pi = (size_t)(kvh * g + hh) * a.num_partitions + part;
             a.partial_out[pi * kD + d] = O * a.v_const;
