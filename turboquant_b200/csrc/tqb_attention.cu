@@ -393,9 +393,9 @@ int32_t tqb_decode_num_partitions(int32_t num_kv_heads, int32_t kv_len) {
     if (num_kv_heads <= 0 || kv_len <= 0) return 1;
     // Measured on B200 (512 KV heads x 8192 tokens): a CTA costs a few microseconds of fixed work
     // (query rotation, pipeline fill, merge), so partitions of 2048..4096 tokens are best once the
-    // grid covers the 148 x 3 resident CTAs; shorter sequences are split further to fill the GPU,
+    // grid covers the 148 x 4 resident CTAs; shorter sequences are split further to fill the GPU,
     // down to 64 tokens per partition.
-    const long long resident = 148 * 3;
+    const long long resident = 148 * 4;
     const int max_p = (kv_len + 63) / 64;
     long long p = (kv_len + 2047) / 2048;
     if ((long long)num_kv_heads * p < resident) p = (resident + num_kv_heads - 1) / num_kv_heads;

@@ -145,6 +145,11 @@ __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
     asm("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr) : "memory");   // ordered against other memory operations only
     return v;
 }
+__device__ __forceinline__ uint4 lds128_volatile(uint32_t addr) {
+    uint4 v;   // volatile: re-read where it is used instead of being kept in registers across the loop
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
 __device__ __forceinline__ uint2 lds64(uint32_t addr) {
     uint2 v;
     asm("ld.shared.v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(addr) : "memory");
@@ -240,14 +245,14 @@ __device__ __forceinline__ void stage_fill(const FillPlan& f, size_t row_off, in
 // P' for heads 0..3 and columns 4..7 the "lo" part, so one MMA delivers the split-precision
 // product.  NSPLIT = false (group 5..8): hi and lo take one MMA each.
 template <typename QT, int BITS, bool NSPLIT>
-__global__ void __launch_bounds__(kThreads, 3) decode_mma_kernel(MmaArgs a) {
+__global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a) {
     using G = Geo<BITS>;
     __shared__ __align__(1024) unsigned char s_raw[kWarps * G::kRingB];
     // 3-bit: the lookup table lives in dynamic shared memory at an 8 KB-aligned address, so that a
     // table address is formed by OR-ing (index << 7) into the lane's base with one LOP3.
     extern __shared__ unsigned char s_dyn[];
     __shared__ float s_q[8 * kD];   // rotated queries (prologue only)
-    __shared__ float s_sign[32];
+    __shared__ __align__(16) uint4 s_afr[8][32];   // A fragments of the rotated queries, [block * 2 + half][lane]
     // epilogue view of the ring memory (the rings are idle then)
     float (*s_o)[8][kD] = reinterpret_cast<float (*)[8][kD]>(s_raw);                 // [kWarps][8][128]
     float (*s_m)[8] = reinterpret_cast<float (*)[8]>(s_raw + kWarps * 8 * kD * 4);   // [kWarps][8]
@@ -310,10 +315,6 @@ __global__ void __launch_bounds__(kThreads, 3) decode_mma_kernel(MmaArgs a) {
     const uint32_t lut_base = BITS == 3 ? (((uint32_t)__cvta_generic_to_shared(s_dyn) + 8191u) & ~8191u) : 0u;
     const uint32_t lut = lut_base + lane * 4;
 
-    if (tid < 32) {
-        const uint32_t neg = 0xB1A6D4B2u;  // src/cache/precomputed/rotation.rs:16-20
-        s_sign[tid] = ((neg >> tid) & 1u) ? -a.sign_mag : a.sign_mag;
-    }
     if (BITS == 3) {
         // entry e = c0 | c1 << 3 -> half2(lut[c0], lut[c1]), one copy per bank
         for (int i = tid; i < 64 * 32; i += kThreads) {
@@ -322,16 +323,17 @@ __global__ void __launch_bounds__(kThreads, 3) decode_mma_kernel(MmaArgs a) {
             asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(lut_base + i * 4), "r"(v) : "memory");
         }
     }
-    __syncthreads();
     // ---- rotate the g queries of this KV head once: q~ = sigma .* H32(q_b) / sqrt(32), constants folded ----
     {
+        const uint32_t neg = 0xB1A6D4B2u;  // src/cache/precomputed/rotation.rs:16-20
+        const float sign = ((neg >> lane) & 1u) ? -a.sign_mag : a.sign_mag;
         const float inv_sqrt = 1.0f / sqrtf(32.0f);
         for (int u = warp; u < 8 * 4; u += kWarps) {
             const int hh = u >> 2, b = u & 3;
             float v = 0.0f;
             if (hh < g) v = to_f32<QT>(reinterpret_cast<const QT*>(a.q)[(size_t)(kvh * g + hh) * kD + b * 32 + lane]);
             v = wht32_lane(v, lane);
-            s_q[hh * kD + b * 32 + lane] = ((v * inv_sqrt) * s_sign[lane]) * a.qk_const;
+            s_q[hh * kD + b * 32 + lane] = ((v * inv_sqrt) * sign) * a.qk_const;
         }
     }
     __syncthreads();
@@ -339,23 +341,19 @@ __global__ void __launch_bounds__(kThreads, 3) decode_mma_kernel(MmaArgs a) {
     // lanes n and n + 4 compute the same scores and need no exchange later).  For block b and half m
     // the k-slots (2j, 2j+1 | 2j+8, 2j+9) hold the dims that the code unpackers deliver:
     //   4-bit: 32b + 8j + 2m + (0, 4 | 1, 5)      3-bit: 32b + 8j + 4m + (0, 1 | 2, 3)
-    uint32_t afr[4][2][4];
     {
         const float* sq = s_q + (NSPLIT ? (n & 3) : n) * kD;
+        const int b = warp;   // one block per warp
 #pragma unroll
-        for (int b = 0; b < 4; ++b) {
-#pragma unroll
-            for (int m = 0; m < 2; ++m) {
-                const int d0 = 32 * b + 8 * j + (BITS == 4 ? 2 * m : 4 * m);
-                const float qa = sq[d0], qb = sq[d0 + (BITS == 4 ? 4 : 1)];
-                const float qc = sq[d0 + (BITS == 4 ? 1 : 2)], qd = sq[d0 + (BITS == 4 ? 5 : 3)];
-                afr[b][m][0] = pack_hi(qa, qb);
-                afr[b][m][1] = pack_lo(qa, qb);
-                afr[b][m][2] = pack_hi(qc, qd);
-                afr[b][m][3] = pack_lo(qc, qd);
-            }
+        for (int m = 0; m < 2; ++m) {
+            const int d0 = 32 * b + 8 * j + (BITS == 4 ? 2 * m : 4 * m);
+            const float qa = sq[d0], qb = sq[d0 + (BITS == 4 ? 4 : 1)];
+            const float qc = sq[d0 + (BITS == 4 ? 1 : 2)], qd = sq[d0 + (BITS == 4 ? 5 : 3)];
+            s_afr[b * 2 + m][lane] = make_uint4(pack_hi(qa, qb), pack_lo(qa, qb), pack_hi(qc, qd), pack_lo(qc, qd));
         }
     }
+    __syncthreads();
+    const uint32_t afr_base = (uint32_t)__cvta_generic_to_shared(&s_afr[0][lane]);
     const bool lo_lane = NSPLIT && n >= 4;   // NSPLIT: this lane's MMA column carries the lo part of P'
 
     float m_run = kNegBig, l_run = 0.0f;
@@ -402,8 +400,9 @@ __global__ void __launch_bounds__(kThreads, 3) decode_mma_kernel(MmaArgs a) {
                     x[3] = lds32(lop3_and_or(w >> 11, 0x1F80u, lut));
                 }
                 float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                mma16816(acc, afr[b][0][0], afr[b][0][1], afr[b][0][2], afr[b][0][3], x[0], x[1]);
-                mma16816(acc, afr[b][1][0], afr[b][1][1], afr[b][1][2], afr[b][1][3], x[2], x[3]);
+                const uint4 a0 = lds128_volatile(afr_base + (b * 2) * 512), a1 = lds128_volatile(afr_base + (b * 2 + 1) * 512);
+                mma16816(acc, a0.x, a0.y, a0.z, a0.w, x[0], x[1]);
+                mma16816(acc, a1.x, a1.y, a1.z, a1.w, x[2], x[3]);
                 const __half2 p0 = u32_as_h2(b < 2 ? sc0.x : sc0.y), p1 = u32_as_h2(b < 2 ? sc1.x : sc1.y);
                 const float k0 = fabsf((b & 1) ? __high2float(p0) : __low2float(p0));
                 const float k1 = fabsf((b & 1) ? __high2float(p1) : __low2float(p1));
