@@ -203,6 +203,15 @@ int tqb_block_quantize(int32_t bits, int32_t head_dim, int32_t norm_mode, int32_
                        uint16_t *scales, int64_t rows_per_group, int64_t out_group_stride,
                        int64_t out_row_offset, tqb_stream_t stream);
 
+/* The same for the K and V tensors of one append in ONE launch (the reference quantizes them one
+ * after the other, quantize_kv_pair in src/cache/common.rs:102-111); both tensors share shape, dtype, stride and
+ * row mapping. */
+int tqb_block_quantize_pair(int32_t bits, int32_t head_dim, int32_t norm_mode, int32_t outlier_blocks,
+                            const void *k, const void *v, int32_t x_dtype, int64_t n, int64_t x_row_stride,
+                            uint8_t *k_indices, uint16_t *k_scales, uint8_t *v_indices, uint16_t *v_scales,
+                            int64_t rows_per_group, int64_t out_group_stride, int64_t out_row_offset,
+                            tqb_stream_t stream);
+
 /* polar_dequantize (src/cache/quantize_tensor.rs:179-220).  Input row mapping as above
  * (rows_per_group = 0: dense); out: device [n, head_dim] of out_dtype, dense. */
 int tqb_block_dequantize(int32_t bits, int32_t head_dim, int32_t norm_mode, int32_t outlier_blocks,
@@ -249,11 +258,14 @@ typedef struct tqb_decode_params {
 } tqb_decode_params;
 
 /* flags: stop after the split-K pass and leave the per-partition (max, sum, out) partials in
- * `scratch` (layout [num_q_heads, P, head_dim] f32, then [num_q_heads, P] max, then sum);
- * `out` is not written. */
+ * `scratch`; `out` is not written.  Scratch layout: merge tickets (one u32 per query head, rounded up to
+ * 256 bytes), then [num_q_heads, P, head_dim] f32, then [num_q_heads, P] max, then sum. */
 #define TQB_DECODE_PARTIALS_ONLY 1
 /* flags: always take the general (SIMT, any shape) kernel; used to cross-check the tensor-core kernels. */
 #define TQB_DECODE_FORCE_GENERAL 2
+/* flags: the caller vouches that the ticket area at the start of `scratch` is zero (zero-filled once when
+ * the buffer was allocated; every completed call leaves it zero), so the library skips clearing it. */
+#define TQB_DECODE_TICKETS_ZERO 4
 
 /* Partitions the library would use for this shape, and the scratch it then needs. */
 int32_t tqb_decode_num_partitions(int32_t num_kv_heads, int32_t kv_len);

@@ -120,4 +120,4 @@ def test_argument_errors_are_reported_before_any_launch():
     assert lib.tqb_fused_attention(*([None] * 14), 0, 4, 2, 128, 0, 0, 48, 4, 3, 1.0, 1, None) == 0  # kv_len == 0
     assert lib.tqb_decode_attention(None, None) == 6
     assert lib.tqb_decode_num_partitions(8, 1024) >= 1
-    assert lib.tqb_decode_scratch_bytes(16, 128, 4) == 4 * 16 * 4 * 130
+    assert lib.tqb_decode_scratch_bytes(16, 128, 4) == 256 + 4 * 16 * 4 * 130   # merge tickets + partials

@@ -79,6 +79,32 @@ def test_append_row_mapping():
     assert np.array_equal(u16(sc)[:, off:off + new].reshape(-1, 4), os_)
 
 
+@pytest.mark.parametrize("bits,nm,ob", [(4, 0, -1), (3, 0, -1), (3, 1, -1), (4, 0, 2)])
+def test_pair_launch_equals_two_single_launches(bits, nm, ob):
+    # K and V of one append in one launch, with the append row mapping
+    heads, new, cap, off = 4, 3, 8, 2
+    g = torch.Generator().manual_seed(bits * 10 + nm)
+    k = torch.randn((heads * new, 128), generator=g).to(torch.bfloat16).cuda()
+    v = torch.randn((heads * new, 128), generator=g).to(torch.bfloat16).cuda()
+    pd = 16 * bits
+
+    def buffers():
+        return (torch.zeros((heads, cap, pd), dtype=torch.uint8, device="cuda"),
+                torch.zeros((heads, cap, 4), dtype=torch.int16, device="cuda"))
+    ki, ks = buffers(); vi, vs = buffers()
+    rc = lib.tqb_block_quantize_pair(bits, 128, nm, ob, k.data_ptr(), v.data_ptr(), 2, heads * new, 0, ki.data_ptr(),
+                                     ks.data_ptr(), vi.data_ptr(), vs.data_ptr(), new, cap, off, None)
+    assert rc == 0
+    ki1, ks1 = buffers(); vi1, vs1 = buffers()
+    tq.block_quantize(k, bits, tq.QuantNormMode(nm), ob, out=(ki1, ks1), rows_per_group=new, group_stride=cap, row_offset=off)
+    tq.block_quantize(v, bits, tq.QuantNormMode(nm), ob, out=(vi1, vs1), rows_per_group=new, group_stride=cap, row_offset=off)
+    torch.cuda.synchronize()
+    for a, b in ((ki, ki1), (ks, ks1), (vi, vi1), (vs, vs1)):
+        assert torch.equal(a, b)
+    assert lib.tqb_block_quantize_pair(bits, 128, nm, ob, k.data_ptr(), None, 2, 4, 0, ki.data_ptr(), ks.data_ptr(),
+                                       vi.data_ptr(), vs.data_ptr(), 0, 0, 0, None) == 6   # null pointer
+
+
 def test_reference_ffi_symbols():
     # the four launchers of src/cache/cuda/ffi.rs:10-79, called with the reference's own argument lists
     rng = np.random.default_rng(2)

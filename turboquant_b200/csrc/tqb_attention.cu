@@ -18,12 +18,13 @@
 #include <mutex>
 
 #include "tqb_common.cuh"
+#include "tqb_merge.cuh"
 
 namespace tqb {
 
 int block_cfg_check(int bits, int head_dim, int norm_mode);
 int launch_decode_mma(const tqb_decode_params* p, int num_partitions, float* partial_out, float* partial_max,
-                      float* partial_sum, float sign_mag, cudaStream_t s);
+                      float* partial_sum, float sign_mag, unsigned* counters, bool counters_clean, cudaStream_t s);
 
 namespace {
 
@@ -251,50 +252,10 @@ decode_general_kernel(DecodeArgs a, Codebook normal, Codebook outlier) {
     }
 }
 
-struct MergeArgs {
-    const float* partial_out;
-    const float* partial_max;
-    const float* partial_sum;
-    const float* dev_signs;
-    void* out;
-    float* lse_out;  // optional [hq][2]
-    int head_dim, nblk, num_partitions;
-    int rotate;      // 1: inputs are in the rotated domain (apply sigma, H32, 1/sqrt(32))
-    float sign_mag;
-};
-
-// Log-sum-exp merge of partitions (tq_attention_kernel.cu:299-332) fused with the single
-// inverse rotation of the output.  Grid: one CTA per query head; warp w handles output
-// blocks w, w+4, ...; lane = element of the block.
-template <typename OT>
+// Log-sum-exp merge of partitions fused with the single inverse rotation of the output (merge_head in
+// tqb_merge.cuh).  Grid: one CTA per query head.
 __global__ void __launch_bounds__(kThreads) decode_merge_kernel(MergeArgs a) {
-    const int head = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int D = a.head_dim, P = a.num_partitions;
-    const float* pm = a.partial_max + (size_t)head * P;
-    const float* ps = a.partial_sum + (size_t)head * P;
-    float M = -FLT_MAX;
-    for (int p = lane; p < P; p += 32) M = fmaxf(M, pm[p]);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-    float L = 0.0f;
-    for (int p = lane; p < P; p += 32) L += ps[p] * expf(pm[p] - M);
-    L = warp_sum(L);
-    const float inv_sqrt = 1.0f / sqrtf((float)kBlock);
-    const uint32_t neg = 0xB1A6D4B2u;
-    const float sg = a.dev_signs ? a.dev_signs[lane] : (((neg >> lane) & 1u) ? -a.sign_mag : a.sign_mag);
-    const float inv_l = L > 0.0f ? 1.0f / L : 0.0f;
-    for (int b = warp; b < a.nblk; b += kWarps) {
-        float acc = 0.0f;
-        for (int p = 0; p < P; ++p)
-            acc = fmaf(a.partial_out[((size_t)head * P + p) * D + b * 32 + lane], expf(pm[p] - M), acc);
-        if (a.rotate) acc = wht32_lane(acc * sg, lane) * inv_sqrt;
-        if (a.lse_out == nullptr) acc *= inv_l;
-        reinterpret_cast<OT*>(a.out)[(size_t)head * D + b * 32 + lane] = from_f32<OT>(acc);
-    }
-    if (a.lse_out != nullptr && threadIdx.x == 0) {
-        a.lse_out[head * 2] = M;
-        a.lse_out[head * 2 + 1] = L;
-    }
+    merge_head(a, blockIdx.x, threadIdx.x & 31, threadIdx.x >> 5, kWarps);
 }
 
 // Shard merge: partial_out [S, hq, D] un-normalised and already in the output domain,
@@ -340,9 +301,8 @@ int launch_general_nb(const DecodeArgs& a, const Codebook& n, const Codebook& o,
     return launch_general<QT, 8>(a, n, o, s);
 }
 
-template <typename OT>
 int launch_merge(const MergeArgs& m, int hq, cudaStream_t s) {
-    decode_merge_kernel<OT><<<hq, kThreads, 0, s>>>(m);
+    decode_merge_kernel<<<hq, kThreads, 0, s>>>(m);
     return check_launch(s);
 }
 
@@ -377,9 +337,8 @@ int run_merge(const DecodeArgs& a, void* out, int out_dtype, float* lse_out, cud
     m.num_partitions = a.num_partitions;
     m.rotate = 1;
     m.sign_mag = a.sign_mag;
-    if (out_dtype == TQB_F32) return launch_merge<float>(m, a.hq, s);
-    if (out_dtype == TQB_F16) return launch_merge<__half>(m, a.hq, s);
-    return launch_merge<__nv_bfloat16>(m, a.hq, s);
+    m.out_dtype = out_dtype;
+    return launch_merge(m, a.hq, s);
 }
 
 }  // namespace
@@ -411,9 +370,13 @@ int32_t tqb_decode_num_partitions(int32_t num_kv_heads, int32_t kv_len) {
     return (int32_t)p;
 }
 
+// Scratch layout: [merge tickets: one u32 per query head, rounded up to 256 bytes][partial out]
+// [partial max][partial sum].
+static size_t ticket_bytes(int32_t num_q_heads) { return (sizeof(unsigned) * (size_t)num_q_heads + 255) / 256 * 256; }
+
 size_t tqb_decode_scratch_bytes(int32_t num_q_heads, int32_t head_dim, int32_t num_partitions) {
     if (num_q_heads <= 0 || head_dim <= 0 || num_partitions <= 0) return 0;
-    return sizeof(float) * (size_t)num_q_heads * num_partitions * ((size_t)head_dim + 2);
+    return ticket_bytes(num_q_heads) + sizeof(float) * (size_t)num_q_heads * num_partitions * ((size_t)head_dim + 2);
 }
 
 int tqb_decode_attention(const tqb_decode_params* p, tqb_stream_t stream) {
@@ -439,7 +402,8 @@ int tqb_decode_attention(const tqb_decode_params* p, tqb_stream_t stream) {
     DecodeArgs a{};
     a.q = p->q;
     a.k_idx = p->k_indices; a.k_sc = p->k_scales; a.v_idx = p->v_indices; a.v_sc = p->v_scales;
-    float* sc = reinterpret_cast<float*>(p->scratch);
+    unsigned* tickets = reinterpret_cast<unsigned*>(p->scratch);
+    float* sc = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(p->scratch) + ticket_bytes(p->num_q_heads));
     a.partial_out = sc;
     a.partial_max = sc + (size_t)p->num_q_heads * P * p->head_dim;
     a.partial_sum = a.partial_max + (size_t)p->num_q_heads * P;
@@ -457,11 +421,9 @@ int tqb_decode_attention(const tqb_decode_params* p, tqb_stream_t stream) {
     const bool partials_only = (p->flags & TQB_DECODE_PARTIALS_ONLY) != 0;
     if (!(p->flags & TQB_DECODE_FORCE_GENERAL)) {
         // tensor-core kernels for the shapes they cover; everything else takes the general kernel
-        st = launch_decode_mma(p, P, a.partial_out, a.partial_max, a.partial_sum, a.sign_mag, as_stream(stream));
-        if (st == TQB_OK) {
-            if (partials_only) return TQB_OK;
-            return run_merge(a, p->out, p->out_dtype, p->lse_out, as_stream(stream));
-        }
+        // (the merge runs inside the kernel, in the CTA that finishes a KV head last)
+        st = launch_decode_mma(p, P, a.partial_out, a.partial_max, a.partial_sum, a.sign_mag,
+                               partials_only ? nullptr : tickets, (p->flags & TQB_DECODE_TICKETS_ZERO) != 0, as_stream(stream));
         if (st != TQB_ERR_UNSUPPORTED) return st;
     }
     return run_decode(a, cn, co, p->q_dtype, p->out, p->out_dtype, p->lse_out, as_stream(stream), partials_only);
@@ -591,8 +553,9 @@ int tqb_decode_attention_static(const tqb_decode_params* p, tqb_stream_t stream)
     q.scratch_bytes = kStaticScratchBytes;
     q.num_partitions = P;
     // Every (head, partition) slot that the merge reads is written by the split-K pass of the same
-    // call, so nothing in the array has to start at zero and stale contents of an earlier call are
-    // never read.
+    // call, and the merge tickets are cleared on the stream before the kernel (their area may hold an
+    // earlier call's partials when the head count changes), so stale contents are never read.
+    q.flags &= ~TQB_DECODE_TICKETS_ZERO;
     return tqb_decode_attention(&q, stream);
 }
 

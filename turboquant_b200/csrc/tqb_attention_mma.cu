@@ -33,6 +33,7 @@
 #include <mutex>
 
 #include "tqb_common.cuh"
+#include "tqb_merge.cuh"
 
 namespace tqb {
 namespace {
@@ -58,6 +59,11 @@ struct MmaArgs {
     float v_const;    // grid step | kappa
     float sign_mag;
     float lut[8];     // 3-bit path: centroid / kappa
+    // fused merge: the CTA that finishes a KV head last combines its partitions (counters == nullptr: off)
+    unsigned* counters;   // [hkv], zero before the launch; left zero by it
+    void* out;
+    float* lse_out;
+    int out_dtype;
 };
 
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -556,6 +562,25 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a) {
             }
         }
     }
+    if (a.counters != nullptr) {
+        // Last-arriver merge: every CTA publishes its partial (fence), then takes a ticket; the CTA that
+        // draws the last ticket of its KV head sees all partials of that head and merges them.
+        __shared__ int s_last;
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) s_last = atomicAdd(a.counters + kvh, 1u) == (unsigned)(a.num_partitions - 1) ? 1 : 0;
+        __syncthreads();
+        if (s_last) {
+            __threadfence();
+            MergeArgs m;
+            m.partial_out = a.partial_out; m.partial_max = a.partial_max; m.partial_sum = a.partial_sum;
+            m.dev_signs = nullptr; m.out = a.out; m.lse_out = a.lse_out;
+            m.head_dim = kD; m.nblk = kD / 32; m.num_partitions = a.num_partitions; m.rotate = 1;
+            m.out_dtype = a.out_dtype; m.sign_mag = a.sign_mag;
+            for (int hh = 0; hh < g; ++hh) merge_head(m, kvh * g + hh, lane, warp, kWarps);
+            if (tid == 0) a.counters[kvh] = 0u;   // ready for the next launch
+        }
+    }
 }
 
 // kappa in [1, 2) such that every centroid / kappa is as close as possible to an f16 value.
@@ -609,8 +634,10 @@ int launch(const MmaArgs& a, int g, int q_dtype, dim3 grid, cudaStream_t s) {
 
 // Returns TQB_ERR_UNSUPPORTED when the shape is outside what the tensor-core kernels cover;
 // the caller then uses the general kernel.
+// `counters` != nullptr fuses the merge into the kernel: [num_kv_heads] tickets, zeroed here unless the
+// caller vouches for them (counters_clean).
 int launch_decode_mma(const tqb_decode_params* p, int num_partitions, float* partial_out, float* partial_max,
-                      float* partial_sum, float sign_mag, cudaStream_t s) {
+                      float* partial_sum, float sign_mag, unsigned* counters, bool counters_clean, cudaStream_t s) {
     const int g = p->num_q_heads / p->num_kv_heads;
     const int nblk = p->head_dim / kBlock;
     const bool all_outlier = p->outlier_blocks < 0 || p->outlier_blocks >= nblk;
@@ -635,6 +662,14 @@ int launch_decode_mma(const tqb_decode_params* p, int num_partitions, float* par
     const int step = kWarps * kGroup;
     a.part_size = ((p->kv_len + num_partitions - 1) / num_partitions + step - 1) / step * step;
     a.sign_mag = sign_mag;
+    a.counters = counters;
+    a.out = p->out;
+    a.lse_out = p->lse_out;
+    a.out_dtype = p->out_dtype;
+    if (counters != nullptr && !counters_clean) {
+        cudaError_t e = cudaMemsetAsync(counters, 0, sizeof(unsigned) * (size_t)p->num_kv_heads, s);
+        if (e != cudaSuccess) { set_cuda_error(e); return TQB_ERR_CUDA; }
+    }
     dim3 grid(p->num_kv_heads, num_partitions);
     const float log2e = 1.4426950408889634f;
     if (pqo4) {

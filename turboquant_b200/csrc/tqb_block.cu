@@ -141,6 +141,10 @@ struct QuantArgs {
     float scale_sign_normal;
     const float* dev_boundaries;  // legacy entry point: boundaries on the device (outlier table)
     int dev_num_boundaries;
+    // second tensor of a pair launch (grid.y = 2: K and V of one append in one launch), else nullptr
+    const void* x2;
+    uint8_t* indices2;
+    uint16_t* scales2;
 };
 
 // src/cache/quantize_tensor.rs:40-176 with the scalar arithmetic of
@@ -148,6 +152,7 @@ struct QuantArgs {
 template <typename T, int BITS>
 __global__ void __launch_bounds__(kThreads)
 block_quantize_kernel(QuantArgs a, Codebook normal, Codebook outlier) {
+    if (blockIdx.y != 0) { a.x = a.x2; a.indices = a.indices2; a.scales = a.scales2; }
     __shared__ float s_b[2][16];
     __shared__ float s_sign[32];
     if (threadIdx.x < 16) {
@@ -306,6 +311,7 @@ constexpr uint32_t kSignMask = 0xB1A6D4B2u;   // bit j set <=> sign j is -1 (pre
 template <typename T, int BITS>
 __global__ void __launch_bounds__(kThreads)
 block_quantize_pqo_kernel(QuantArgs a, Codebook cb) {
+    if (blockIdx.y != 0) { a.x = a.x2; a.indices = a.indices2; a.scales = a.scales2; }
     const unsigned total = (unsigned)(a.n_rows * a.nblk);
     const unsigned nblk = (unsigned)a.nblk;
     const float inv_sqrt = 1.0f / sqrtf((float)kBlock);
@@ -497,15 +503,15 @@ int launch_quant(int bits, const QuantArgs& a, const Codebook& n, const Codebook
     const bool pqo = a.norm_mode == TQB_MAXNORM && !a.pre_rotated && a.dev_boundaries == nullptr &&
                      a.outlier_blocks >= a.nblk && (bits == 3 || bits == 4) && blocks < (1LL << 31) &&
                      a.map.rows_per_group < (1LL << 31) &&
-                     ((uintptr_t)a.indices % 16) == 0;
+                     ((uintptr_t)a.indices % 16) == 0 && ((uintptr_t)a.indices2 % 16) == 0;
     if (pqo) {
-        const int grid = grid_for(blocks);
+        const dim3 grid(grid_for(blocks), a.x2 ? 2 : 1);
         if (bits == 4) block_quantize_pqo_kernel<T, 4><<<grid, kThreads, 0, s>>>(a, o);
         else block_quantize_pqo_kernel<T, 3><<<grid, kThreads, 0, s>>>(a, o);
         return check_launch(s);
     }
     const long long lanes = a.n_rows * a.nblk * 4;
-    const int grid = grid_for(lanes);
+    const dim3 grid(grid_for(lanes), a.x2 ? 2 : 1);
     switch (bits) {
         case 2: block_quantize_kernel<T, 2><<<grid, kThreads, 0, s>>>(a, n, o); break;
         case 3: block_quantize_kernel<T, 3><<<grid, kThreads, 0, s>>>(a, n, o); break;
@@ -548,20 +554,23 @@ using namespace tqb;
 
 extern "C" {
 
-int tqb_block_quantize(int32_t bits, int32_t head_dim, int32_t norm_mode, int32_t outlier_blocks, const void* x,
-                       int32_t x_dtype, int64_t n, int64_t x_row_stride, uint8_t* indices, uint16_t* scales,
-                       int64_t rows_per_group, int64_t out_group_stride, int64_t out_row_offset,
-                       tqb_stream_t stream) {
+static int block_quantize_impl(int32_t bits, int32_t head_dim, int32_t norm_mode, int32_t outlier_blocks, const void* x,
+                               const void* x2, int32_t x_dtype, int64_t n, int64_t x_row_stride, uint8_t* indices,
+                               uint16_t* scales, uint8_t* indices2, uint16_t* scales2, int64_t rows_per_group,
+                               int64_t out_group_stride, int64_t out_row_offset, tqb_stream_t stream) {
     int st = block_cfg_check(bits, head_dim, norm_mode);
     if (st != TQB_OK) return st;
     if (n < 0 || x_row_stride < 0 || rows_per_group < 0) return TQB_ERR_INVALID_ARGUMENT;
     if (n == 0) return TQB_OK;
     if (!x || !indices || !scales) return TQB_ERR_NULL_POINTER;
+    if (x2 && (!indices2 || !scales2)) return TQB_ERR_NULL_POINTER;
     if (x_row_stride != 0 && x_row_stride < head_dim) return TQB_ERR_INVALID_ARGUMENT;
     const size_t esz = x_dtype == TQB_F32 ? 4 : 2;
     if (x_dtype != TQB_F32 && x_dtype != TQB_F16 && x_dtype != TQB_BF16) return TQB_ERR_INVALID_ARGUMENT;
     if (((uintptr_t)x % 16) != 0 || ((x_row_stride * esz) % 16) != 0 || ((uintptr_t)indices % 4) != 0 ||
         ((uintptr_t)scales % 2) != 0)
+        return TQB_ERR_MISALIGNED;
+    if (x2 && (((uintptr_t)x2 % 16) != 0 || ((uintptr_t)indices2 % 4) != 0 || ((uintptr_t)scales2 % 2) != 0))
         return TQB_ERR_MISALIGNED;
     Codebook cn, co;
     if (!block_codebook(bits - 1, norm_mode, cn) || !block_codebook(bits, norm_mode, co)) return TQB_ERR_UNSUPPORTED_BITS;
@@ -571,6 +580,9 @@ int tqb_block_quantize(int32_t bits, int32_t head_dim, int32_t norm_mode, int32_
     a.x_row_stride = x_row_stride;
     a.indices = indices;
     a.scales = scales;
+    a.x2 = x2;
+    a.indices2 = x2 ? indices2 : nullptr;
+    a.scales2 = x2 ? scales2 : nullptr;
     a.map = RowMap{rows_per_group, out_group_stride, out_row_offset};
     a.nblk = head_dim / kBlock;
     a.outlier_blocks = outlier_blocks < 0 || outlier_blocks > a.nblk ? a.nblk : outlier_blocks;
@@ -585,6 +597,23 @@ int tqb_block_quantize(int32_t bits, int32_t head_dim, int32_t norm_mode, int32_
     if (x_dtype == TQB_F32) return launch_quant<float>(bits, a, cn, co, s);
     if (x_dtype == TQB_F16) return launch_quant<__half>(bits, a, cn, co, s);
     return launch_quant<__nv_bfloat16>(bits, a, cn, co, s);
+}
+
+int tqb_block_quantize(int32_t bits, int32_t head_dim, int32_t norm_mode, int32_t outlier_blocks, const void* x,
+                       int32_t x_dtype, int64_t n, int64_t x_row_stride, uint8_t* indices, uint16_t* scales,
+                       int64_t rows_per_group, int64_t out_group_stride, int64_t out_row_offset,
+                       tqb_stream_t stream) {
+    return block_quantize_impl(bits, head_dim, norm_mode, outlier_blocks, x, nullptr, x_dtype, n, x_row_stride, indices,
+                               scales, nullptr, nullptr, rows_per_group, out_group_stride, out_row_offset, stream);
+}
+
+int tqb_block_quantize_pair(int32_t bits, int32_t head_dim, int32_t norm_mode, int32_t outlier_blocks, const void* k,
+                            const void* v, int32_t x_dtype, int64_t n, int64_t x_row_stride, uint8_t* k_indices,
+                            uint16_t* k_scales, uint8_t* v_indices, uint16_t* v_scales, int64_t rows_per_group,
+                            int64_t out_group_stride, int64_t out_row_offset, tqb_stream_t stream) {
+    if (n > 0 && !v) return TQB_ERR_NULL_POINTER;
+    return block_quantize_impl(bits, head_dim, norm_mode, outlier_blocks, k, v, x_dtype, n, x_row_stride, k_indices,
+                               k_scales, v_indices, v_scales, rows_per_group, out_group_stride, out_row_offset, stream);
 }
 
 int tqb_block_dequantize(int32_t bits, int32_t head_dim, int32_t norm_mode, int32_t outlier_blocks,

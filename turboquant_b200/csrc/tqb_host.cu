@@ -55,6 +55,23 @@ struct DevBuf {
 // ---------------------------------------------------------------------------------------
 // PqoCache
 // ---------------------------------------------------------------------------------------
+// Grows the decode scratch when needed and keeps its ticket area (the first bytes) zero: it is cleared
+// when the buffer is new or the head count changed; completed decode calls leave it zero.
+static int prepare_scratch(DevBuf& scratch, int& ticket_heads, size_t need, int num_q_heads, int head_dim,
+                           int num_partitions, cudaStream_t s) {
+    if (need > scratch.bytes) {
+        TQB_CUDA(cudaStreamSynchronize(s));
+        TQB_TRY(scratch.reserve(need + need / 4));
+        ticket_heads = -1;
+    }
+    if (ticket_heads != num_q_heads) {
+        const size_t partials = sizeof(float) * (size_t)num_q_heads * num_partitions * ((size_t)head_dim + 2);
+        TQB_CUDA(cudaMemsetAsync(scratch.p, 0, need - partials, s));
+        ticket_heads = num_q_heads;
+    }
+    return TQB_OK;
+}
+
 struct tqb_pqo_cache {
     tqb_cache_config cfg;
     int nblk, packed_dim, heads;  // heads = batch * num_kv_heads
@@ -158,10 +175,8 @@ struct tqb_pqo_cache {
         TQB_TRY(ensure_capacity(layer, old_len + new_tokens, s));
         Layer& l = layers[layer];
         const int64_t rows = (int64_t)heads * new_tokens;
-        TQB_TRY(tqb_block_quantize(cfg.bits, cfg.head_dim, cfg.norm_mode, cfg.outlier_blocks, k_dev, dtype, rows, 0, l.ki,
-                                   l.ks, new_tokens, l.cap, old_len, s));
-        TQB_TRY(tqb_block_quantize(cfg.bits, cfg.head_dim, cfg.norm_mode, cfg.outlier_blocks, v_dev, dtype, rows, 0, l.vi,
-                                   l.vs, new_tokens, l.cap, old_len, s));
+        TQB_TRY(tqb_block_quantize_pair(cfg.bits, cfg.head_dim, cfg.norm_mode, cfg.outlier_blocks, k_dev, v_dev, dtype, rows, 0,
+                                        l.ki, l.ks, l.vi, l.vs, new_tokens, l.cap, old_len, s));
         l.len = old_len + new_tokens;
         l.active = true;
         return TQB_OK;
@@ -209,14 +224,13 @@ struct tqb_pqo_cache {
         p.num_partitions = tqb_decode_num_partitions(heads, (int32_t)l.len);
         p.softmax_scale = softmax_scale;
         const size_t need = tqb_decode_scratch_bytes(p.num_q_heads, cfg.head_dim, p.num_partitions);
-        if (need > scratch.bytes) {
-            TQB_CUDA(cudaStreamSynchronize(s));
-            TQB_TRY(scratch.reserve(need + need / 4));
-        }
+        TQB_TRY(prepare_scratch(scratch, ticket_heads, need, p.num_q_heads, cfg.head_dim, p.num_partitions, s));
         p.scratch = scratch.p;
         p.scratch_bytes = scratch.bytes;
+        p.flags = TQB_DECODE_TICKETS_ZERO;
         return tqb_decode_attention(&p, s);
     }
+    int ticket_heads = -1;   // head count the zeroed ticket area of `scratch` was sized for
 };
 
 extern "C" {
@@ -863,12 +877,10 @@ int tqb_tq_cache_decode_fused(tqb_tq_cache* c, int32_t layer, const void* k, con
     p.num_partitions = tqb_decode_num_partitions(b->heads, (int32_t)L.len);
     p.softmax_scale = softmax_scale;
     const size_t need = tqb_decode_scratch_bytes(p.num_q_heads, b->cfg.head_dim, p.num_partitions);
-    if (need > b->scratch.bytes) {
-        TQB_CUDA(cudaStreamSynchronize(s));
-        TQB_TRY(b->scratch.reserve(need + need / 4));
-    }
+    TQB_TRY(prepare_scratch(b->scratch, b->ticket_heads, need, p.num_q_heads, b->cfg.head_dim, p.num_partitions, s));
     p.scratch = b->scratch.p;
     p.scratch_bytes = b->scratch.bytes;
+    p.flags = TQB_DECODE_TICKETS_ZERO;
     return tqb_decode_attention(&p, s);
 }
 
