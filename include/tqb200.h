@@ -266,6 +266,15 @@ typedef struct tqb_decode_params {
 /* flags: the caller vouches that the ticket area at the start of `scratch` is zero (zero-filled once when
  * the buffer was allocated; every completed call leaves it zero), so the library skips clearing it. */
 #define TQB_DECODE_TICKETS_ZERO 4
+/* flags: stage the packed tiles with the tensor copy engine (TMA: 2-D tiled maps with the 64-byte swizzle for
+ * the index arrays, 1-D maps for the scale rows, one 64-token tile per CTA and stage) instead of per-warp
+ * cp.async rings.  Same bits; measured 5 % slower on B200, so it is opt-in.  Falls back to cp.async by itself
+ * when kv_stride is odd or a cache array is not 16-byte aligned. */
+#define TQB_DECODE_TMA 8
+
+/* Diagnostic: how many bounded waits on a staged tile ran out on the current device since the library was
+ * loaded (synchronises the device).  Always 0 in a healthy run; -1 on a CUDA error.  No reference counterpart. */
+long long tqb_decode_stage_timeouts(void);
 
 /* Partitions the library would use for this shape, and the scratch it then needs. */
 int32_t tqb_decode_num_partitions(int32_t num_kv_heads, int32_t kv_len);

@@ -109,6 +109,30 @@ def test_tensor_core_kernel_against_oracle_and_general_kernel(bits, g, L):
         assert np.abs(got - want).max() < tol
 
 
+@pytest.mark.parametrize("bits", [3, 4])
+@pytest.mark.parametrize("g", [4, 8])
+@pytest.mark.parametrize("L,stride", [(5, 16), (100, 128), (1000, 1024), (4133, 4200), (700, 701)])
+def test_tensor_copy_staging_equals_cp_async_staging(bits, g, L, stride):
+    # With the TMA flag even strides take the TMA-staged kernel, odd ones (701) fall back by themselves; both
+    # must give the bits of the cp.async-staged kernel.  The slots behind the last token hold NaN/Inf scale patterns and
+    # random codes: nothing of them may reach the result.
+    rng = np.random.default_rng(bits * 1000 + g * 10 + L)
+    hkv = 3
+    ki, ks, vi, vs = make_cache(rng, hkv, L, stride, bits)
+    for arr, fill in ((ks, 0x7E00), (vs, 0xFC00)):
+        arr[:, L:] = fill
+    ki[:, L:] = 0xA5
+    vi[:, L:] = 0x5A
+    q = (rng.standard_normal((hkv * g, 128)) / np.sqrt(128)).astype(np.float32)
+    want = o.block_attention(bits, 128, 0, -1, q, ki, ks, vi, vs, L, 0.0884, nthreads=8)
+    for parts in (0, 1, 3):
+        a = gpu_attend(q, ki, ks, vi, vs, L, bits, 0.0884, num_partitions=parts, tma=True)
+        b = gpu_attend(q, ki, ks, vi, vs, L, bits, 0.0884, num_partitions=parts)
+        assert torch.equal(a, b)
+        assert np.abs(a.cpu().numpy() - want).max() < (2e-5 if bits == 4 else 3e-4)
+    assert lib.tqb_decode_stage_timeouts() == 0
+
+
 @pytest.mark.parametrize("bits,nm,ob", [(3, 0, -1), (3, 1, -1), (3, 0, 0), (4, 0, -1)])
 def test_tensor_core_kernel_sharp_softmax(bits, nm, ob):
     # large logits: a handful of tokens carry all the weight, so element errors are not averaged away.

@@ -81,6 +81,7 @@ def _declare(lib):
         "tqb_block_codebook": (c_int, [I, I, P, P]),
         "tqb_block_sign_pattern": (None, [P]),
         "tqb_block_quantize": (c_int, [I, I, I, I, P, I, L, L, P, P, L, L, L, P]),
+        "tqb_decode_stage_timeouts": (ctypes.c_longlong, []),
         "tqb_block_quantize_pair": (c_int, [I, I, I, I, P, P, I, L, L, P, P, P, P, L, L, L, P]),
         "tqb_block_dequantize": (c_int, [I, I, I, I, P, P, L, L, L, L, P, I, P]),
         "tqb_decode_num_partitions": (I, [I, I]),

@@ -28,7 +28,10 @@
 //   is chosen so that all table values are (almost) exactly representable in f16.
 // Both the rotated query and P' are split into f16 hi + lo parts, so every product entering the
 // f32 accumulators is exact up to the (tiny) table error of the 3-bit path.
+#include <cuda.h>
+#include <cudaTypedefs.h>
 #include <float.h>
+#include <string.h>
 
 #include <mutex>
 
@@ -146,6 +149,53 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
 
+// ---- TMA staging (used when asked for and the cache layout allows it) ---------------------------
+// A stage holds one 64-token tile of the CTA (16 tokens per warp).  One thread arms the stage's "full"
+// mbarrier with the byte count and issues four tensor copies: the K and V index tiles (2-D maps [row bytes,
+// all token rows], box = 64 rows; 64-byte swizzle for 4-bit rows) and the K and V scale rows (1-D maps of
+// 8-byte elements, box = 64).  Rows past the end of the arrays are zero-filled by the hardware.  Each warp
+// arrives on the stage's "empty" mbarrier when it is done with its rows; the producer waits for the four
+// arrivals before it refills the stage.  Every wait polls a phase parity with a bound.
+struct alignas(64) TmaMaps {
+    CUtensorMap k, v, ks, vs;
+};
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred P1;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, P1;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: try_wait itself sleeps up to a hardware time limit per call.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (int i = 0; i < (1 << 16); ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_load_1d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x) {
+    asm volatile("cp.async.bulk.tensor.1d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3}], [%2];\n"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+template <int BITS>
+__device__ __forceinline__ void tma_tile_fill(const TmaMaps& m, uint32_t tile, uint32_t bar, int row);
+
+__device__ unsigned g_stage_timeouts = 0;   // staging waits that ran out (never expected)
+
 __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
     uint32_t v;
     asm("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr) : "memory");   // ordered against other memory operations only
@@ -178,10 +228,24 @@ template <int BITS>
 struct Geo {
     static constexpr int kRowB = 16 * BITS;            // packed bytes per token row
     static constexpr int kIdxB = kGroup * kRowB;       // one index array of a stage
-    static constexpr int kStageB = 2 * kIdxB + 256;    // + K and V scales
+    // + K and V scales; 4-bit stages are padded to a multiple of 512 bytes so that the XOR pattern below
+    // (bits 4..5 of an address ^ bits 7..8) is the same in every stage - it is TMA's 64-byte swizzle
+    static constexpr int kStageB = BITS == 4 ? (2 * kIdxB + 256 + 511) / 512 * 512 : 2 * kIdxB + 256;
     static constexpr int kRingB = kStages * kStageB;
+    static constexpr int kTileB = kWarps * (2 * kIdxB + 256);   // TMA staging: one 64-token tile of the CTA
     static constexpr int kPieces = kIdxB / 16;         // 16-byte pieces per index array (64 | 48)
 };
+
+// Tile layout: [K rows of warps 0..3][V rows of warps 0..3][K scale rows][V scale rows].
+template <int BITS>
+__device__ __forceinline__ void tma_tile_fill(const TmaMaps& m, uint32_t tile, uint32_t bar, int row) {
+    using G = Geo<BITS>;
+    mbar_expect_tx(bar, G::kTileB);
+    tma_load_2d(tile, &m.k, bar, 0, row);
+    tma_load_2d(tile + kWarps * G::kIdxB, &m.v, bar, 0, row);
+    tma_load_1d(tile + 2 * kWarps * G::kIdxB, &m.ks, bar, row);
+    tma_load_1d(tile + 2 * kWarps * G::kIdxB + kWarps * 128, &m.vs, bar, row);
+}
 
 // Per-lane copy plan of one stage: up to two 16-byte index pieces of K and of V, and one 8-byte
 // scale row (K for lanes 0..15, V for lanes 16..31).
@@ -250,15 +314,27 @@ __device__ __forceinline__ void stage_fill(const FillPlan& f, size_t row_off, in
 // NSPLIT = true (GQA group <= 4): the MMA columns 0..3 of O^T = V^T P' carry the f16 "hi" part of
 // P' for heads 0..3 and columns 4..7 the "lo" part, so one MMA delivers the split-precision
 // product.  NSPLIT = false (group 5..8): hi and lo take one MMA each.
-template <typename QT, int BITS, bool NSPLIT>
-__global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a) {
+//
+// TMA = true: stages are filled by the tensor copy engine (one lane per warp issues them); otherwise by
+// per-lane cp.async.  Both deliver the same bytes in the same swizzled layout.  Measured at 512 KV heads x
+// 8192 tokens: cp.async 181-184 us per launch, TMA 191-195 us (4-bit); 230 vs 236-239 us (3-bit).  A first
+// TMA version with one 16-token box set per warp (four small copies per warp and step) was slower still
+// (193-196 us).  The per-warp cp.async rings let the four warps drift apart freely and keep the copy issue
+// off any single warp's critical path; the shared tile ring couples them through its barriers.  So cp.async
+// is the default and TMA is opt-in (TQB_DECODE_TMA).
+template <typename QT, int BITS, bool NSPLIT, bool TMA>
+__global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, const __grid_constant__ TmaMaps maps) {
     using G = Geo<BITS>;
-    __shared__ __align__(1024) unsigned char s_raw[kWarps * G::kRingB];
-    // 3-bit: the lookup table lives in dynamic shared memory at an 8 KB-aligned address, so that a
-    // table address is formed by OR-ing (index << 7) into the lane's base with one LOP3.
+    // Dynamic shared memory: [3-bit only: lookup table at an 8 KB-aligned address, so that a table address
+    // is formed by OR-ing (index << 7) into the lane's base with one LOP3][stage rings, 1 KB-aligned].
     extern __shared__ unsigned char s_dyn[];
+    __shared__ __align__(8) unsigned long long s_bar[2][kStages];   // TMA staging: full / empty barriers of the stages
     __shared__ float s_q[8 * kD];   // rotated queries (prologue only)
     __shared__ __align__(16) uint4 s_afr[8][32];   // A fragments of the rotated queries, [block * 2 + half][lane]
+    const uint32_t dyn_base = (uint32_t)__cvta_generic_to_shared(s_dyn);
+    const uint32_t lut_base = BITS == 3 ? ((dyn_base + 8191u) & ~8191u) : 0u;
+    const uint32_t rings_base = BITS == 3 ? lut_base + 8192u : ((dyn_base + 1023u) & ~1023u);
+    unsigned char* s_raw = s_dyn + (rings_base - dyn_base);
     // epilogue view of the ring memory (the rings are idle then)
     float (*s_o)[8][kD] = reinterpret_cast<float (*)[8][kD]>(s_raw);                 // [kWarps][8][128]
     float (*s_m)[8] = reinterpret_cast<float (*)[8]>(s_raw + kWarps * 8 * kD * 4);   // [kWarps][8]
@@ -278,16 +354,46 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a) {
     const int first = t_begin + warp * kGroup;
     const int stride = kWarps * kGroup;
     const int ngroups = first < t_end ? (t_end - first + stride - 1) / stride : 0;
-    const uint32_t ring = (uint32_t)__cvta_generic_to_shared(s_raw) + warp * G::kRingB;
-    const FillPlan plan = make_plan<BITS>(a, row0, first, lane);
+    // cp.async: every warp owns a ring of 16-token stages.  TMA: the CTA owns a ring of 64-token tiles and
+    // `ring` / `st` address this warp's K rows inside a tile.
+    constexpr uint32_t kPitch = TMA ? G::kTileB : G::kStageB;           // distance between stages
+    constexpr uint32_t kVD = TMA ? kWarps * G::kIdxB : G::kIdxB;        // from a warp's K rows to its V rows
+    constexpr uint32_t kSD = TMA ? kWarps * 128 : 128;                  // from its K scale rows to its V scale rows
+    const uint32_t ring = TMA ? rings_base + warp * G::kIdxB : rings_base + warp * G::kRingB;
+    const uint32_t sdelta = TMA ? 2 * kWarps * G::kIdxB - warp * (G::kIdxB - 128) : 2 * G::kIdxB;   // K rows -> K scale rows
+    const FillPlan plan = TMA ? FillPlan{} : make_plan<BITS>(a, row0, first, lane);
+    const uint32_t full0 = (uint32_t)__cvta_generic_to_shared(&s_bar[0][0]);
+    const uint32_t empty0 = (uint32_t)__cvta_generic_to_shared(&s_bar[1][0]);
+    const int ntiles = t_begin < t_end ? (t_end - t_begin + stride - 1) / stride : 0;   // 64-token tiles of the CTA
+    const int nsteps = TMA ? ntiles : ngroups;
+    const int trow0 = (int)row0 + t_begin;                     // TMA: token row of tile 0 in the whole array
+    const bool producer = TMA && tid == 0;
+    if (TMA) {
+        if (producer) {
 #pragma unroll
-    for (int i = 0; i < kStages - 1; ++i) {
-        if (i < ngroups) stage_fill<BITS>(plan, (size_t)i * stride, first + i * stride, last, ring + i * G::kStageB);
-        cp_async_commit();
+            for (int i = 0; i < kStages; ++i) {
+                mbar_init(full0 + 8 * i, 1);
+                mbar_init(empty0 + 8 * i, kWarps);
+            }
+            asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+#pragma unroll
+            for (int i = 0; i < kStages - 1; ++i)
+                if (i < ntiles) tma_tile_fill<BITS>(maps, rings_base + i * G::kTileB, full0 + 8 * i, trow0 + i * stride);
+        }
+        // the other threads first touch a barrier after the block-wide barriers of the query prologue
+    } else {
+#pragma unroll
+        for (int i = 0; i < kStages - 1; ++i) {
+            if (i < ngroups) stage_fill<BITS>(plan, (size_t)i * stride, first + i * stride, last, ring + i * G::kStageB);
+            cp_async_commit();
+        }
     }
-    uint32_t st = ring;                                        // stage being consumed
-    uint32_t st_fill = ring + (kStages - 1) * G::kStageB;      // stage being refilled
+    uint32_t st = ring;                                        // stage being consumed (this warp's K rows)
+    uint32_t st_fill = TMA ? rings_base + (kStages - 1) * G::kTileB : ring + (kStages - 1) * G::kStageB;   // stage being refilled
     size_t fill_row = (size_t)(kStages - 1) * stride;
+    // TMA: barrier offset (8 x stage) of st / of st_fill, phase of st's full barrier, phase of st_fill's empty barrier
+    uint32_t boff = 0, boff_fill = 8 * (kStages - 1), parity = 0, eparity = 1;
+    bool stage_ok = true;
 
     // per-thread shared-memory offsets inside a stage
     uint32_t koff[4], voff[4];
@@ -298,8 +404,8 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a) {
         const int tok = 8 * ((lane >> 3) & 1) + (lane & 7), blk = lane >> 4;
         koff[0] = tok * 64 + ((blk ^ ((tok >> 1) & 3)) << 4);
         koff[1] = koff[0] ^ 32;                      // blocks 2, 3: piece index ^ 2
-        voff[0] = G::kIdxB + koff[0];
-        voff[1] = G::kIdxB + koff[1];
+        voff[0] = kVD + koff[0];
+        voff[1] = kVD + koff[1];
         koff[2] = koff[3] = voff[2] = voff[3] = 0;
     } else {
         // K: the 24 bits at byte 3j of block b;  V: the 12 bits at bit 12n of block b
@@ -312,13 +418,12 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a) {
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
             koff[b] = n * 48 + 12 * b + 4 * kw0;                                // token n (+8o: +384)
-            voff[b] = G::kIdxB + (2 * j) * 48 + 12 * b + 4 * vw0;               // token 2j (+e: +48, +8o: +384)
+            voff[b] = kVD + (2 * j) * 48 + 12 * b + 4 * vw0;               // token 2j (+e: +48, +8o: +384)
         }
     }
     constexpr uint32_t kOct = 8 * G::kRowB;                                     // 8 token rows
     constexpr uint32_t kRow = G::kRowB;
-    const uint32_t scoff = 2 * G::kIdxB + (2 * j) * 8;                          // scales of token 2j (+e: +8, +8o: +64)
-    const uint32_t lut_base = BITS == 3 ? (((uint32_t)__cvta_generic_to_shared(s_dyn) + 8191u) & ~8191u) : 0u;
+    const uint32_t scoff = sdelta + (2 * j) * 8;                          // scales of token 2j (+e: +8, +8o: +64)
     const uint32_t lut = lut_base + lane * 4;
 
     if (BITS == 3) {
@@ -371,14 +476,31 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) o[b][m][i] = 0.0f;
 
-    for (int it = 0; it < ngroups; ++it) {
+    for (int it = 0; it < nsteps; ++it) {
         const int gs = first + it * stride;
-        if (it + kStages - 1 < ngroups) stage_fill<BITS>(plan, fill_row, gs + (kStages - 1) * stride, last, st_fill);
-        cp_async_commit();
-        fill_row += stride;
-        st_fill = (st_fill + G::kStageB == ring + G::kRingB) ? ring : st_fill + G::kStageB;
-        cp_async_wait<kStages - 1>();
-        __syncwarp();
+        if (TMA) {
+            // A warp whose 16 rows of the tile lie past the end of the partition runs the step on them all
+            // the same: every such token is masked below and contributes exactly nothing.
+            if (producer && it + kStages - 1 < ntiles) {
+                // refill the stage of tile it - 1 once all four warps have released it
+                if (it >= 1 && !mbar_wait(empty0 + boff_fill, eparity)) stage_ok = false;
+                else tma_tile_fill<BITS>(maps, st_fill, full0 + boff_fill, trow0 + (it + kStages - 1) * stride);
+            }
+            __syncwarp();
+            if (boff_fill + 8 == 8 * kStages) { boff_fill = 0; eparity ^= 1u; } else boff_fill += 8;
+            st_fill = (st_fill + kPitch == rings_base + kStages * kPitch) ? rings_base : st_fill + kPitch;
+            if (!mbar_wait(full0 + boff, parity)) {   // never expected: give up on this partition and say so
+                stage_ok = false;
+                break;
+            }
+        } else {
+            if (it + kStages - 1 < ngroups) stage_fill<BITS>(plan, fill_row, gs + (kStages - 1) * stride, last, st_fill);
+            cp_async_commit();
+            fill_row += stride;
+            st_fill = (st_fill + G::kStageB == ring + G::kRingB) ? ring : st_fill + G::kStageB;
+            cp_async_wait<kStages - 1>();
+            __syncwarp();
+        }
 
         // ---- S^T = Q~ K^T ----
         uint32_t kw[2][4];   // 4-bit: [block pair][octet | block parity << 1] -> word j of token n of the octet
@@ -416,12 +538,20 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a) {
                 s[o8][1] = fmaf(k1, acc[1] + acc[3], s[o8][1]);
             }
         }
-        if (gs + kGroup > a.kv_len) {   // ragged tail: tokens past the end get zero weight
+        if (gs + kGroup > t_end) {   // ragged tail: tokens past the end (of the sequence, or of the partition) get zero weight
+            if (TMA) {
+                // the tensor copies brought whatever lies behind the last token: clear those scale rows, so
+                // that a zero probability never meets an Inf or NaN scale
+                const int t = lane & 15;
+                if (gs + t >= t_end)
+                    asm volatile("st.shared.v2.u32 [%0], {%1, %1};\n" ::"r"(st + sdelta + (lane >> 4) * kSD + t * 8), "r"(0u) : "memory");
+                __syncwarp();
+            }
 #pragma unroll
             for (int o8 = 0; o8 < 2; ++o8)
 #pragma unroll
                 for (int e = 0; e < 2; ++e)
-                    if (gs + 8 * o8 + 2 * j + e > last) s[o8][e] = kNegBig;
+                    if (gs + 8 * o8 + 2 * j + e >= t_end) s[o8][e] = kNegBig;
         }
         // ---- online softmax for head n (the quad holds its 16 tokens) ----
         float mx = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
@@ -461,7 +591,7 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a) {
         __half2 sv[2][4];   // |scale| of (token 2j, token 2j+1) of the octet, per block
 #pragma unroll
         for (int o8 = 0; o8 < 2; ++o8) {
-            const uint2 va = lds64(st + 128 + scoff + o8 * 64), vb = lds64(st + 128 + scoff + o8 * 64 + 8);
+            const uint2 va = lds64(st + kSD + scoff + o8 * 64), vb = lds64(st + kSD + scoff + o8 * 64 + 8);
             sv[o8][0] = u32_as_h2(__byte_perm(va.x, vb.x, 0x5410) & 0x7FFF7FFFu);
             sv[o8][1] = u32_as_h2(__byte_perm(va.x, vb.x, 0x7632) & 0x7FFF7FFFu);
             sv[o8][2] = u32_as_h2(__byte_perm(va.y, vb.y, 0x5410) & 0x7FFF7FFFu);
@@ -516,9 +646,17 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a) {
             }
         }
         __syncwarp();   // every lane is done with this stage before it is refilled
-        st = (st + G::kStageB == ring + G::kRingB) ? ring : st + G::kStageB;
+        st = (st + kPitch == ring + kStages * kPitch) ? ring : st + kPitch;
+        if (TMA) {
+            if (lane == 0) mbar_arrive(empty0 + boff);   // this warp releases its rows of the tile
+            if (boff + 8 == 8 * kStages) { boff = 0; parity ^= 1u; } else boff += 8;
+        }
     }
-    cp_async_wait<0>();
+    if (TMA) {
+        if (!stage_ok && lane == 0) atomicAdd(&g_stage_timeouts, 1u);
+    } else {
+        cp_async_wait<0>();
+    }
     __syncthreads();    // all rings idle: the memory is reused for the merge
 
     // ---- merge the four warps (scores are in log2 units; partials are stored in natural units) ----
@@ -609,25 +747,81 @@ struct LutCache {
 std::mutex g_lut_mutex;
 LutCache g_lut_cache[2][2];   // [norm_mode][all_outlier]
 
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda).
+PFN_cuTensorMapEncodeTiled tensor_map_encoder() {
+    static PFN_cuTensorMapEncodeTiled fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<PFN_cuTensorMapEncodeTiled>(p);
+    }();
+    return fn;
+}
+
+// Tensor maps over the packed cache of one launch.  Index arrays: 2-D [row bytes, token rows of all KV
+// heads], box = one 64-token tile, 64-byte swizzle for 64-byte rows.  Scale arrays: 1-D, one 8-byte
+// element per token row.  False when the layout does not meet the copy engine's alignment rules: a copy
+// starts at token row kvh * kv_stride + 64 k, which must be a multiple of 16 bytes in the scale array.
 template <int BITS>
-int launch(const MmaArgs& a, int g, int q_dtype, dim3 grid, cudaStream_t s) {
-    const size_t dyn = BITS == 3 ? 16384 : 0;   // 8 KB table + slack for its 8 KB alignment
-#define TQB_LAUNCH_MMA(QT)                                                                  \
-    do {                                                                                    \
-        if (dyn) {  /* static + dynamic shared memory passes 48 KB: opt in */               \
-            cudaError_t e = g <= 4                                                          \
-                ? cudaFuncSetAttribute(decode_mma_kernel<QT, BITS, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn)  \
-                : cudaFuncSetAttribute(decode_mma_kernel<QT, BITS, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn); \
-            if (e != cudaSuccess) { set_cuda_error(e); return TQB_ERR_CUDA; }               \
-        }                                                                                   \
-        if (g <= 4) decode_mma_kernel<QT, BITS, true><<<grid, kThreads, dyn, s>>>(a);       \
-        else decode_mma_kernel<QT, BITS, false><<<grid, kThreads, dyn, s>>>(a);             \
+bool make_tma_maps(const MmaArgs& a, TmaMaps& m) {
+    using G = Geo<BITS>;
+    PFN_cuTensorMapEncodeTiled enc = tensor_map_encoder();
+    if (!enc) return false;
+    const unsigned long long rows = (unsigned long long)a.hkv * (unsigned long long)a.kv_stride;
+    if ((a.kv_stride & 1) || rows >= (1ull << 31)) return false;
+    if (((uintptr_t)a.kb % 16) || ((uintptr_t)a.vb % 16) || ((uintptr_t)a.ks % 16) || ((uintptr_t)a.vs % 16)) return false;
+    const cuuint64_t idx_dim[2] = {(cuuint64_t)G::kRowB, rows};
+    const cuuint64_t idx_stride[1] = {(cuuint64_t)G::kRowB};
+    const cuuint32_t idx_box[2] = {(cuuint32_t)G::kRowB, (cuuint32_t)(kWarps * kGroup)};
+    const cuuint32_t ones[2] = {1, 1};
+    const CUtensorMapSwizzle sw = BITS == 4 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE;
+    const cuuint64_t sc_dim[1] = {rows};
+    const cuuint32_t sc_box[1] = {(cuuint32_t)(kWarps * kGroup)};
+    bool ok = true;
+    ok = ok && enc(&m.k, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(a.kb), idx_dim, idx_stride, idx_box, ones,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    ok = ok && enc(&m.v, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(a.vb), idx_dim, idx_stride, idx_box, ones,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    ok = ok && enc(&m.ks, CU_TENSOR_MAP_DATA_TYPE_UINT64, 1, const_cast<uint16_t*>(a.ks), sc_dim, idx_stride, sc_box, ones,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    ok = ok && enc(&m.vs, CU_TENSOR_MAP_DATA_TYPE_UINT64, 1, const_cast<uint16_t*>(a.vs), sc_dim, idx_stride, sc_box, ones,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    return ok;
+}
+
+template <typename QT, int BITS, bool NSPLIT, bool TMA>
+int launch_one(const MmaArgs& a, const TmaMaps& maps, dim3 grid, cudaStream_t s) {
+    using G = Geo<BITS>;
+    // dynamic shared memory: the stage rings (1 KB alignment slack), for 3-bit after the 8 KB table and its slack
+    const size_t dyn = BITS == 3 ? 16384 + kWarps * G::kRingB : 1024 + kWarps * G::kRingB;
+    cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<QT, BITS, NSPLIT, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn);
+    if (e != cudaSuccess) { set_cuda_error(e); return TQB_ERR_CUDA; }
+    decode_mma_kernel<QT, BITS, NSPLIT, TMA><<<grid, kThreads, dyn, s>>>(a, maps);
+    return check_launch(s);
+}
+
+template <int BITS>
+int launch(const MmaArgs& a, int g, int q_dtype, bool allow_tma, dim3 grid, cudaStream_t s) {
+    TmaMaps maps;
+    memset(&maps, 0, sizeof(maps));
+    const bool tma = allow_tma && make_tma_maps<BITS>(a, maps);
+#define TQB_LAUNCH_MMA(QT)                                                                       \
+    do {                                                                                         \
+        if (g <= 4) return tma ? launch_one<QT, BITS, true, true>(a, maps, grid, s)              \
+                               : launch_one<QT, BITS, true, false>(a, maps, grid, s);            \
+        return tma ? launch_one<QT, BITS, false, true>(a, maps, grid, s)                         \
+                   : launch_one<QT, BITS, false, false>(a, maps, grid, s);                       \
     } while (0)
     if (q_dtype == TQB_F32) TQB_LAUNCH_MMA(float);
     else if (q_dtype == TQB_F16) TQB_LAUNCH_MMA(__half);
     else TQB_LAUNCH_MMA(__nv_bfloat16);
 #undef TQB_LAUNCH_MMA
-    return check_launch(s);
 }
 
 }  // namespace
@@ -671,13 +865,14 @@ int launch_decode_mma(const tqb_decode_params* p, int num_partitions, float* par
         if (e != cudaSuccess) { set_cuda_error(e); return TQB_ERR_CUDA; }
     }
     dim3 grid(p->num_kv_heads, num_partitions);
+    const bool allow_tma = (p->flags & TQB_DECODE_TMA) != 0;
     const float log2e = 1.4426950408889634f;
     if (pqo4) {
         const float R = 2.1573f;
         const float grid_step = (2.0f * R) / 15.0f;   // codebooks.rs:64-67
         a.qk_const = p->softmax_scale * log2e * grid_step;
         a.v_const = grid_step;
-        return launch<4>(a, g, p->q_dtype, grid, s);
+        return launch<4>(a, g, p->q_dtype, allow_tma, grid, s);
     }
     {
         std::lock_guard<std::mutex> lock(g_lut_mutex);
@@ -695,7 +890,13 @@ int launch_decode_mma(const tqb_decode_params* p, int num_partitions, float* par
         a.v_const = lc.kappa;
         for (int i = 0; i < 8; ++i) a.lut[i] = lc.lut[i];
     }
-    return launch<3>(a, g, p->q_dtype, grid, s);
+    return launch<3>(a, g, p->q_dtype, allow_tma, grid, s);
 }
 
 }  // namespace tqb
+
+extern "C" long long tqb_decode_stage_timeouts(void) {
+    unsigned v = 0;
+    if (cudaMemcpyFromSymbol(&v, tqb::g_stage_timeouts, sizeof(v)) != cudaSuccess) return -1;
+    return (long long)v;
+}
