@@ -256,7 +256,7 @@ def run_ours(args):
                          "what": "per-layer bulk fill: 2 x 64 x 8 x 8192 bf16 vectors -> PQO4 (328 B per vector in+out)"},
             "clocks": clocks,
         }
-        if not args.no_cpu:
+        if not args.no_cpu and world == 1:   # the CPU leg runs at N = 1 only
             line["cpu_baseline"] = cpu_baseline(max_seconds=20.0)
         tr = os.path.join(ROOT, "profiles", "decode_traffic.json")
         if os.path.exists(tr):
