@@ -246,7 +246,7 @@ def run_ours(args):
             "pct_of_hbm_peak": round(100 * value / (peak * world), 2),
             "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "tokens_per_s": round(B * world * args.steps / (e2e_ms * 1e-3), 1)},
-            "gpu_launches": args.steps * L * 2,   # per layer: one K+V append, one decode kernel with the merge inside
+            "gpu_launches": args.steps * L,   # per layer: one kernel (append of the new token, attention, split-K merge)
             "roofline": {"bound": "hbm", "kernel": "decode attention (split-K pass)", "achieved": round(achieved, 1),
                          "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4), "traffic": None,
                          "peak_source": peak_src, "launch_us": round(launch_ms * 1e3, 1),

@@ -255,6 +255,13 @@ typedef struct tqb_decode_params {
     int32_t num_partitions;       /* 0 = let the library choose */
     float softmax_scale;
     int32_t flags;                /* TQB_DECODE_* bits */
+    /* Optional fused append (src/cache/pqo.rs:106-174 quantizes the new token, stores it, then attends):
+     * device [num_kv_heads, head_dim] of q_dtype each, or both NULL.  The vectors are quantized and written
+     * to row kv_len - 1 of every KV head (kv_len counts the new token; the cache arrays are written
+     * although declared const) before attention reads them - inside the attention kernel for the
+     * tensor-core shapes, by one extra launch otherwise. */
+    const void *append_k;
+    const void *append_v;
 } tqb_decode_params;
 
 /* flags: stop after the split-K pass and leave the per-partition (max, sum, out) partials in

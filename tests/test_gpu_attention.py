@@ -133,6 +133,37 @@ def test_tensor_copy_staging_equals_cp_async_staging(bits, g, L, stride):
     assert lib.tqb_decode_stage_timeouts() == 0
 
 
+@pytest.mark.parametrize("bits,nm,ob", [(4, 0, -1), (3, 0, -1), (3, 1, -1), (4, 0, 2)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("L", [1, 64, 65, 1000, 4097])
+def test_fused_append_equals_append_then_attend(bits, nm, ob, dtype, L):
+    # The new token's K/V rows quantized inside the attention call (in the kernel for the all-outlier MaxNorm
+    # format, by a launch of its own otherwise) against quantize-then-attend: same cache bytes, same output.
+    rng = np.random.default_rng(bits * 100 + nm * 10 + L)
+    hkv, g, stride = 3, 4, L + 6
+    mode = tq.QuantNormMode(nm)
+    ki, ks, vi, vs = (dev(x) for x in make_cache(rng, hkv, L - 1, stride, bits, nm=nm, ob=ob))
+    ks, vs = ks.view(torch.int16), vs.view(torch.int16)
+    newk = torch.from_numpy(rng.standard_normal((hkv, 128)).astype(np.float32)).to(dtype).cuda()
+    newv = torch.from_numpy(rng.standard_normal((hkv, 128)).astype(np.float32)).to(dtype).cuda()
+    q = torch.from_numpy((rng.standard_normal((hkv * g, 128)) / np.sqrt(128)).astype(np.float32)).to(dtype).cuda()
+    # reference: separate append, then attention
+    ref = [t.clone() for t in (ki, ks, vi, vs)]
+    tq.block_quantize(newk, bits, mode, ob, out=(ref[0], ref[1]), rows_per_group=1, group_stride=stride, row_offset=L - 1)
+    tq.block_quantize(newv, bits, mode, ob, out=(ref[2], ref[3]), rows_per_group=1, group_stride=stride, row_offset=L - 1)
+    want = tq.decode_attention(q, *ref, L, bits, 0.0884, norm_mode=mode, outlier_blocks=ob)
+    for parts in (0, 1, 3):
+        got_cache = [t.clone() for t in (ki, ks, vi, vs)]
+        got = tq.decode_attention(q, *got_cache, L, bits, 0.0884, norm_mode=mode, outlier_blocks=ob, num_partitions=parts,
+                                  append=(newk, newv))
+        for a, b in zip(got_cache, ref):
+            assert torch.equal(a, b)
+        if parts == 0:
+            assert torch.equal(got, want)
+        else:
+            assert (got.float() - want.float()).abs().max() < (1e-2 if dtype == torch.bfloat16 else 1e-5)
+
+
 @pytest.mark.parametrize("bits,nm,ob", [(3, 0, -1), (3, 1, -1), (3, 0, 0), (4, 0, -1)])
 def test_tensor_core_kernel_sharp_softmax(bits, nm, ob):
     # large logits: a handful of tokens carry all the weight, so element errors are not averaged away.

@@ -35,7 +35,7 @@ class TqbDecodeParams(ctypes.Structure):
                 ("qjl_enabled", c_int32), ("q_dtype", c_int32), ("out_dtype", c_int32), ("bits", c_int32),
                 ("head_dim", c_int32), ("norm_mode", c_int32), ("outlier_blocks", c_int32), ("num_q_heads", c_int32),
                 ("num_kv_heads", c_int32), ("kv_len", c_int32), ("kv_stride", c_int32), ("num_partitions", c_int32),
-                ("softmax_scale", c_float), ("flags", c_int32)]
+                ("softmax_scale", c_float), ("flags", c_int32), ("append_k", c_void_p), ("append_v", c_void_p)]
 
 
 def declared_symbols(header_path=HEADER_PATH):

@@ -512,7 +512,7 @@ def block_dequantize(indices, scales, bits, head_dim, norm_mode=QuantNormMode.Ma
 
 def decode_attention(q, k_idx, k_sc, v_idx, v_sc, kv_len, bits, softmax_scale, norm_mode=QuantNormMode.MaxNorm,
                      outlier_blocks=ALL_BLOCKS, num_partitions=0, out_dtype=None, return_lse=False, qjl=None,
-                     scratch=None, out=None, partials_only=False, force_general=False, tma=False):
+                     scratch=None, out=None, partials_only=False, force_general=False, tma=False, append=None):
     """Fused decode attention over packed K/V.
 
     q [Hq, D]; k_idx/v_idx [Hkv, kv_stride, D*bits/8]; k_sc/v_sc [Hkv, kv_stride, D/32].
@@ -541,6 +541,10 @@ def decode_attention(q, k_idx, k_sc, v_idx, v_sc, kv_len, bits, softmax_scale, n
     p.num_q_heads, p.num_kv_heads, p.kv_len, p.kv_stride = hq, hkv, kv_len, stride
     p.num_partitions, p.softmax_scale = parts, softmax_scale
     p.flags = (1 if partials_only else 0) | (2 if force_general else 0) | (8 if tma else 0)
+    if append is not None:   # (k, v): the new token's vectors [Hkv, D] in q's dtype, written to row kv_len - 1
+        ak, av = (t.contiguous() for t in append)
+        assert ak.dtype == q.dtype and av.dtype == q.dtype
+        p.append_k, p.append_v = ak.data_ptr(), av.data_ptr()
     check(lib.tqb_decode_attention(ctypes.byref(p), _stream()))
     return (out, lse) if return_lse else out
 

@@ -391,6 +391,8 @@ int tqb_decode_attention(const tqb_decode_params* p, tqb_stream_t stream) {
     if (p->kv_len > 0 && (!p->k_indices || !p->k_scales || !p->v_indices || !p->v_scales)) return TQB_ERR_NULL_POINTER;
     if (p->qjl_enabled && (!p->qjl_signs || !p->qjl_norms || !p->rq)) return TQB_ERR_NULL_POINTER;
     if (p->lse_out && p->out_dtype != TQB_F32) return TQB_ERR_INVALID_ARGUMENT;
+    if ((p->append_k == nullptr) != (p->append_v == nullptr)) return TQB_ERR_NULL_POINTER;
+    if (p->append_k != nullptr && p->kv_len < 1) return TQB_ERR_RANGE_OUT_OF_BOUNDS;
     if (((uintptr_t)p->k_indices % 4) || ((uintptr_t)p->v_indices % 4) || ((uintptr_t)p->scratch % 16) ||
         ((uintptr_t)p->qjl_signs % 4))
         return TQB_ERR_MISALIGNED;
@@ -419,12 +421,32 @@ int tqb_decode_attention(const tqb_decode_params* p, tqb_stream_t stream) {
     a.softmax_scale = p->softmax_scale;
     a.sign_mag = cpu_sign_magnitude();
     const bool partials_only = (p->flags & TQB_DECODE_PARTIALS_ONLY) != 0;
+    tqb_decode_params local = *p;
+    // The append as a launch of its own (shapes the tensor-core kernels do not cover).
+    auto append_separately = [&]() -> int {
+        int rc = tqb_block_quantize_pair(p->bits, p->head_dim, p->norm_mode, p->outlier_blocks, p->append_k, p->append_v,
+                                         p->q_dtype, p->num_kv_heads, 0, const_cast<uint8_t*>(p->k_indices),
+                                         const_cast<uint16_t*>(p->k_scales), const_cast<uint8_t*>(p->v_indices),
+                                         const_cast<uint16_t*>(p->v_scales), 1, p->kv_stride, p->kv_len - 1, stream);
+        local.append_k = local.append_v = nullptr;
+        return rc;
+    };
     if (!(p->flags & TQB_DECODE_FORCE_GENERAL)) {
         // tensor-core kernels for the shapes they cover; everything else takes the general kernel
         // (the merge runs inside the kernel, in the CTA that finishes a KV head last)
-        st = launch_decode_mma(p, P, a.partial_out, a.partial_max, a.partial_sum, a.sign_mag,
+        st = launch_decode_mma(&local, P, a.partial_out, a.partial_max, a.partial_sum, a.sign_mag,
                                partials_only ? nullptr : tickets, (p->flags & TQB_DECODE_TICKETS_ZERO) != 0, as_stream(stream));
+        if (st == TQB_ERR_UNSUPPORTED && local.append_k != nullptr) {
+            st = append_separately();
+            if (st != TQB_OK) return st;
+            st = launch_decode_mma(&local, P, a.partial_out, a.partial_max, a.partial_sum, a.sign_mag,
+                                   partials_only ? nullptr : tickets, (p->flags & TQB_DECODE_TICKETS_ZERO) != 0, as_stream(stream));
+        }
         if (st != TQB_ERR_UNSUPPORTED) return st;
+    }
+    if (local.append_k != nullptr) {
+        st = append_separately();
+        if (st != TQB_OK) return st;
     }
     return run_decode(a, cn, co, p->q_dtype, p->out, p->out_dtype, p->lse_out, as_stream(stream), partials_only);
 }

@@ -37,6 +37,7 @@
 
 #include "tqb_common.cuh"
 #include "tqb_merge.cuh"
+#include "tqb_pqo_quant.cuh"
 
 namespace tqb {
 namespace {
@@ -67,6 +68,11 @@ struct MmaArgs {
     void* out;
     float* lse_out;
     int out_dtype;
+    // fused append: the new token's K / V vectors [hkv, 128] of the query dtype (nullptr: off).  The CTA whose
+    // partition holds token kv_len - 1 quantizes them into row kv_len - 1 before it starts streaming.
+    const void* app_k;
+    const void* app_v;
+    float outer_centroid;
 };
 
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -323,7 +329,8 @@ __device__ __forceinline__ void stage_fill(const FillPlan& f, size_t row_off, in
 // off any single warp's critical path; the shared tile ring couples them through its barriers.  So cp.async
 // is the default and TMA is opt-in (TQB_DECODE_TMA).
 template <typename QT, int BITS, bool NSPLIT, bool TMA>
-__global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, const __grid_constant__ TmaMaps maps) {
+__global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, const __grid_constant__ TmaMaps maps,
+                                                                 const __grid_constant__ Codebook app_cb) {
     using G = Geo<BITS>;
     // Dynamic shared memory: [3-bit only: lookup table at an 8 KB-aligned address, so that a table address
     // is formed by OR-ing (index << 7) into the lane's base with one LOP3][stage rings, 1 KB-aligned].
@@ -354,6 +361,29 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
     const int first = t_begin + warp * kGroup;
     const int stride = kWarps * kGroup;
     const int ngroups = first < t_end ? (t_end - first + stride - 1) / stride : 0;
+    if (a.app_k != nullptr && last >= t_begin && last < t_end) {
+        // Fused append.  Only this CTA ever reads row `last` of this KV head, so a block-wide barrier after
+        // the stores is all the ordering needed.  One thread per 32-block: warp w takes block w of K (lane 0)
+        // and of V (lane 1); same code, same bits as block_quantize_pqo_kernel.
+        if (lane < 2) {
+            const bool is_v = lane == 1;
+            const QT* src = reinterpret_cast<const QT*>(is_v ? a.app_v : a.app_k) + (size_t)kvh * kD + warp * 32;
+            uint32_t w[4];
+            const float scale = pqo_quantize_block<QT, BITS>(src, app_cb, a.outer_centroid, w);
+            const size_t row = row0 + last;
+            uint8_t* bp = const_cast<uint8_t*>(is_v ? a.vb : a.kb) + row * G::kRowB + warp * (4 * BITS);
+            if (BITS == 4) {
+                *reinterpret_cast<uint4*>(bp) = make_uint4(w[0], w[1], w[2], w[3]);
+            } else {
+                uint32_t* wp = reinterpret_cast<uint32_t*>(bp);
+                wp[0] = w[0]; wp[1] = w[1]; wp[2] = w[2];
+            }
+            const_cast<uint16_t*>(is_v ? a.vs : a.ks)[row * 4 + warp] = f32_to_f16_bits(-scale);   // outlier blocks store -scale
+        }
+        __threadfence_block();
+        if (TMA) asm volatile("fence.proxy.async;\n" ::: "memory");   // the tensor copies read through the async proxy
+        __syncthreads();
+    }
     // cp.async: every warp owns a ring of 16-token stages.  TMA: the CTA owns a ring of 64-token tiles and
     // `ring` / `st` address this warp's K rows inside a tile.
     constexpr uint32_t kPitch = TMA ? G::kTileB : G::kStageB;           // distance between stages
@@ -796,27 +826,27 @@ bool make_tma_maps(const MmaArgs& a, TmaMaps& m) {
 }
 
 template <typename QT, int BITS, bool NSPLIT, bool TMA>
-int launch_one(const MmaArgs& a, const TmaMaps& maps, dim3 grid, cudaStream_t s) {
+int launch_one(const MmaArgs& a, const TmaMaps& maps, const Codebook& app_cb, dim3 grid, cudaStream_t s) {
     using G = Geo<BITS>;
     // dynamic shared memory: the stage rings (1 KB alignment slack), for 3-bit after the 8 KB table and its slack
     const size_t dyn = BITS == 3 ? 16384 + kWarps * G::kRingB : 1024 + kWarps * G::kRingB;
     cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<QT, BITS, NSPLIT, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn);
     if (e != cudaSuccess) { set_cuda_error(e); return TQB_ERR_CUDA; }
-    decode_mma_kernel<QT, BITS, NSPLIT, TMA><<<grid, kThreads, dyn, s>>>(a, maps);
+    decode_mma_kernel<QT, BITS, NSPLIT, TMA><<<grid, kThreads, dyn, s>>>(a, maps, app_cb);
     return check_launch(s);
 }
 
 template <int BITS>
-int launch(const MmaArgs& a, int g, int q_dtype, bool allow_tma, dim3 grid, cudaStream_t s) {
+int launch(const MmaArgs& a, int g, int q_dtype, bool allow_tma, const Codebook& app_cb, dim3 grid, cudaStream_t s) {
     TmaMaps maps;
     memset(&maps, 0, sizeof(maps));
     const bool tma = allow_tma && make_tma_maps<BITS>(a, maps);
 #define TQB_LAUNCH_MMA(QT)                                                                       \
     do {                                                                                         \
-        if (g <= 4) return tma ? launch_one<QT, BITS, true, true>(a, maps, grid, s)              \
-                               : launch_one<QT, BITS, true, false>(a, maps, grid, s);            \
-        return tma ? launch_one<QT, BITS, false, true>(a, maps, grid, s)                         \
-                   : launch_one<QT, BITS, false, false>(a, maps, grid, s);                       \
+        if (g <= 4) return tma ? launch_one<QT, BITS, true, true>(a, maps, app_cb, grid, s)              \
+                               : launch_one<QT, BITS, true, false>(a, maps, app_cb, grid, s);            \
+        return tma ? launch_one<QT, BITS, false, true>(a, maps, app_cb, grid, s)                         \
+                   : launch_one<QT, BITS, false, false>(a, maps, app_cb, grid, s);                       \
     } while (0)
     if (q_dtype == TQB_F32) TQB_LAUNCH_MMA(float);
     else if (q_dtype == TQB_F16) TQB_LAUNCH_MMA(__half);
@@ -856,6 +886,15 @@ int launch_decode_mma(const tqb_decode_params* p, int num_partitions, float* par
     const int step = kWarps * kGroup;
     a.part_size = ((p->kv_len + num_partitions - 1) / num_partitions + step - 1) / step * step;
     a.sign_mag = sign_mag;
+    // fused append: the one-thread-per-block quantizer covers the all-outlier MaxNorm format
+    Codebook app_cb{};
+    if (p->append_k != nullptr) {
+        if (!(p->norm_mode == TQB_MAXNORM && all_outlier) || !block_codebook(p->bits, p->norm_mode, app_cb)) return TQB_ERR_UNSUPPORTED;
+        if (((uintptr_t)p->append_k % 16) || ((uintptr_t)p->append_v % 16)) return TQB_ERR_UNSUPPORTED;
+        a.app_k = p->append_k;
+        a.app_v = p->append_v;
+        a.outer_centroid = app_cb.c[app_cb.n - 1];   // precomputed/mod.rs:78
+    }
     a.counters = counters;
     a.out = p->out;
     a.lse_out = p->lse_out;
@@ -872,7 +911,7 @@ int launch_decode_mma(const tqb_decode_params* p, int num_partitions, float* par
         const float grid_step = (2.0f * R) / 15.0f;   // codebooks.rs:64-67
         a.qk_const = p->softmax_scale * log2e * grid_step;
         a.v_const = grid_step;
-        return launch<4>(a, g, p->q_dtype, allow_tma, grid, s);
+        return launch<4>(a, g, p->q_dtype, allow_tma, app_cb, grid, s);
     }
     {
         std::lock_guard<std::mutex> lock(g_lut_mutex);
@@ -890,7 +929,7 @@ int launch_decode_mma(const tqb_decode_params* p, int num_partitions, float* par
         a.v_const = lc.kappa;
         for (int i = 0; i < 8; ++i) a.lut[i] = lc.lut[i];
     }
-    return launch<3>(a, g, p->q_dtype, allow_tma, grid, s);
+    return launch<3>(a, g, p->q_dtype, allow_tma, app_cb, grid, s);
 }
 
 }  // namespace tqb

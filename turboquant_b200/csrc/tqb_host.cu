@@ -206,8 +206,21 @@ struct tqb_pqo_cache {
         return TQB_OK;
     }
 
+    // One decode step of a layer: append the new token's K / V rows (device, one vector per KV head) and
+    // attend, in a single tqb_decode_attention call (the append runs inside the attention kernel where the
+    // tensor-core kernels apply).
+    int append_and_attend(int layer, const void* k_dev, const void* v_dev, const void* q_dev, int dtype, int num_q_heads,
+                          float softmax_scale, void* out_dev, cudaStream_t s) {
+        const int64_t old_len = layers[layer].len;
+        TQB_TRY(ensure_capacity(layer, old_len + 1, s));
+        Layer& l = layers[layer];
+        l.len = old_len + 1;
+        l.active = true;
+        return attend(layer, q_dev, dtype, num_q_heads, softmax_scale, out_dev, dtype, nullptr, s, k_dev, v_dev);
+    }
+
     int attend(int layer, const void* q_dev, int dtype, int num_q_heads, float softmax_scale, void* out_dev, int out_dtype,
-               float* lse_out, cudaStream_t s) {
+               float* lse_out, cudaStream_t s, const void* append_k = nullptr, const void* append_v = nullptr) {
         Layer& l = layers[layer];
         tqb_decode_params p{};
         p.q = q_dev;
@@ -228,6 +241,8 @@ struct tqb_pqo_cache {
         p.scratch = scratch.p;
         p.scratch_bytes = scratch.bytes;
         p.flags = TQB_DECODE_TICKETS_ZERO;
+        p.append_k = append_k;
+        p.append_v = append_v;
         return tqb_decode_attention(&p, s);
     }
     int ticket_heads = -1;   // head count the zeroed ticket area of `scratch` was sized for
@@ -306,10 +321,7 @@ int tqb_pqo_cache_decode(tqb_pqo_cache* c, int32_t layer, const void* k, const v
     const size_t esz = dtype_size(dtype);
     const size_t kv_bytes = (size_t)c->heads * c->cfg.head_dim * esz;
     const size_t q_bytes = (size_t)c->cfg.batch * num_q_heads * c->cfg.head_dim * esz;
-    if (!host_buffers) {
-        TQB_TRY(c->quantize_and_store(layer, k, v, dtype, 1, s));
-        return c->attend(layer, q, dtype, num_q_heads, softmax_scale, out, dtype, nullptr, s);
-    }
+    if (!host_buffers) return c->append_and_attend(layer, k, v, q, dtype, num_q_heads, softmax_scale, out, s);
     // Host buffers: inputs go up on one copy stream into one of two staging slots, the kernels run on
     // the caller's stream once the slot is filled, and the result goes down on a second copy stream
     // once they are done, so the next call's inputs travel while this call's kernels run.  A slot is
@@ -332,8 +344,7 @@ int tqb_pqo_cache_decode(tqb_pqo_cache* c, int32_t layer, const void* k, const v
     TQB_CUDA(cudaMemcpyAsync(sl.q.p, q, q_bytes, cudaMemcpyHostToDevice, c->copy_stream));
     TQB_CUDA(cudaEventRecord(sl.in_ready, c->copy_stream));
     TQB_CUDA(cudaStreamWaitEvent(s, sl.in_ready, 0));
-    TQB_TRY(c->quantize_and_store(layer, sl.k.p, sl.v.p, dtype, 1, s));
-    TQB_TRY(c->attend(layer, sl.q.p, dtype, num_q_heads, softmax_scale, sl.out.p, dtype, nullptr, s));
+    TQB_TRY(c->append_and_attend(layer, sl.k.p, sl.v.p, sl.q.p, dtype, num_q_heads, softmax_scale, sl.out.p, s));
     TQB_CUDA(cudaEventRecord(sl.compute_done, s));
     TQB_CUDA(cudaStreamWaitEvent(c->down_stream, sl.compute_done, 0));
     TQB_CUDA(cudaMemcpyAsync(out, sl.out.p, q_bytes, cudaMemcpyDeviceToHost, c->down_stream));
