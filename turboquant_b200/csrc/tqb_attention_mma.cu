@@ -5,23 +5,26 @@
 // V).  On the SIMT pipes that is more lane-instructions than the chip can issue, so the
 // QK^T and PV contractions go through mma.sync.m16n8k16 (f16 in, f32 accumulate) and the SIMT
 // pipes only unpack codes.  tcgen05 is not used: its operands must be staged in shared memory,
-// which would cost a shared-memory write per dequantized value, while mma.sync takes the
-// unpacked codes straight from registers.
+// which would cost a shared-memory write per dequantized value, and the per-(token, block) V scale
+// leaves its P V product only 8 useful rows of a 64-row MMA; mma.sync takes the unpacked codes
+// straight from registers.
 //
 // Layout of one warp step (16 tokens t0..t0+15, lane = 4*n + j):
-//   S^T = Q~ K^T :  M = query heads (rows 0..7: f16 hi part of q~, rows 8..15: its lo part),
-//       N = 8 tokens, K = 16 dims of ONE 32-block.  Lane (n, j) supplies, for token t0+8o+n and
-//       block b, the eight codes j*8..j*8+7 of the block; two MMAs per (octet o, block b).
-//       Because each MMA stays inside one block, the per-block scale |s| is applied to the f32
-//       accumulator (2 FMAs), not to the elements.
-//   O^T = V^T P' :  M = 16 dims of ONE block, N = 8 heads, K = 16 tokens.  The accumulator
-//       fragment of S^T (head n, tokens 2j, 2j+1) is exactly the B fragment of this MMA, so the
-//       probabilities never leave registers; the V scale is folded into them (P' = p |s_v|).
+//   S = K~ Q~^T :  M = 16 tokens (rows n and n + 8), N = 8 columns of rotated queries (group <= 4: the f16
+//       hi parts of heads 0..3, then their lo parts; else 8 heads, hi and lo in two MMAs), K = 16 dims of
+//       ONE 32-block.  Lane (n, j) supplies, for tokens t0+n and t0+8+n and block b, the eight codes
+//       j*8..j*8+7 of the block; two MMAs per block cover all 16 tokens.  Because each MMA stays inside one
+//       block, the per-block scale |s| is applied to the f32 accumulator (one FMA per token and column),
+//       not to the elements.  Softmax runs on (token n / n + 8, two heads per lane); the row maximum is
+//       reduced over the 8 lane groups n.
+//   O^T = V^T P' :  M = 16 dims of ONE block, N = 8 columns (as above), K = 16 tokens.  The probabilities
+//       (times the V scale, P' = p |s_v|) are transposed from (token rows, head columns) to the B fragment
+//       (tokens 2j, 2j+1 of column n) by movmatrix, one instruction per 8 x 8 block.
 //
 // Code -> f16:
-//   4-bit MaxNorm grid (codebooks.rs:63-73): centroid i = (2R/15)(i - 7.5).  Codes become the exact
-//   f16 integers i - 8 by the magic-number trick ((w & 0x000f000f) | 0x64006400 is the half2
-//   (1024 + i, 1024 + i')); the 0.5 offset is carried separately in f32.
+//   4-bit MaxNorm grid (codebooks.rs:63-73): centroid i = (2R/15)(i - 7.5).  A nibble masked into
+//   mantissa bits 1..4 (5..8) of 0x6400 reads 1024 + 2i (1024 + 32i); one HFMA2 with exactly
+//   representable constants turns it into the exact f16 value i - 7.5 (see nibbles_to_half2).
 //   3-bit (any codebook of 8 entries, or 4 entries stored at 3-bit width): a 64-entry half2 table
 //   indexed by two codes, replicated once per bank (entry e of lane l at word 32*e + l) so that
 //   every lookup is conflict-free.  The table holds centroid / kappa, where the f32 factor kappa
@@ -228,6 +231,14 @@ __device__ __forceinline__ void ldsm4(uint32_t addr, uint32_t (&r)[4]) {
 __device__ __forceinline__ void ldsm4t(uint32_t addr, uint32_t (&r)[4]) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr) : "memory");
+}
+
+// Transpose of an 8x8 matrix of 16-bit elements held one row per lane group: lane (n, j) gives elements
+// (2j, 2j+1) of row n and receives elements (2j, 2j+1) of column n.
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
+    return d;
 }
 
 template <int BITS>
@@ -478,26 +489,40 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
         }
     }
     __syncthreads();
-    // A fragments: rows 0..7 = hi(q~) of head n, rows 8..15 = lo(q~) of head n (NSPLIT: head n & 3, so
-    // lanes n and n + 4 compute the same scores and need no exchange later).  For block b and half m
-    // the k-slots (2j, 2j+1 | 2j+8, 2j+9) hold the dims that the code unpackers deliver:
+    // Scores are computed as S = K~ Q~^T: the A operand is the unpacked K tile (M = 16 tokens, K = 16 dims of
+    // one block), the B operand holds the rotated queries (N = 8 columns).  NSPLIT (group <= 4): column c is
+    // the f16 hi part of q~ of head c for c < 4 and the lo part of head c - 4 otherwise, so one MMA gives the
+    // split-precision product; else two operand sets (hi, lo) of 8 heads.  For block b and half m the k-slots
+    // (2j, 2j+1 | 2j+8, 2j+9) hold the dims that the code unpackers deliver:
     //   4-bit: 32b + 8j + 2m + (0, 4 | 1, 5)      3-bit: 32b + 8j + 4m + (0, 1 | 2, 3)
+    // s_afr[set * 4 + b][lane] = (b0, b1 of half 0, b0, b1 of half 1) of the lane's column n.
     {
         const float* sq = s_q + (NSPLIT ? (n & 3) : n) * kD;
         const int b = warp;   // one block per warp
 #pragma unroll
-        for (int m = 0; m < 2; ++m) {
-            const int d0 = 32 * b + 8 * j + (BITS == 4 ? 2 * m : 4 * m);
-            const float qa = sq[d0], qb = sq[d0 + (BITS == 4 ? 4 : 1)];
-            const float qc = sq[d0 + (BITS == 4 ? 1 : 2)], qd = sq[d0 + (BITS == 4 ? 5 : 3)];
-            s_afr[b * 2 + m][lane] = make_uint4(pack_hi(qa, qb), pack_lo(qa, qb), pack_hi(qc, qd), pack_lo(qc, qd));
+        for (int set = 0; set < (NSPLIT ? 1 : 2); ++set) {
+            const bool lo_part = NSPLIT ? (n >= 4) : (set == 1);
+            uint32_t r[4];
+#pragma unroll
+            for (int m = 0; m < 2; ++m) {
+                const int d0 = 32 * b + 8 * j + (BITS == 4 ? 2 * m : 4 * m);
+                const float qa = sq[d0], qb = sq[d0 + (BITS == 4 ? 4 : 1)];
+                const float qc = sq[d0 + (BITS == 4 ? 1 : 2)], qd = sq[d0 + (BITS == 4 ? 5 : 3)];
+                r[2 * m] = lo_part ? pack_lo(qa, qb) : pack_hi(qa, qb);
+                r[2 * m + 1] = lo_part ? pack_lo(qc, qd) : pack_hi(qc, qd);
+            }
+            s_afr[set * 4 + b][lane] = make_uint4(r[0], r[1], r[2], r[3]);
         }
     }
     __syncthreads();
     const uint32_t afr_base = (uint32_t)__cvta_generic_to_shared(&s_afr[0][lane]);
-    const bool lo_lane = NSPLIT && n >= 4;   // NSPLIT: this lane's MMA column carries the lo part of P'
+    // After the scores, lane (n, j) holds tokens n and n + 8 of the step and the two heads
+    //   h(e) = 2 (j & 1) + e (NSPLIT; lanes j and j ^ 2 hold the same values)  |  2 j + e (otherwise).
+    // Columns of the P' operand: NSPLIT lanes j >= 2 supply the lo part, lanes j < 2 the hi part.
+    const bool lo_lane = NSPLIT && j >= 2;
+    const __half2 nsel = u32_as_h2(lo_lane ? 0xBC00BC00u : 0u);   // half2(-1) | half2(0)
 
-    float m_run = kNegBig, l_run = 0.0f;
+    float m_run[2] = {kNegBig, kNegBig}, l_run[2] = {0.0f, 0.0f};   // per head h(e); l_run: this lane's tokens only
     float o[4][2][4];
 #pragma unroll
     for (int b = 0; b < 4; ++b)
@@ -532,41 +557,52 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
             __syncwarp();
         }
 
-        // ---- S^T = Q~ K^T ----
+        // ---- S = K~ Q~^T : rows = tokens (n, n + 8), columns = heads ----
         uint32_t kw[2][4];   // 4-bit: [block pair][octet | block parity << 1] -> word j of token n of the octet
         if (BITS == 4) {
             ldsm4(st + koff[0], kw[0]);
             ldsm4(st + koff[1], kw[1]);
         }
-        float s[2][2];
-#pragma unroll
-        for (int o8 = 0; o8 < 2; ++o8) {
-            s[o8][0] = 0.0f;
-            s[o8][1] = 0.0f;
-            const uint2 sc0 = lds64(st + scoff + o8 * 64), sc1 = lds64(st + scoff + o8 * 64 + 8);
+        float s[2][2] = {{0.0f, 0.0f}, {0.0f, 0.0f}};   // [token n | n + 8][head h(e)]
+        {
+            const uint2 sca = lds64(st + sdelta + n * 8), scb = lds64(st + sdelta + n * 8 + 64);   // scale rows of the two tokens
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
-                uint32_t x[4];
-                if (BITS == 4) {
-                    nibbles_to_half2(kw[b >> 1][o8 + 2 * (b & 1)], x);
-                } else {
-                    const uint32_t lo = lds32(st + koff[b] + o8 * kOct), hi = lds32(st + koff[b] + o8 * kOct + khi);
-                    const uint32_t w = __funnelshift_r(lo, hi, ksh);          // codes 8j..8j+7 in bits 0..23
-                    x[0] = lds32(lop3_and_or(w << 7, 0x1F80u, lut));
-                    x[1] = lds32(lop3_and_or(w << 1, 0x1F80u, lut));
-                    x[2] = lds32(lop3_and_or(w >> 5, 0x1F80u, lut));
-                    x[3] = lds32(lop3_and_or(w >> 11, 0x1F80u, lut));
+                uint32_t x[2][4];   // [token n | n + 8]: codes 8j..8j+7 of block b as four half2
+#pragma unroll
+                for (int t = 0; t < 2; ++t) {
+                    if (BITS == 4) {
+                        nibbles_to_half2(kw[b >> 1][t + 2 * (b & 1)], x[t]);
+                    } else {
+                        const uint32_t lo = lds32(st + koff[b] + t * kOct), hi = lds32(st + koff[b] + t * kOct + khi);
+                        const uint32_t w = __funnelshift_r(lo, hi, ksh);          // codes 8j..8j+7 in bits 0..23
+                        x[t][0] = lds32(lop3_and_or(w << 7, 0x1F80u, lut));
+                        x[t][1] = lds32(lop3_and_or(w << 1, 0x1F80u, lut));
+                        x[t][2] = lds32(lop3_and_or(w >> 5, 0x1F80u, lut));
+                        x[t][3] = lds32(lop3_and_or(w >> 11, 0x1F80u, lut));
+                    }
                 }
                 float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                const uint4 a0 = lds128_volatile(afr_base + (b * 2) * 512), a1 = lds128_volatile(afr_base + (b * 2 + 1) * 512);
-                mma16816(acc, a0.x, a0.y, a0.z, a0.w, x[0], x[1]);
-                mma16816(acc, a1.x, a1.y, a1.z, a1.w, x[2], x[3]);
-                const __half2 p0 = u32_as_h2(b < 2 ? sc0.x : sc0.y), p1 = u32_as_h2(b < 2 ? sc1.x : sc1.y);
-                const float k0 = fabsf((b & 1) ? __high2float(p0) : __low2float(p0));
-                const float k1 = fabsf((b & 1) ? __high2float(p1) : __low2float(p1));
-                s[o8][0] = fmaf(k0, acc[0] + acc[2], s[o8][0]);
-                s[o8][1] = fmaf(k1, acc[1] + acc[3], s[o8][1]);
+#pragma unroll
+                for (int set = 0; set < (NSPLIT ? 1 : 2); ++set) {
+                    const uint4 q4 = lds128_volatile(afr_base + (set * 4 + b) * 512);
+                    mma16816(acc, x[0][0], x[1][0], x[0][1], x[1][1], q4.x, q4.y);
+                    mma16816(acc, x[0][2], x[1][2], x[0][3], x[1][3], q4.z, q4.w);
+                }
+                const __half2 pa = u32_as_h2(b < 2 ? sca.x : sca.y), pb = u32_as_h2(b < 2 ? scb.x : scb.y);
+                const float ka = fabsf((b & 1) ? __high2float(pa) : __low2float(pa));
+                const float kb = fabsf((b & 1) ? __high2float(pb) : __low2float(pb));
+                s[0][0] = fmaf(ka, acc[0], s[0][0]);
+                s[0][1] = fmaf(ka, acc[1], s[0][1]);
+                s[1][0] = fmaf(kb, acc[2], s[1][0]);
+                s[1][1] = fmaf(kb, acc[3], s[1][1]);
             }
+        }
+        if (NSPLIT) {   // hi columns (lanes j < 2) + lo columns (lanes j >= 2)
+#pragma unroll
+            for (int t = 0; t < 2; ++t)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) s[t][e] += __shfl_xor_sync(0xffffffffu, s[t][e], 2);
         }
         if (gs + kGroup > t_end) {   // ragged tail: tokens past the end (of the sequence, or of the partition) get zero weight
             if (TMA) {
@@ -578,54 +614,58 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
                 __syncwarp();
             }
 #pragma unroll
-            for (int o8 = 0; o8 < 2; ++o8)
-#pragma unroll
-                for (int e = 0; e < 2; ++e)
-                    if (gs + 8 * o8 + 2 * j + e >= t_end) s[o8][e] = kNegBig;
+            for (int t = 0; t < 2; ++t)
+                if (gs + n + 8 * t >= t_end) s[t][0] = s[t][1] = kNegBig;
         }
-        // ---- online softmax for head n (the quad holds its 16 tokens) ----
-        float mx = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        const float m_new = fmaxf(m_run, mx);
-        const float resc = ex2(m_run - m_new);
-        m_run = m_new;
-        float p[2][2];
+        // ---- online softmax: the 16 tokens of a head are spread over the 8 lane groups n ----
+        float resc[2], p[2][2];
 #pragma unroll
-        for (int o8 = 0; o8 < 2; ++o8)
-#pragma unroll
-            for (int e = 0; e < 2; ++e) p[o8][e] = ex2(s[o8][e] - m_new);
-        l_run = l_run * resc + ((p[0][0] + p[0][1]) + (p[1][0] + p[1][1]));
-        if (__any_sync(0xffffffffu, resc != 1.0f)) {
-            // column c of O^T belongs to head c (NSPLIT: head c & 3)
-            const int h0 = NSPLIT ? ((2 * j) & 3) : 2 * j, h1 = NSPLIT ? ((2 * j + 1) & 3) : 2 * j + 1;
-            const float r0 = __shfl_sync(0xffffffffu, resc, 4 * h0);
-            const float r1 = __shfl_sync(0xffffffffu, resc, 4 * h1);
+        for (int e = 0; e < 2; ++e) {
+            float mx = fmaxf(s[0][e], s[1][e]);
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+            const float m_new = fmaxf(m_run[e], mx);
+            resc[e] = ex2(m_run[e] - m_new);
+            m_run[e] = m_new;
+            p[0][e] = ex2(s[0][e] - m_new);
+            p[1][e] = ex2(s[1][e] - m_new);
+            l_run[e] = l_run[e] * resc[e] + (p[0][e] + p[1][e]);
+        }
+        if (__any_sync(0xffffffffu, resc[0] != 1.0f || resc[1] != 1.0f)) {
+            // columns (2j, 2j+1) of O^T belong to this lane's heads h(0), h(1)
 #pragma unroll
             for (int b = 0; b < 4; ++b)
 #pragma unroll
                 for (int m = 0; m < 2; ++m) {
-                    o[b][m][0] *= r0; o[b][m][1] *= r1; o[b][m][2] *= r0; o[b][m][3] *= r1;
+                    o[b][m][0] *= resc[0]; o[b][m][1] *= resc[1]; o[b][m][2] *= resc[0]; o[b][m][3] *= resc[1];
                 }
         }
-        // ---- P' = p |s_v| as an exact f16 pair, in half2 arithmetic ----
-        // p = ph + pl (f16 each).  hi = rn(ph s) and ph s - hi are both f16 values (the product of two
-        // 11-bit significands has 22 bits), so hi + lo with lo = fma(pl, s, fma(ph, s, -hi)) equals p s
-        // up to 2^-22 relative.
-        __half2 ph[2], pl[2];
+        // ---- P' = p |s_v| as an exact f16 pair, in half2 arithmetic, then transposed for the next MMA ----
+        // p = ph + pl (f16 each).  hi = rn(ph s) and ph s - hi are both f16 values (the product of two 11-bit
+        // significands has 22 bits), so hi + lo with lo = fma(pl, s, fma(ph, s, -hi)) equals p s up to 2^-22
+        // relative.  Here a register pairs the lane's two heads of one token; movmatrix turns the 8 x 8 matrix
+        // (token rows, head columns) into the B fragment (tokens 2j, 2j+1 of column n) of O^T = V^T P'.
+        uint32_t pq[NSPLIT ? 1 : 2][4][2];   // [hi | lo][block][octet]
 #pragma unroll
-        for (int o8 = 0; o8 < 2; ++o8) {
-            ph[o8] = u32_as_h2(pack_hi(p[o8][0], p[o8][1]));
-            pl[o8] = u32_as_h2(pack_lo(p[o8][0], p[o8][1]));
-        }
-        __half2 sv[2][4];   // |scale| of (token 2j, token 2j+1) of the octet, per block
+        for (int t = 0; t < 2; ++t) {
+            const __half2 ph = u32_as_h2(pack_hi(p[t][0], p[t][1]));
+            __half2 pl = u32_as_h2(pack_lo(p[t][0], p[t][1]));
+            if (NSPLIT && !lo_lane) pl = u32_as_h2(0u);   // hi lanes: lo = fma(0, s, fma(ph, s, -0 * hi)) = hi
+            const uint2 vsr = lds64(st + kSD + sdelta + n * 8 + t * 64);   // V scale row of token n + 8t
 #pragma unroll
-        for (int o8 = 0; o8 < 2; ++o8) {
-            const uint2 va = lds64(st + kSD + scoff + o8 * 64), vb = lds64(st + kSD + scoff + o8 * 64 + 8);
-            sv[o8][0] = u32_as_h2(__byte_perm(va.x, vb.x, 0x5410) & 0x7FFF7FFFu);
-            sv[o8][1] = u32_as_h2(__byte_perm(va.x, vb.x, 0x7632) & 0x7FFF7FFFu);
-            sv[o8][2] = u32_as_h2(__byte_perm(va.y, vb.y, 0x5410) & 0x7FFF7FFFu);
-            sv[o8][3] = u32_as_h2(__byte_perm(va.y, vb.y, 0x7632) & 0x7FFF7FFFu);
+            for (int b = 0; b < 4; ++b) {
+                const __half2 sv = __habs2(u32_as_h2(__byte_perm(b < 2 ? vsr.x : vsr.y, 0u, (b & 1) ? 0x3232 : 0x1010)));   // (s, s)
+                const __half2 hi = __hmul2(ph, sv);
+                const __half2 nhi = NSPLIT ? __hmul2(hi, nsel) : __hneg2(hi);
+                const __half2 lo = __hfma2(pl, sv, __hfma2(ph, sv, nhi));
+                if (NSPLIT) {
+                    pq[0][b][t] = movmatrix_trans(h2_as_u32(lo));
+                } else {
+                    pq[0][b][t] = movmatrix_trans(h2_as_u32(hi));
+                    pq[NSPLIT ? 0 : 1][b][t] = movmatrix_trans(h2_as_u32(lo));
+                }
+            }
         }
         // ---- O^T += V^T P' ----
         uint32_t vw[2][4];   // 4-bit: codes 4n..4n+3 of (token 2j | token 2j+1 << 16), indexed like kw
@@ -635,14 +675,6 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
         }
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
-            uint32_t bh[2], bl[2];
-#pragma unroll
-            for (int o8 = 0; o8 < 2; ++o8) {
-                const __half2 hi = __hmul2(ph[o8], sv[o8][b]);
-                const __half2 lo = __hfma2(pl[o8], sv[o8][b], __hfma2(ph[o8], sv[o8][b], __hneg2(hi)));
-                bh[o8] = h2_as_u32(hi);
-                bl[o8] = h2_as_u32(lo);
-            }
             // codes 4n..4n+3 of block b of the four tokens, paired (token 2j, token 2j+1)
             uint32_t xab[4], xcd[4];
             if (BITS == 4) {
@@ -664,15 +696,10 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
                     xo[3] = lds32(lop3_and_or(z1 << 1, 0x1F80u, lut));
                 }
             }
-            if (NSPLIT) {
-                const uint32_t b0 = lo_lane ? bl[0] : bh[0], b1 = lo_lane ? bl[1] : bh[1];
-                mma16816(o[b][0], xab[0], xab[1], xcd[0], xcd[1], b0, b1);
-                mma16816(o[b][1], xab[2], xab[3], xcd[2], xcd[3], b0, b1);
-            } else {
-                mma16816(o[b][0], xab[0], xab[1], xcd[0], xcd[1], bh[0], bh[1]);
-                mma16816(o[b][0], xab[0], xab[1], xcd[0], xcd[1], bl[0], bl[1]);
-                mma16816(o[b][1], xab[2], xab[3], xcd[2], xcd[3], bh[0], bh[1]);
-                mma16816(o[b][1], xab[2], xab[3], xcd[2], xcd[3], bl[0], bl[1]);
+#pragma unroll
+            for (int ps = 0; ps < (NSPLIT ? 1 : 2); ++ps) {
+                mma16816(o[b][0], xab[0], xab[1], xcd[0], xcd[1], pq[ps][b][0], pq[ps][b][1]);
+                mma16816(o[b][1], xab[2], xab[3], xcd[2], xcd[3], pq[ps][b][0], pq[ps][b][1]);
             }
         }
         __syncwarp();   // every lane is done with this stage before it is refilled
@@ -690,11 +717,17 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
     __syncthreads();    // all rings idle: the memory is reused for the merge
 
     // ---- merge the four warps (scores are in log2 units; partials are stored in natural units) ----
-    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
-    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
-    if (j == 0 && (!NSPLIT || n < 4)) {
-        s_m[warp][n] = m_run;
-        s_l[warp][n] = l_run;
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        float l = l_run[e];   // sum over the lane groups n (each holds two tokens per step)
+        l += __shfl_xor_sync(0xffffffffu, l, 4);
+        l += __shfl_xor_sync(0xffffffffu, l, 8);
+        l += __shfl_xor_sync(0xffffffffu, l, 16);
+        if (n == 0 && (!NSPLIT || j < 2)) {
+            const int h = (NSPLIT ? 2 * (j & 1) : 2 * j) + e;
+            s_m[warp][h] = m_run[e];
+            s_l[warp][h] = l;
+        }
     }
 #pragma unroll
     for (int b = 0; b < 4; ++b)
