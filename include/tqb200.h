@@ -311,6 +311,10 @@ int tqb_decode_attention_static(const tqb_decode_params *p, tqb_stream_t stream)
  *   partial_lse [num_shards, num_q_heads, 2] f32 (max, sum);  out [num_q_heads, head_dim]. */
 int tqb_lse_combine(const float *partial_out, const float *partial_lse, int32_t num_shards,
                     int32_t num_q_heads, int32_t head_dim, void *out, int32_t out_dtype, tqb_stream_t stream);
+/* The same for shards packed one record per shard, [num_q_heads * head_dim floats of out | num_q_heads * 2 floats
+ * of (max, sum)]: the layout a single all-gather of one flat buffer per rank produces. */
+int tqb_lse_combine_packed(const float *gathered, int32_t num_shards, int32_t num_q_heads, int32_t head_dim,
+                           void *out, int32_t out_dtype, tqb_stream_t stream);
 
 /* =====================================================================================
  * 5. Host-side cache objects (own their device memory; calls are ordered on `stream`).

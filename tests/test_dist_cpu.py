@@ -77,7 +77,14 @@ def _worker(rank, world, port, ret):
     outs, lses = d.gather_partials(torch.from_numpy(out), torch.from_numpy(lse))
     merged = _combine(outs.numpy(), lses.numpy())
     want = o.sdpa(q, kd, vd, 0.0884)
-    ret[rank] = float(np.abs(merged - want).max())
+    err = float(np.abs(merged - want).max())
+    # the packed form used by SequenceParallelDecoder: one flat record per rank, ONE all-gather
+    rec = torch.from_numpy(np.concatenate([out.ravel(), lse.ravel()]))
+    gathered = torch.empty((world * rec.numel(),), dtype=torch.float32)
+    dist.all_gather_into_tensor(gathered, rec)
+    g = gathered.numpy().reshape(world, -1)
+    merged2 = _combine(g[:, :hq * D].reshape(world, hq, D), g[:, hq * D:].reshape(world, hq, 2))
+    ret[rank] = max(err, float(np.abs(merged2 - want).max()))
     dist.barrier()
     dist.destroy_process_group()
 

@@ -357,3 +357,17 @@ def test_pqo_cache_growth_batch_and_host_buffers():
     want = o.block_attention(4, 128, 0, -1, q.float().numpy().reshape(24, 128), kp.reshape(6, 351, -1), ksc.reshape(6, 351, -1),
                              vp.reshape(6, 351, -1), vsc.reshape(6, 351, -1), 351, 0.0884, nthreads=8)
     assert np.abs(out_host.float().numpy().reshape(24, 128) - want).max() < 1e-2   # bf16 output rounding
+
+
+def test_packed_shard_merge_equals_plain_shard_merge():
+    # tqb_lse_combine_packed reads [out | (max, sum)] records, one per shard: the layout of a single all-gather
+    g = torch.Generator(device="cuda").manual_seed(5)
+    S, hq, D = 3, 16, 128
+    outs = torch.randn((S, hq, D), generator=g, device="cuda")
+    lses = torch.stack([torch.randn((S, hq), generator=g, device="cuda") * 3, torch.rand((S, hq), generator=g, device="cuda") + 0.5], dim=2)
+    want = tq.lse_combine(outs, lses)
+    packed = torch.cat([outs.reshape(S, -1), lses.reshape(S, -1)], dim=1).contiguous()
+    got = torch.empty((hq, D), dtype=torch.float32, device="cuda")
+    assert lib.tqb_lse_combine_packed(packed.data_ptr(), S, hq, D, got.data_ptr(), 0, None) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)

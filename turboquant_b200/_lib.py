@@ -90,6 +90,7 @@ def _declare(lib):
         "tqb_decode_attention_static": (c_int, [P, P]),
         "tqb_decode_static_scratch_capacity": (S, []),
         "tqb_lse_combine": (c_int, [P, P, I, I, I, P, I, P]),
+        "tqb_lse_combine_packed": (c_int, [P, I, I, I, P, I, P]),
         "tqb_pqo_cache_create": (c_int, [P, P]),
         "tqb_pqo_cache_destroy": (None, [P]),
         "tqb_pqo_cache_prefill": (c_int, [P, I, P, P, I, I, P, P, I, P]),

@@ -260,19 +260,21 @@ __global__ void __launch_bounds__(kThreads) decode_merge_kernel(MergeArgs a) {
 
 // Shard merge: partial_out [S, hq, D] un-normalised and already in the output domain,
 // partial_lse [S, hq, 2].
+// Shard merge: per shard an un-normalised output [hq, D] already in the output domain and (max, sum) pairs
+// [hq, 2]; shard s starts at po + s * po_stride and lse + s * lse_stride (floats).
 template <typename OT>
-__global__ void lse_combine_kernel(const float* __restrict__ po, const float* __restrict__ lse, int S, int hq, int D,
-                                   OT* __restrict__ out) {
+__global__ void lse_combine_kernel(const float* __restrict__ po, const float* __restrict__ lse, size_t po_stride,
+                                   size_t lse_stride, int S, int hq, int D, OT* __restrict__ out) {
     const int head = blockIdx.x;
     float M = -FLT_MAX;
-    for (int s = 0; s < S; ++s) M = fmaxf(M, lse[((size_t)s * hq + head) * 2]);
+    for (int s = 0; s < S; ++s) M = fmaxf(M, lse[s * lse_stride + (size_t)head * 2]);
     float L = 0.0f;
-    for (int s = 0; s < S; ++s) L += lse[((size_t)s * hq + head) * 2 + 1] * expf(lse[((size_t)s * hq + head) * 2] - M);
+    for (int s = 0; s < S; ++s) L += lse[s * lse_stride + (size_t)head * 2 + 1] * expf(lse[s * lse_stride + (size_t)head * 2] - M);
     const float inv_l = L > 0.0f ? 1.0f / L : 0.0f;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         float acc = 0.0f;
         for (int s = 0; s < S; ++s)
-            acc = fmaf(po[((size_t)s * hq + head) * D + d], expf(lse[((size_t)s * hq + head) * 2] - M), acc);
+            acc = fmaf(po[s * po_stride + (size_t)head * D + d], expf(lse[s * lse_stride + (size_t)head * 2] - M), acc);
         out[(size_t)head * D + d] = from_f32<OT>(acc * inv_l);
     }
 }
@@ -451,19 +453,33 @@ int tqb_decode_attention(const tqb_decode_params* p, tqb_stream_t stream) {
     return run_decode(a, cn, co, p->q_dtype, p->out, p->out_dtype, p->lse_out, as_stream(stream), partials_only);
 }
 
-int tqb_lse_combine(const float* partial_out, const float* partial_lse, int32_t num_shards, int32_t num_q_heads,
-                    int32_t head_dim, void* out, int32_t out_dtype, tqb_stream_t stream) {
-    if (!partial_out || !partial_lse || !out) return TQB_ERR_NULL_POINTER;
+static int lse_combine_impl(const float* po, const float* lse, size_t po_stride, size_t lse_stride, int32_t num_shards,
+                            int32_t num_q_heads, int32_t head_dim, void* out, int32_t out_dtype, tqb_stream_t stream) {
+    if (!po || !lse || !out) return TQB_ERR_NULL_POINTER;
     if (num_shards <= 0 || num_q_heads <= 0 || head_dim <= 0) return TQB_ERR_INVALID_ARGUMENT;
     cudaStream_t s = as_stream(stream);
     if (out_dtype == TQB_F32)
-        lse_combine_kernel<float><<<num_q_heads, 128, 0, s>>>(partial_out, partial_lse, num_shards, num_q_heads, head_dim, (float*)out);
+        lse_combine_kernel<float><<<num_q_heads, 128, 0, s>>>(po, lse, po_stride, lse_stride, num_shards, num_q_heads, head_dim, (float*)out);
     else if (out_dtype == TQB_F16)
-        lse_combine_kernel<__half><<<num_q_heads, 128, 0, s>>>(partial_out, partial_lse, num_shards, num_q_heads, head_dim, (__half*)out);
+        lse_combine_kernel<__half><<<num_q_heads, 128, 0, s>>>(po, lse, po_stride, lse_stride, num_shards, num_q_heads, head_dim, (__half*)out);
     else if (out_dtype == TQB_BF16)
-        lse_combine_kernel<__nv_bfloat16><<<num_q_heads, 128, 0, s>>>(partial_out, partial_lse, num_shards, num_q_heads, head_dim, (__nv_bfloat16*)out);
+        lse_combine_kernel<__nv_bfloat16><<<num_q_heads, 128, 0, s>>>(po, lse, po_stride, lse_stride, num_shards, num_q_heads, head_dim, (__nv_bfloat16*)out);
     else return TQB_ERR_INVALID_ARGUMENT;
     return check_launch(s);
+}
+
+int tqb_lse_combine(const float* partial_out, const float* partial_lse, int32_t num_shards, int32_t num_q_heads,
+                    int32_t head_dim, void* out, int32_t out_dtype, tqb_stream_t stream) {
+    return lse_combine_impl(partial_out, partial_lse, (size_t)num_q_heads * head_dim, (size_t)num_q_heads * 2, num_shards,
+                            num_q_heads, head_dim, out, out_dtype, stream);
+}
+
+int tqb_lse_combine_packed(const float* gathered, int32_t num_shards, int32_t num_q_heads, int32_t head_dim, void* out,
+                           int32_t out_dtype, tqb_stream_t stream) {
+    if (!gathered) return TQB_ERR_NULL_POINTER;
+    const size_t rec = (size_t)num_q_heads * ((size_t)head_dim + 2);
+    return lse_combine_impl(gathered, gathered + (size_t)num_q_heads * head_dim, rec, rec, num_shards, num_q_heads, head_dim,
+                            out, out_dtype, stream);
 }
 
 int tqb_fused_attention(const float* q, const uint8_t* k_indices, const uint16_t* k_scales, const uint8_t* v_indices,

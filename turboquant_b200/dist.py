@@ -39,3 +39,32 @@ def sequence_parallel_attend(cache, layer, q, softmax_scale, group=None, out_dty
     out, lse = cache.attend_partial(layer, q, softmax_scale)
     outs, lses = gather_partials(out, lse, group)
     return lse_combine(outs, lses, out_dtype)
+
+
+class SequenceParallelDecoder:
+    """sequence_parallel_attend with everything pre-allocated and ONE all-gather per layer: the shard-local
+    (out, max, sum) of all heads live in one flat record, the records of all ranks are gathered into one
+    buffer and merged by tqb_lse_combine_packed."""
+
+    def __init__(self, cache, num_q_heads, group=None, out_dtype=torch.float32, device=None):
+        from ._lib import lib
+        self.cache, self.group, self.out_dtype, self._lib = cache, group, out_dtype, lib
+        self.world = dist.get_world_size(group)
+        self.hq = cache.config.batch * num_q_heads
+        self.nq = num_q_heads
+        d = cache.config.head_dim
+        dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.rec = torch.empty((self.hq * (d + 2),), dtype=torch.float32, device=dev)
+        self.gathered = torch.empty((self.world * self.hq * (d + 2),), dtype=torch.float32, device=dev)
+        self.out = torch.empty((self.hq, d), dtype=out_dtype, device=dev)
+
+    def attend(self, layer, q, softmax_scale):
+        from .api import check, _dtype_code, _stream
+        lib, d = self._lib, self.cache.config.head_dim
+        q = q.contiguous()
+        check(lib.tqb_pqo_cache_attend_partial(self.cache._h, layer, q.data_ptr(), _dtype_code(q.dtype), self.nq, softmax_scale,
+                                               self.rec.data_ptr(), self.rec.data_ptr() + 4 * self.hq * d, _stream()))
+        dist.all_gather_into_tensor(self.gathered, self.rec, group=self.group)
+        check(lib.tqb_lse_combine_packed(self.gathered.data_ptr(), self.world, self.hq, d, self.out.data_ptr(),
+                                         _dtype_code(self.out_dtype), _stream()))
+        return self.out
