@@ -113,20 +113,33 @@ def run_ours(args):
     cache = tq.PqoCache(tq.CacheConfig(bits=BITS, head_dim=D, num_kv_heads=HKV, num_layers=L, batch=B))
     att = tq.AttendConfig(softmax_scale=scale, n_kv_groups=HQ // HKV)
 
-    # ---- fill the cache with the batched quantize kernel (timed per layer: bulk quantize) ----
+    # ---- fill the cache with the batched quantize kernel ----
+    # The bulk-quantize figure is taken on the last layer's K/V into buffers allocated beforehand (a cache
+    # fill also allocates and clears the layer's storage, which is not the kernel's time).
+    nvec = 2 * B * HKV * CTX
+    quant_bytes = nvec * (D * 2 + D * BITS // 8 + (D // 32) * 2)
     qt = []
     for layer in range(L):
         k, v = synth_layer(layer, CTX, dev)
-        e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
-        e0.record()
         cache.prefill(layer, k, v)
-        e1.record()
-        e1.synchronize()
-        qt.append(e0.elapsed_time(e1))
+        if layer == L - 1:
+            rows = B * HKV * CTX
+            qi = torch.empty((2, rows, D * BITS // 8), dtype=torch.uint8, device=dev)
+            qs_ = torch.empty((2, rows, D // 32), dtype=torch.int16, device=dev)
+            for rep in range(4):
+                e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
+                e0.record()
+                rc = lib.tqb_block_quantize_pair(BITS, D, 0, -1, k.data_ptr(), v.data_ptr(), 2, rows, 0, qi[0].data_ptr(),
+                                                 qs_[0].data_ptr(), qi[1].data_ptr(), qs_[1].data_ptr(), 0, 0, 0,
+                                                 ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+                e1.record()
+                assert rc == 0, rc
+                e1.synchronize()
+                if rep:
+                    qt.append(e0.elapsed_time(e1))
+            del qi, qs_
         del k, v
-    nvec = 2 * B * HKV * CTX
     quant_ms = float(np.median(qt))
-    quant_bytes = nvec * (D * 2 + D * BITS // 8 + (D // 32) * 2)
 
     g = torch.Generator(device=dev).manual_seed(1234 + rank)
     n_tok = args.warmup + args.steps + 2 * (args.warmup + args.steps) + 4
@@ -253,7 +266,7 @@ def run_ours(args):
                          "algorithmic_bytes_per_launch": launch_bytes},
             "quantize": {"mvec_per_s": round(nvec / (quant_ms * 1e-3) / 1e6, 1), "gbps": round(quant_bytes / (quant_ms * 1e-3) / 1e9, 1),
                          "frac_of_hbm_peak": round(quant_bytes / (quant_ms * 1e-3) / 1e9 / peak, 4),
-                         "what": "per-layer bulk fill: 2 x 64 x 8 x 8192 bf16 vectors -> PQO4 (328 B per vector in+out)"},
+                         "what": "bulk quantize of one layer: K and V, 2 x 64 x 8 x 8192 bf16 vectors -> PQO4 in one launch (328 B per vector in+out)"},
             "clocks": clocks,
         }
         if not args.no_cpu and world == 1:   # the CPU leg runs at N = 1 only
