@@ -37,6 +37,7 @@
 #include <string.h>
 
 #include <mutex>
+#include <type_traits>
 
 #include "tqb_common.cuh"
 #include "tqb_merge.cuh"
@@ -154,6 +155,11 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
 __device__ __forceinline__ void cp_async8(uint32_t dst, const void* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(dst), "l"(src) : "memory");
 }
+// The same with immediate offsets folded into the address operands (no address arithmetic in registers).
+template <int DOFF, int SOFF>
+__device__ __forceinline__ void cp_async16_o(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0+%2], [%1+%3], 16;\n" ::"r"(dst), "l"(src), "n"(DOFF), "n"(SOFF) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
@@ -210,6 +216,24 @@ __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
     asm("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr) : "memory");   // ordered against other memory operations only
     return v;
 }
+template <int OFF>
+__device__ __forceinline__ uint32_t lds32_o(uint32_t base) {
+    uint32_t v;
+    asm("ld.shared.u32 %0, [%1+%2];\n" : "=r"(v) : "r"(base), "n"(OFF) : "memory");
+    return v;
+}
+template <int OFF>
+__device__ __forceinline__ uint2 lds64_o(uint32_t base) {
+    uint2 v;
+    asm("ld.shared.v2.u32 {%0,%1}, [%2+%3];\n" : "=r"(v.x), "=r"(v.y) : "r"(base), "n"(OFF) : "memory");
+    return v;
+}
+template <int OFF>
+__device__ __forceinline__ uint4 lds128_volatile_o(uint32_t base) {
+    uint4 v;   // volatile: re-read where it is used instead of being kept in registers across the loop
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(base), "n"(OFF));
+    return v;
+}
 __device__ __forceinline__ uint4 lds128_volatile(uint32_t addr) {
     uint4 v;   // volatile: re-read where it is used instead of being kept in registers across the loop
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
@@ -228,6 +252,16 @@ __device__ __forceinline__ void ldsm4(uint32_t addr, uint32_t (&r)[4]) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr) : "memory");
 }
+template <int OFF>
+__device__ __forceinline__ void ldsm4_o(uint32_t base, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4+%5];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(base), "n"(OFF) : "memory");
+}
+template <int OFF>
+__device__ __forceinline__ void ldsm4t_o(uint32_t base, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4+%5];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(base), "n"(OFF) : "memory");
+}
 __device__ __forceinline__ void ldsm4t(uint32_t addr, uint32_t (&r)[4]) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr) : "memory");
@@ -239,6 +273,15 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
     uint32_t d;
     asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
     return d;
+}
+
+// Compile-time loop: f(std::integral_constant<int, I>) for I = 0..N-1 (lets loop indices be immediate operands).
+template <int I, int N, typename F>
+__device__ __forceinline__ void static_for(F&& f) {
+    if constexpr (I < N) {
+        f(std::integral_constant<int, I>{});
+        static_for<I + 1, N>(f);
+    }
 }
 
 template <int BITS>
@@ -265,13 +308,14 @@ __device__ __forceinline__ void tma_tile_fill(const TmaMaps& m, uint32_t tile, u
 }
 
 // Per-lane copy plan of one stage: up to two 16-byte index pieces of K and of V, and one 8-byte
-// scale row (K for lanes 0..15, V for lanes 16..31).
+// scale row (K for lanes 0..15, V for lanes 16..31).  The 16 token rows of a stage are contiguous in
+// global memory, so piece c of the stage sits at (stage start) + 16 c: the plan keeps running pointers
+// to the lane's first piece (the second is 512 bytes further) and to its scale row.
 struct FillPlan {
-    const uint8_t* k0;    // piece 0 of group 0
-    const uint8_t* v0;
+    const uint8_t* k;     // lane's piece of the stage that is filled next
+    const uint8_t* v;
     const uint16_t* sc;
-    uint32_t dst0, dst1, dsts;
-    int src1_delta;       // byte distance from piece 0 to piece 1 in global memory
+    uint32_t dst0, dst1, dsts;   // shared-memory offsets inside a stage
     int t0, t1, ts;       // token rows (inside the group) of the two pieces and of the scale row
     bool has1;
 };
@@ -286,9 +330,8 @@ __device__ __forceinline__ FillPlan make_plan(const MmaArgs& a, size_t row0, int
     f.t1 = c1 / ppr;
     const int pc0 = c0 - f.t0 * ppr, pc1 = c1 - f.t1 * ppr;
     f.has1 = c1 < G::kPieces;
-    f.k0 = a.kb + (row0 + first + f.t0) * G::kRowB + pc0 * 16;
-    f.v0 = a.vb + (row0 + first + f.t0) * G::kRowB + pc0 * 16;
-    f.src1_delta = (f.t1 - f.t0) * G::kRowB + (pc1 - pc0) * 16;
+    f.k = a.kb + (row0 + first) * G::kRowB + c0 * 16;
+    f.v = a.vb + (row0 + first) * G::kRowB + c0 * 16;
     if (BITS == 4) {
         f.dst0 = f.t0 * 64 + ((pc0 ^ ((f.t0 >> 1) & 3)) << 4);
         f.dst1 = f.t1 * 64 + ((pc1 ^ ((f.t1 >> 1) & 3)) << 4);
@@ -302,26 +345,38 @@ __device__ __forceinline__ FillPlan make_plan(const MmaArgs& a, size_t row0, int
     return f;
 }
 
-// Issues the copies of the 16 tokens starting at `gs` (= first + row_off rows) into the stage at
-// shared address `st`.  Rows past the last valid token re-read the last token (they are masked
-// later), which only happens in the final group of a sequence.
+// Issues the copies of the 16 tokens starting at `gs` (where the plan's pointers stand) into the stage at
+// shared address `st`, then moves the pointers on by `stride` tokens.  In the final group of a sequence rows
+// past the last valid token re-read the last token (they are masked later).
 template <int BITS>
-__device__ __forceinline__ void stage_fill(const FillPlan& f, size_t row_off, int gs, int last, uint32_t st) {
+__device__ __forceinline__ void stage_fill(FillPlan& f, bool issue, int stride, int gs, int last, uint32_t st) {
     using G = Geo<BITS>;
-    const size_t boff = row_off * G::kRowB;
-    long long b0 = 0, b1 = 0, bs = 0;
-    if (gs + kGroup > last + 1) {
-        b0 = (long long)(min(gs + f.t0, last) - (gs + f.t0)) * G::kRowB;
-        b1 = (long long)(min(gs + f.t1, last) - (gs + f.t1)) * G::kRowB;
-        bs = (long long)(min(gs + f.ts, last) - (gs + f.ts)) * 4;
+    if (issue) {
+        if (gs + kGroup <= last + 1) {
+            const uint32_t d0 = st + f.dst0, d1 = st + f.dst1;
+            cp_async16_o<0, 0>(d0, f.k);
+            cp_async16_o<G::kIdxB, 0>(d0, f.v);
+            if (f.has1) {
+                cp_async16_o<0, 512>(d1, f.k);
+                cp_async16_o<G::kIdxB, 512>(d1, f.v);
+            }
+            cp_async8(st + f.dsts, f.sc);
+        } else {
+            const long long b0 = (long long)(min(gs + f.t0, last) - (gs + f.t0)) * G::kRowB;
+            const long long b1 = (long long)(min(gs + f.t1, last) - (gs + f.t1)) * G::kRowB;
+            const long long bs = (long long)(min(gs + f.ts, last) - (gs + f.ts)) * 4;
+            cp_async16(st + f.dst0, f.k + b0);
+            cp_async16(st + G::kIdxB + f.dst0, f.v + b0);
+            if (f.has1) {
+                cp_async16(st + f.dst1, f.k + 512 + b1);
+                cp_async16(st + G::kIdxB + f.dst1, f.v + 512 + b1);
+            }
+            cp_async8(st + f.dsts, f.sc + bs);
+        }
     }
-    cp_async16(st + f.dst0, f.k0 + boff + b0);
-    cp_async16(st + G::kIdxB + f.dst0, f.v0 + boff + b0);
-    if (f.has1) {
-        cp_async16(st + f.dst1, f.k0 + boff + f.src1_delta + b1);
-        cp_async16(st + G::kIdxB + f.dst1, f.v0 + boff + f.src1_delta + b1);
-    }
-    cp_async8(st + f.dsts, f.sc + row_off * 4 + bs);
+    f.k += (size_t)stride * G::kRowB;
+    f.v += (size_t)stride * G::kRowB;
+    f.sc += (size_t)stride * 4;
 }
 
 // Grid (kv heads, partitions), 4 warps; each warp walks its partition in steps of 16 tokens and
@@ -402,7 +457,7 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
     constexpr uint32_t kSD = TMA ? kWarps * 128 : 128;                  // from its K scale rows to its V scale rows
     const uint32_t ring = TMA ? rings_base + warp * G::kIdxB : rings_base + warp * G::kRingB;
     const uint32_t sdelta = TMA ? 2 * kWarps * G::kIdxB - warp * (G::kIdxB - 128) : 2 * G::kIdxB;   // K rows -> K scale rows
-    const FillPlan plan = TMA ? FillPlan{} : make_plan<BITS>(a, row0, first, lane);
+    FillPlan plan = TMA ? FillPlan{} : make_plan<BITS>(a, row0, first, lane);
     const uint32_t full0 = (uint32_t)__cvta_generic_to_shared(&s_bar[0][0]);
     const uint32_t empty0 = (uint32_t)__cvta_generic_to_shared(&s_bar[1][0]);
     const int ntiles = t_begin < t_end ? (t_end - t_begin + stride - 1) / stride : 0;   // 64-token tiles of the CTA
@@ -425,46 +480,40 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
     } else {
 #pragma unroll
         for (int i = 0; i < kStages - 1; ++i) {
-            if (i < ngroups) stage_fill<BITS>(plan, (size_t)i * stride, first + i * stride, last, ring + i * G::kStageB);
+            stage_fill<BITS>(plan, i < ngroups, stride, first + i * stride, last, ring + i * G::kStageB);
             cp_async_commit();
         }
     }
     uint32_t st = ring;                                        // stage being consumed (this warp's K rows)
     uint32_t st_fill = TMA ? rings_base + (kStages - 1) * G::kTileB : ring + (kStages - 1) * G::kStageB;   // stage being refilled
-    size_t fill_row = (size_t)(kStages - 1) * stride;
     // TMA: barrier offset (8 x stage) of st / of st_fill, phase of st's full barrier, phase of st_fill's empty barrier
     uint32_t boff = 0, boff_fill = 8 * (kStages - 1), parity = 0, eparity = 1;
     bool stage_ok = true;
 
-    // per-thread shared-memory offsets inside a stage
-    uint32_t koff[4], voff[4];
-    uint32_t khi = 0, vhi = 0, ksh = 0, vsh = 0;   // 3-bit: distance to the second word, funnel shifts
+    // per-thread shared-memory offsets inside a stage; every load of the token loop is one of three or four
+    // per-step base registers (stage + offset) plus an immediate
+    uint32_t offK0, offK1, offV = 0, offVh = 0;      // 4-bit: ldmatrix rows of blocks (0,1) / (2,3); 3-bit: first / second word
+    uint32_t ksh = 0, vsh = 0;                       // 3-bit: funnel shifts
     if (BITS == 4) {
         // ldmatrix row addresses: lane l supplies row l & 7 of matrix l >> 3.  Matrix m covers the token
         // octet m & 1 and the block 2 * pair + (m >> 1); a row is the 16-byte piece of one token.
         const int tok = 8 * ((lane >> 3) & 1) + (lane & 7), blk = lane >> 4;
-        koff[0] = tok * 64 + ((blk ^ ((tok >> 1) & 3)) << 4);
-        koff[1] = koff[0] ^ 32;                      // blocks 2, 3: piece index ^ 2
-        voff[0] = kVD + koff[0];
-        voff[1] = kVD + koff[1];
-        koff[2] = koff[3] = voff[2] = voff[3] = 0;
+        offK0 = tok * 64 + ((blk ^ ((tok >> 1) & 3)) << 4);
+        offK1 = offK0 ^ 32;                          // blocks 2, 3: piece index ^ 2
     } else {
-        // K: the 24 bits at byte 3j of block b;  V: the 12 bits at bit 12n of block b
+        // K: the 24 bits at byte 3j of block b of token n;  V: the 12 bits at bit 12n of block b of token 2j
         const int kw0 = (3 * j) >> 2;
         const int vw0 = (12 * n) >> 5;
-        khi = (kw0 < 2) ? 4 : 0;
         ksh = ((3 * j) & 3) * 8;
         vsh = (12 * n) & 31;
-        vhi = (vsh + 12 > 32) ? 4 : 0;
-#pragma unroll
-        for (int b = 0; b < 4; ++b) {
-            koff[b] = n * 48 + 12 * b + 4 * kw0;                                // token n (+8o: +384)
-            voff[b] = kVD + (2 * j) * 48 + 12 * b + 4 * vw0;               // token 2j (+e: +48, +8o: +384)
-        }
+        offK0 = n * 48 + 4 * kw0;                    // + 12 b, + 8 rows per octet
+        offK1 = offK0 + ((kw0 < 2) ? 4 : 0);
+        offV = kVD + (2 * j) * 48 + 4 * vw0;         // + 12 b, + 48 per token, + 8 rows per octet
+        offVh = offV + ((vsh + 12 > 32) ? 4 : 0);
     }
     constexpr uint32_t kOct = 8 * G::kRowB;                                     // 8 token rows
     constexpr uint32_t kRow = G::kRowB;
-    const uint32_t scoff = sdelta + (2 * j) * 8;                          // scales of token 2j (+e: +8, +8o: +64)
+    const uint32_t offS = sdelta + n * 8;                                       // K scale row of token n (+64: token n + 8)
     const uint32_t lut = lut_base + lane * 4;
 
     if (BITS == 3) {
@@ -549,46 +598,46 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
                 break;
             }
         } else {
-            if (it + kStages - 1 < ngroups) stage_fill<BITS>(plan, fill_row, gs + (kStages - 1) * stride, last, st_fill);
+            stage_fill<BITS>(plan, it + kStages - 1 < ngroups, stride, gs + (kStages - 1) * stride, last, st_fill);
             cp_async_commit();
-            fill_row += stride;
             st_fill = (st_fill + G::kStageB == ring + G::kRingB) ? ring : st_fill + G::kStageB;
             cp_async_wait<kStages - 1>();
             __syncwarp();
         }
 
+        const uint32_t bK0 = st + offK0, bK1 = st + offK1, bS = st + offS;
         // ---- S = K~ Q~^T : rows = tokens (n, n + 8), columns = heads ----
         uint32_t kw[2][4];   // 4-bit: [block pair][octet | block parity << 1] -> word j of token n of the octet
         if (BITS == 4) {
-            ldsm4(st + koff[0], kw[0]);
-            ldsm4(st + koff[1], kw[1]);
+            ldsm4_o<0>(bK0, kw[0]);
+            ldsm4_o<0>(bK1, kw[1]);
         }
         float s[2][2] = {{0.0f, 0.0f}, {0.0f, 0.0f}};   // [token n | n + 8][head h(e)]
         {
-            const uint2 sca = lds64(st + sdelta + n * 8), scb = lds64(st + sdelta + n * 8 + 64);   // scale rows of the two tokens
-#pragma unroll
-            for (int b = 0; b < 4; ++b) {
+            const uint2 sca = lds64_o<0>(bS), scb = lds64_o<64>(bS);   // scale rows of the two tokens
+            static_for<0, 4>([&](auto b_) {
+                constexpr int b = decltype(b_)::value;
                 uint32_t x[2][4];   // [token n | n + 8]: codes 8j..8j+7 of block b as four half2
-#pragma unroll
-                for (int t = 0; t < 2; ++t) {
+                static_for<0, 2>([&](auto t_) {
+                    constexpr int t = decltype(t_)::value;
                     if (BITS == 4) {
                         nibbles_to_half2(kw[b >> 1][t + 2 * (b & 1)], x[t]);
                     } else {
-                        const uint32_t lo = lds32(st + koff[b] + t * kOct), hi = lds32(st + koff[b] + t * kOct + khi);
+                        const uint32_t lo = lds32_o<12 * b + t * kOct>(bK0), hi = lds32_o<12 * b + t * kOct>(bK1);
                         const uint32_t w = __funnelshift_r(lo, hi, ksh);          // codes 8j..8j+7 in bits 0..23
                         x[t][0] = lds32(lop3_and_or(w << 7, 0x1F80u, lut));
                         x[t][1] = lds32(lop3_and_or(w << 1, 0x1F80u, lut));
                         x[t][2] = lds32(lop3_and_or(w >> 5, 0x1F80u, lut));
                         x[t][3] = lds32(lop3_and_or(w >> 11, 0x1F80u, lut));
                     }
-                }
+                });
                 float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-                for (int set = 0; set < (NSPLIT ? 1 : 2); ++set) {
-                    const uint4 q4 = lds128_volatile(afr_base + (set * 4 + b) * 512);
+                static_for<0, (NSPLIT ? 1 : 2)>([&](auto set_) {
+                    constexpr int set = decltype(set_)::value;
+                    const uint4 q4 = lds128_volatile_o<(set * 4 + b) * 512>(afr_base);
                     mma16816(acc, x[0][0], x[1][0], x[0][1], x[1][1], q4.x, q4.y);
                     mma16816(acc, x[0][2], x[1][2], x[0][3], x[1][3], q4.z, q4.w);
-                }
+                });
                 const __half2 pa = u32_as_h2(b < 2 ? sca.x : sca.y), pb = u32_as_h2(b < 2 ? scb.x : scb.y);
                 const float ka = fabsf((b & 1) ? __high2float(pa) : __low2float(pa));
                 const float kb = fabsf((b & 1) ? __high2float(pb) : __low2float(pb));
@@ -596,7 +645,7 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
                 s[0][1] = fmaf(ka, acc[1], s[0][1]);
                 s[1][0] = fmaf(kb, acc[2], s[1][0]);
                 s[1][1] = fmaf(kb, acc[3], s[1][1]);
-            }
+            });
         }
         if (NSPLIT) {   // hi columns (lanes j < 2) + lo columns (lanes j >= 2)
 #pragma unroll
@@ -618,6 +667,10 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
                 if (gs + n + 8 * t >= t_end) s[t][0] = s[t][1] = kNegBig;
         }
         // ---- online softmax: the 16 tokens of a head are spread over the 8 lane groups n ----
+        // The reference value m_run is only raised when the step's maximum exceeds it by more than kLazy
+        // (in log2 units): any common reference gives the same result, p stays below 2^kLazy, and the
+        // rescaling of the 32 accumulators becomes rare.
+        constexpr float kLazy = 6.0f;
         float resc[2], p[2][2];
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
@@ -625,7 +678,7 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
-            const float m_new = fmaxf(m_run[e], mx);
+            const float m_new = (mx - m_run[e] > kLazy) ? mx : m_run[e];
             resc[e] = ex2(m_run[e] - m_new);
             m_run[e] = m_new;
             p[0][e] = ex2(s[0][e] - m_new);
@@ -647,12 +700,12 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
         // relative.  Here a register pairs the lane's two heads of one token; movmatrix turns the 8 x 8 matrix
         // (token rows, head columns) into the B fragment (tokens 2j, 2j+1 of column n) of O^T = V^T P'.
         uint32_t pq[NSPLIT ? 1 : 2][4][2];   // [hi | lo][block][octet]
-#pragma unroll
-        for (int t = 0; t < 2; ++t) {
+        static_for<0, 2>([&](auto t_) {
+            constexpr int t = decltype(t_)::value;
             const __half2 ph = u32_as_h2(pack_hi(p[t][0], p[t][1]));
             __half2 pl = u32_as_h2(pack_lo(p[t][0], p[t][1]));
             if (NSPLIT && !lo_lane) pl = u32_as_h2(0u);   // hi lanes: lo = fma(0, s, fma(ph, s, -0 * hi)) = hi
-            const uint2 vsr = lds64(st + kSD + sdelta + n * 8 + t * 64);   // V scale row of token n + 8t
+            const uint2 vsr = lds64_o<kSD + t * 64>(bS);   // V scale row of token n + 8t
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
                 const __half2 sv = __habs2(u32_as_h2(__byte_perm(b < 2 ? vsr.x : vsr.y, 0u, (b & 1) ? 0x3232 : 0x1010)));   // (s, s)
@@ -666,26 +719,27 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
                     pq[NSPLIT ? 0 : 1][b][t] = movmatrix_trans(h2_as_u32(lo));
                 }
             }
-        }
+        });
         // ---- O^T += V^T P' ----
         uint32_t vw[2][4];   // 4-bit: codes 4n..4n+3 of (token 2j | token 2j+1 << 16), indexed like kw
         if (BITS == 4) {
-            ldsm4t(st + voff[0], vw[0]);
-            ldsm4t(st + voff[1], vw[1]);
+            ldsm4t_o<kVD>(bK0, vw[0]);
+            ldsm4t_o<kVD>(bK1, vw[1]);
         }
-#pragma unroll
-        for (int b = 0; b < 4; ++b) {
+        const uint32_t bV = st + offV, bVh = st + offVh;   // 3-bit only
+        static_for<0, 4>([&](auto b_) {
+            constexpr int b = decltype(b_)::value;
             // codes 4n..4n+3 of block b of the four tokens, paired (token 2j, token 2j+1)
             uint32_t xab[4], xcd[4];
             if (BITS == 4) {
                 nibbles_to_half2(vw[b >> 1][2 * (b & 1)], xab);
                 nibbles_to_half2(vw[b >> 1][2 * (b & 1) + 1], xcd);
             } else {
-#pragma unroll
-                for (int o8 = 0; o8 < 2; ++o8) {
-                    const uint32_t base = st + voff[b] + o8 * kOct;
-                    const uint32_t xa = __funnelshift_r(lds32(base), lds32(base + vhi), vsh);                // token 2j
-                    const uint32_t xb = __funnelshift_r(lds32(base + kRow), lds32(base + kRow + vhi), vsh);  // token 2j+1
+                static_for<0, 2>([&](auto o_) {
+                    constexpr int o8 = decltype(o_)::value;
+                    constexpr int off = 12 * b + o8 * kOct;
+                    const uint32_t xa = __funnelshift_r(lds32_o<off>(bV), lds32_o<off>(bVh), vsh);                // token 2j
+                    const uint32_t xb = __funnelshift_r(lds32_o<off + kRow>(bV), lds32_o<off + kRow>(bVh), vsh);  // token 2j+1
                     // 6-bit fields (code of token 2j | code of token 2j+1 << 3): codes 0, 2 in z0, codes 1, 3 in z1
                     const uint32_t z0 = bit_select(xa, xb << 3, 0x1C7u);
                     const uint32_t z1 = bit_select(xa >> 3, xb, 0x1C7u);
@@ -694,14 +748,14 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
                     xo[2] = lds32(lop3_and_or(z0 << 1, 0x1F80u, lut));
                     xo[1] = lds32(lop3_and_or(z1 << 7, 0x1F80u, lut));
                     xo[3] = lds32(lop3_and_or(z1 << 1, 0x1F80u, lut));
-                }
+                });
             }
 #pragma unroll
             for (int ps = 0; ps < (NSPLIT ? 1 : 2); ++ps) {
                 mma16816(o[b][0], xab[0], xab[1], xcd[0], xcd[1], pq[ps][b][0], pq[ps][b][1]);
                 mma16816(o[b][1], xab[2], xab[3], xcd[2], xcd[3], pq[ps][b][0], pq[ps][b][1]);
             }
-        }
+        });
         __syncwarp();   // every lane is done with this stage before it is refilled
         st = (st + kPitch == ring + kStages * kPitch) ? ring : st + kPitch;
         if (TMA) {
