@@ -24,7 +24,8 @@ namespace tqb {
 
 int block_cfg_check(int bits, int head_dim, int norm_mode);
 int launch_decode_mma(const tqb_decode_params* p, int num_partitions, float* partial_out, float* partial_max,
-                      float* partial_sum, float sign_mag, unsigned* counters, bool counters_clean, cudaStream_t s);
+                      float* partial_sum, float sign_mag, unsigned* counters, bool counters_clean, cudaStream_t s,
+                      const int* gate = nullptr, int gate_want = 0, const float* dev_signs = nullptr);
 
 namespace {
 
@@ -52,6 +53,7 @@ struct DecodeArgs {
     int outlier_mode;  // 0 all normal, 1 all outlier, 2 by sign of the scale
     float softmax_scale;
     float sign_mag;
+    const int* gate;     // reference entry point: run only if *gate == 0 (the caller's tables are not the standard ones)
 };
 
 __device__ __forceinline__ float warp_sum(float v) {
@@ -73,6 +75,7 @@ __device__ __forceinline__ float wht32_lane(float v, int lane) {
 template <typename QT, int NB>
 __global__ void __launch_bounds__(kThreads)
 decode_general_kernel(DecodeArgs a, Codebook normal, Codebook outlier) {
+    if (a.gate != nullptr && *a.gate != 0) return;   // a tensor-core kernel of the same call does the work
     extern __shared__ float smem[];
     const int D = a.head_dim;
     const int g = a.hq / a.hkv;
@@ -277,6 +280,44 @@ __global__ void lse_combine_kernel(const float* __restrict__ po, const float* __
             acc = fmaf(po[s * po_stride + (size_t)head * D + d], expf(lse[s * lse_stride + (size_t)head * 2] - M), acc);
         out[(size_t)head * D + d] = from_f32<OT>(acc * inv_l);
     }
+}
+
+// Verdict on the caller's device tables: 1 = the MaxNorm codebook of this width and the standard sign pattern,
+// 2 = the L2Norm codebook and the standard sign pattern, 0 = anything else.
+__global__ void table_gate_kernel(const float* __restrict__ codebook, const float* __restrict__ signs, int n, Codebook std_max,
+                                  Codebook std_l2, int* __restrict__ gate) {
+    const int lane = threadIdx.x;
+    const uint32_t neg = 0xB1A6D4B2u;   // src/cache/precomputed/rotation.rs:16-20
+    // the crate uploads rotation_fwd[0] * sqrt(32) (src/cache/pqo.rs:134-138): +-1 up to one f32 rounding
+    const float mag = fabsf(signs[0]);
+    const bool sign_ok = fabsf(mag - 1.0f) < 1e-6f && signs[lane] == (((neg >> lane) & 1u) ? -mag : mag);
+    const bool is_max = lane >= n || codebook[lane] == std_max.c[lane];
+    const bool is_l2 = lane >= n || codebook[lane] == std_l2.c[lane];
+    const bool s_ok = __all_sync(0xffffffffu, sign_ok);
+    const bool m_ok = __all_sync(0xffffffffu, is_max);
+    const bool l_ok = __all_sync(0xffffffffu, is_l2);
+    if (lane == 0) *gate = !s_ok ? 0 : (m_ok ? 1 : (l_ok ? 2 : 0));
+}
+
+// Gate words: a ring of slots in a static device array, one per call in flight (the ring is far longer than
+// any realistic number of concurrent calls).
+constexpr int kGateSlots = 4096;
+__device__ int g_gate_slots[kGateSlots];
+std::mutex g_gate_mutex;
+int* g_gate_base[64] = {};
+unsigned g_gate_next = 0;
+
+int gate_slot(int** out) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return TQB_ERR_CUDA;
+    std::lock_guard<std::mutex> lock(g_gate_mutex);
+    if (!g_gate_base[dev]) {
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_gate_slots) != cudaSuccess || !ptr) return TQB_ERR_CUDA;
+        g_gate_base[dev] = static_cast<int*>(ptr);
+    }
+    *out = g_gate_base[dev] + (g_gate_next++ % kGateSlots);
+    return TQB_OK;
 }
 
 size_t general_smem_bytes(int D) {
@@ -517,7 +558,35 @@ int tqb_fused_attention(const float* q, const uint8_t* k_indices, const uint16_t
     a.outlier_mode = 1;  // the caller's codebook decodes every block
     a.softmax_scale = softmax_scale;
     a.sign_mag = 1.0f;
-    return run_decode(a, dummy, dummy, TQB_F32, output, TQB_F32, nullptr, as_stream(stream));
+    cudaStream_t s = as_stream(stream);
+    // The tables arrive as device pointers, so the host cannot know whether they are the crate's own
+    // (src/cache/precomputed/codebooks.rs, rotation.rs) - the only ones the tensor-core kernels decode.  A
+    // one-warp kernel compares them on the device and leaves a verdict in a gate word; the tensor-core
+    // kernel(s) and the general kernel are all launched and every CTA of those whose verdict it is not
+    // returns at once.  No host synchronisation, safe under stream capture.
+    const bool fast_shape = head_dim == 128 && !qjl_enabled && (bits == 3 || bits == 4) &&
+                            num_attention_heads / num_kv_heads <= 8;
+    Codebook std_max{}, std_l2{};
+    int* gate = nullptr;
+    if (fast_shape && block_codebook(bits, TQB_MAXNORM, std_max) && block_codebook(bits, TQB_L2NORM, std_l2) &&
+        gate_slot(&gate) == TQB_OK) {
+        table_gate_kernel<<<1, 32, 0, s>>>(codebook, sign_pattern, 1 << bits, std_max, std_l2, gate);
+        tqb_decode_params p{};
+        p.q = q; p.k_indices = k_indices; p.k_scales = k_scales; p.v_indices = v_indices; p.v_scales = v_scales;
+        p.out = output; p.q_dtype = TQB_F32; p.out_dtype = TQB_F32; p.bits = bits; p.head_dim = head_dim;
+        p.outlier_blocks = -1; p.num_q_heads = num_attention_heads; p.num_kv_heads = num_kv_heads;
+        p.kv_len = kv_len; p.kv_stride = kv_stride; p.num_partitions = num_partitions; p.softmax_scale = softmax_scale;
+        bool any_fast = false;
+        for (int mode = 0; mode < 2; ++mode) {   // verdict 1: MaxNorm tables, verdict 2: L2Norm tables
+            p.norm_mode = mode == 0 ? TQB_MAXNORM : TQB_L2NORM;
+            const int st = launch_decode_mma(&p, num_partitions, partial_out, partial_max, partial_sum, 1.0f, nullptr, true, s,
+                                             gate, mode + 1, sign_pattern);
+            if (st == TQB_OK) any_fast = true;
+            else if (st != TQB_ERR_UNSUPPORTED) return st;
+        }
+        if (any_fast) a.gate = gate;
+    }
+    return run_decode(a, dummy, dummy, TQB_F32, output, TQB_F32, nullptr, s);
 }
 
 void tq_fused_attention(const float* q, const uint8_t* k_indices, const uint16_t* k_scales, const uint8_t* v_indices,

@@ -77,6 +77,10 @@ struct MmaArgs {
     const void* app_k;
     const void* app_v;
     float outer_centroid;
+    // reference entry point: the kernel runs only if *gate == gate_want (nullptr: always)
+    const int* gate;
+    int gate_want;
+    const float* dev_signs;   // with a gate: the caller's sign pattern (its magnitude replaces sign_mag)
 };
 
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -397,6 +401,7 @@ __device__ __forceinline__ void stage_fill(FillPlan& f, bool issue, int stride, 
 template <typename QT, int BITS, bool NSPLIT, bool TMA>
 __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, const __grid_constant__ TmaMaps maps,
                                                                  const __grid_constant__ Codebook app_cb) {
+    if (a.gate != nullptr && *a.gate != a.gate_want) return;   // the caller's tables are not the ones this kernel decodes
     using G = Geo<BITS>;
     // Dynamic shared memory: [3-bit only: lookup table at an 8 KB-aligned address, so that a table address
     // is formed by OR-ing (index << 7) into the lane's base with one LOP3][stage rings, 1 KB-aligned].
@@ -527,7 +532,8 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
     // ---- rotate the g queries of this KV head once: q~ = sigma .* H32(q_b) / sqrt(32), constants folded ----
     {
         const uint32_t neg = 0xB1A6D4B2u;  // src/cache/precomputed/rotation.rs:16-20
-        const float sign = ((neg >> lane) & 1u) ? -a.sign_mag : a.sign_mag;
+        const float mag = a.dev_signs != nullptr ? fabsf(a.dev_signs[0]) : a.sign_mag;
+        const float sign = ((neg >> lane) & 1u) ? -mag : mag;
         const float inv_sqrt = 1.0f / sqrtf(32.0f);
         for (int u = warp; u < 8 * 4; u += kWarps) {
             const int hh = u >> 2, b = u & 3;
@@ -948,7 +954,8 @@ int launch(const MmaArgs& a, int g, int q_dtype, bool allow_tma, const Codebook&
 // `counters` != nullptr fuses the merge into the kernel: [num_kv_heads] tickets, zeroed here unless the
 // caller vouches for them (counters_clean).
 int launch_decode_mma(const tqb_decode_params* p, int num_partitions, float* partial_out, float* partial_max,
-                      float* partial_sum, float sign_mag, unsigned* counters, bool counters_clean, cudaStream_t s) {
+                      float* partial_sum, float sign_mag, unsigned* counters, bool counters_clean, cudaStream_t s,
+                      const int* gate, int gate_want, const float* dev_signs) {
     const int g = p->num_q_heads / p->num_kv_heads;
     const int nblk = p->head_dim / kBlock;
     const bool all_outlier = p->outlier_blocks < 0 || p->outlier_blocks >= nblk;
@@ -982,6 +989,9 @@ int launch_decode_mma(const tqb_decode_params* p, int num_partitions, float* par
         a.app_v = p->append_v;
         a.outer_centroid = app_cb.c[app_cb.n - 1];   // precomputed/mod.rs:78
     }
+    a.gate = gate;
+    a.gate_want = gate_want;
+    a.dev_signs = dev_signs;
     a.counters = counters;
     a.out = p->out;
     a.lse_out = p->lse_out;
