@@ -387,11 +387,11 @@ __device__ __forceinline__ void stage_fill(FillPlan& f, bool issue, int stride, 
 // keeps its own online-softmax state; the four states are merged through shared memory at the
 // end and written as one split-K partial.
 //
-// NSPLIT = true (GQA group <= 4): the MMA columns 0..3 of O^T = V^T P' carry the f16 "hi" part of
-// P' for heads 0..3 and columns 4..7 the "lo" part, so one MMA delivers the split-precision
-// product.  NSPLIT = false (group 5..8): hi and lo take one MMA each.
+// NSPLIT = true (GQA group <= 4): the 8 MMA columns carry the f16 "hi" parts of heads 0..3 and then their
+// "lo" parts - of the rotated query in S = K~ Q~^T, of P' in O^T = V^T P' - so one MMA delivers the
+// split-precision product.  NSPLIT = false (group 5..8): 8 heads per MMA, hi and lo take one MMA each.
 //
-// TMA = true: stages are filled by the tensor copy engine (one lane per warp issues them); otherwise by
+// TMA = true: stages are filled by the tensor copy engine (one thread per CTA issues them); otherwise by
 // per-lane cp.async.  Both deliver the same bytes in the same swizzled layout.  Measured at 512 KV heads x
 // 8192 tokens: cp.async 181-184 us per launch, TMA 191-195 us (4-bit); 230 vs 236-239 us (3-bit).  A first
 // TMA version with one 16-token box set per warp (four small copies per warp and step) was slower still
@@ -408,7 +408,7 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
     extern __shared__ unsigned char s_dyn[];
     __shared__ __align__(8) unsigned long long s_bar[2][kStages];   // TMA staging: full / empty barriers of the stages
     __shared__ float s_q[8 * kD];   // rotated queries (prologue only)
-    __shared__ __align__(16) uint4 s_afr[8][32];   // A fragments of the rotated queries, [block * 2 + half][lane]
+    __shared__ __align__(16) uint4 s_qfr[8][32];   // MMA fragments of the rotated queries, [operand set * 4 + block][lane]
     const uint32_t dyn_base = (uint32_t)__cvta_generic_to_shared(s_dyn);
     const uint32_t lut_base = BITS == 3 ? ((dyn_base + 8191u) & ~8191u) : 0u;
     const uint32_t rings_base = BITS == 3 ? lut_base + 8192u : ((dyn_base + 1023u) & ~1023u);
@@ -550,7 +550,7 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
     // split-precision product; else two operand sets (hi, lo) of 8 heads.  For block b and half m the k-slots
     // (2j, 2j+1 | 2j+8, 2j+9) hold the dims that the code unpackers deliver:
     //   4-bit: 32b + 8j + 2m + (0, 4 | 1, 5)      3-bit: 32b + 8j + 4m + (0, 1 | 2, 3)
-    // s_afr[set * 4 + b][lane] = (b0, b1 of half 0, b0, b1 of half 1) of the lane's column n.
+    // s_qfr[set * 4 + b][lane] = (b0, b1 of half 0, b0, b1 of half 1) of the lane's column n.
     {
         const float* sq = s_q + (NSPLIT ? (n & 3) : n) * kD;
         const int b = warp;   // one block per warp
@@ -566,11 +566,11 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
                 r[2 * m] = lo_part ? pack_lo(qa, qb) : pack_hi(qa, qb);
                 r[2 * m + 1] = lo_part ? pack_lo(qc, qd) : pack_hi(qc, qd);
             }
-            s_afr[set * 4 + b][lane] = make_uint4(r[0], r[1], r[2], r[3]);
+            s_qfr[set * 4 + b][lane] = make_uint4(r[0], r[1], r[2], r[3]);
         }
     }
     __syncthreads();
-    const uint32_t afr_base = (uint32_t)__cvta_generic_to_shared(&s_afr[0][lane]);
+    const uint32_t qfr_base = (uint32_t)__cvta_generic_to_shared(&s_qfr[0][lane]);
     // After the scores, lane (n, j) holds tokens n and n + 8 of the step and the two heads
     //   h(e) = 2 (j & 1) + e (NSPLIT; lanes j and j ^ 2 hold the same values)  |  2 j + e (otherwise).
     // Columns of the P' operand: NSPLIT lanes j >= 2 supply the lo part, lanes j < 2 the hi part.
@@ -640,7 +640,7 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
                 float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
                 static_for<0, (NSPLIT ? 1 : 2)>([&](auto set_) {
                     constexpr int set = decltype(set_)::value;
-                    const uint4 q4 = lds128_volatile_o<(set * 4 + b) * 512>(afr_base);
+                    const uint4 q4 = lds128_volatile_o<(set * 4 + b) * 512>(qfr_base);
                     mma16816(acc, x[0][0], x[1][0], x[0][1], x[1][1], q4.x, q4.y);
                     mma16816(acc, x[0][2], x[1][2], x[0][3], x[1][3], q4.z, q4.w);
                 });
