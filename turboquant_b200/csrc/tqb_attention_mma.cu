@@ -387,9 +387,8 @@ __device__ __forceinline__ void stage_fill(FillPlan& f, bool issue, int stride, 
 // keeps its own online-softmax state; the four states are merged through shared memory at the
 // end and written as one split-K partial.
 //
-// NSPLIT = true (GQA group <= 4): the 8 MMA columns carry the f16 "hi" parts of heads 0..3 and then their
-// "lo" parts - of the rotated query in S = K~ Q~^T, of P' in O^T = V^T P' - so one MMA delivers the
-// split-precision product.  NSPLIT = false (group 5..8): 8 heads per MMA, hi and lo take one MMA each.
+// NSPLIT = true (GQA group <= 4): MMA columns 2h and 2h + 1 carry the f16 "hi" and "lo" part of head h - of
+// the rotated query in S = K~ Q~^T, of P' in O^T = V^T P' - so one MMA delivers the split-precision product.  NSPLIT = false (group 5..8): 8 heads per MMA, hi and lo take one MMA each.
 //
 // TMA = true: stages are filled by the tensor copy engine (one thread per CTA issues them); otherwise by
 // per-lane cp.async.  Both deliver the same bytes in the same swizzled layout.  Measured at 512 KV heads x
@@ -545,18 +544,18 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
     }
     __syncthreads();
     // Scores are computed as S = K~ Q~^T: the A operand is the unpacked K tile (M = 16 tokens, K = 16 dims of
-    // one block), the B operand holds the rotated queries (N = 8 columns).  NSPLIT (group <= 4): column c is
-    // the f16 hi part of q~ of head c for c < 4 and the lo part of head c - 4 otherwise, so one MMA gives the
-    // split-precision product; else two operand sets (hi, lo) of 8 heads.  For block b and half m the k-slots
+    // one block), the B operand holds the rotated queries (N = 8 columns).  NSPLIT (group <= 4): columns 2h and
+    // 2h + 1 are the f16 hi and lo parts of q~ of head h, so one MMA gives the split-precision product and
+    // both parts of a head land in the same lane; else two operand sets (hi, lo) of 8 heads.  For block b and half m the k-slots
     // (2j, 2j+1 | 2j+8, 2j+9) hold the dims that the code unpackers deliver:
     //   4-bit: 32b + 8j + 2m + (0, 4 | 1, 5)      3-bit: 32b + 8j + 4m + (0, 1 | 2, 3)
     // s_qfr[set * 4 + b][lane] = (b0, b1 of half 0, b0, b1 of half 1) of the lane's column n.
     {
-        const float* sq = s_q + (NSPLIT ? (n & 3) : n) * kD;
+        const float* sq = s_q + (NSPLIT ? (n >> 1) : n) * kD;
         const int b = warp;   // one block per warp
 #pragma unroll
         for (int set = 0; set < (NSPLIT ? 1 : 2); ++set) {
-            const bool lo_part = NSPLIT ? (n >= 4) : (set == 1);
+            const bool lo_part = NSPLIT ? (n & 1) : (set == 1);
             uint32_t r[4];
 #pragma unroll
             for (int m = 0; m < 2; ++m) {
@@ -571,13 +570,15 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
     }
     __syncthreads();
     const uint32_t qfr_base = (uint32_t)__cvta_generic_to_shared(&s_qfr[0][lane]);
-    // After the scores, lane (n, j) holds tokens n and n + 8 of the step and the two heads
-    //   h(e) = 2 (j & 1) + e (NSPLIT; lanes j and j ^ 2 hold the same values)  |  2 j + e (otherwise).
-    // Columns of the P' operand: NSPLIT lanes j >= 2 supply the lo part, lanes j < 2 the hi part.
-    const bool lo_lane = NSPLIT && j >= 2;
-    const __half2 nsel = u32_as_h2(lo_lane ? 0xBC00BC00u : 0u);   // half2(-1) | half2(0)
-
-    float m_run[2] = {kNegBig, kNegBig}, l_run[2] = {0.0f, 0.0f};   // per head h(e); l_run: this lane's tokens only
+    // After the scores, lane (n, j) holds tokens n and n + 8 of the step and kE heads:
+    //   NSPLIT: head j (its hi and lo columns 2j, 2j+1 are summed in the lane)  |  otherwise heads 2j, 2j+1.
+    constexpr int kE = NSPLIT ? 1 : 2;
+    float m_run[kE], l_run[kE];   // per head; l_run: this lane's tokens only
+#pragma unroll
+    for (int e = 0; e < kE; ++e) {
+        m_run[e] = kNegBig;
+        l_run[e] = 0.0f;
+    }
     float o[4][2][4];
 #pragma unroll
     for (int b = 0; b < 4; ++b)
@@ -653,11 +654,15 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
                 s[1][1] = fmaf(kb, acc[3], s[1][1]);
             });
         }
-        if (NSPLIT) {   // hi columns (lanes j < 2) + lo columns (lanes j >= 2)
+        float sc[2][kE];   // scores [token n | n + 8][head]
 #pragma unroll
-            for (int t = 0; t < 2; ++t)
+        for (int t = 0; t < 2; ++t) {
+            if (NSPLIT) {
+                sc[t][0] = s[t][0] + s[t][1];   // hi column + lo column of head j
+            } else {
 #pragma unroll
-                for (int e = 0; e < 2; ++e) s[t][e] += __shfl_xor_sync(0xffffffffu, s[t][e], 2);
+                for (int e = 0; e < kE; ++e) sc[t][e] = s[t][e];
+            }
         }
         if (gs + kGroup > t_end) {   // ragged tail: tokens past the end (of the sequence, or of the partition) get zero weight
             if (TMA) {
@@ -670,56 +675,74 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
             }
 #pragma unroll
             for (int t = 0; t < 2; ++t)
-                if (gs + n + 8 * t >= t_end) s[t][0] = s[t][1] = kNegBig;
+                if (gs + n + 8 * t >= t_end) {
+#pragma unroll
+                    for (int e = 0; e < kE; ++e) sc[t][e] = kNegBig;
+                }
         }
         // ---- online softmax: the 16 tokens of a head are spread over the 8 lane groups n ----
         // The reference value m_run is only raised when the step's maximum exceeds it by more than kLazy
         // (in log2 units): any common reference gives the same result, p stays below 2^kLazy, and the
         // rescaling of the 32 accumulators becomes rare.
         constexpr float kLazy = 6.0f;
-        float resc[2], p[2][2];
+        float resc[kE], p[2][kE];
+        bool changed = false;
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-            float mx = fmaxf(s[0][e], s[1][e]);
+        for (int e = 0; e < kE; ++e) {
+            float mx = fmaxf(sc[0][e], sc[1][e]);
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
             const float m_new = (mx - m_run[e] > kLazy) ? mx : m_run[e];
             resc[e] = ex2(m_run[e] - m_new);
+            changed |= resc[e] != 1.0f;
             m_run[e] = m_new;
-            p[0][e] = ex2(s[0][e] - m_new);
-            p[1][e] = ex2(s[1][e] - m_new);
+            p[0][e] = ex2(sc[0][e] - m_new);
+            p[1][e] = ex2(sc[1][e] - m_new);
             l_run[e] = l_run[e] * resc[e] + (p[0][e] + p[1][e]);
         }
-        if (__any_sync(0xffffffffu, resc[0] != 1.0f || resc[1] != 1.0f)) {
-            // columns (2j, 2j+1) of O^T belong to this lane's heads h(0), h(1)
+        if (__any_sync(0xffffffffu, changed)) {
+            // columns (2j, 2j+1) of O^T: NSPLIT the hi and lo column of head j, otherwise heads 2j and 2j+1
+            const float r0 = resc[0], r1 = resc[kE - 1];
 #pragma unroll
             for (int b = 0; b < 4; ++b)
 #pragma unroll
                 for (int m = 0; m < 2; ++m) {
-                    o[b][m][0] *= resc[0]; o[b][m][1] *= resc[1]; o[b][m][2] *= resc[0]; o[b][m][3] *= resc[1];
+                    o[b][m][0] *= r0; o[b][m][1] *= r1; o[b][m][2] *= r0; o[b][m][3] *= r1;
                 }
         }
         // ---- P' = p |s_v| as an exact f16 pair, in half2 arithmetic, then transposed for the next MMA ----
         // p = ph + pl (f16 each).  hi = rn(ph s) and ph s - hi are both f16 values (the product of two 11-bit
         // significands has 22 bits), so hi + lo with lo = fma(pl, s, fma(ph, s, -hi)) equals p s up to 2^-22
-        // relative.  Here a register pairs the lane's two heads of one token; movmatrix turns the 8 x 8 matrix
-        // (token rows, head columns) into the B fragment (tokens 2j, 2j+1 of column n) of O^T = V^T P'.
+        // relative.  A register holds the lane's two columns of one token row - NSPLIT: (hi, lo) of head j,
+        // otherwise the hi (or lo) parts of heads 2j, 2j+1; movmatrix turns each 8 x 8 matrix (token rows,
+        // columns) into the B fragment (tokens 2j, 2j+1 of column n) of O^T = V^T P'.
         uint32_t pq[NSPLIT ? 1 : 2][4][2];   // [hi | lo][block][octet]
+        uint32_t php = 0, plp = 0;           // NSPLIT: (ph, pl) of the lane's head for tokens (n, n + 8), packed
+        if (NSPLIT) {
+            php = pack_hi(p[0][0], p[1][0]);
+            plp = pack_lo(p[0][0], p[1][0]);
+        }
         static_for<0, 2>([&](auto t_) {
             constexpr int t = decltype(t_)::value;
-            const __half2 ph = u32_as_h2(pack_hi(p[t][0], p[t][1]));
-            __half2 pl = u32_as_h2(pack_lo(p[t][0], p[t][1]));
-            if (NSPLIT && !lo_lane) pl = u32_as_h2(0u);   // hi lanes: lo = fma(0, s, fma(ph, s, -0 * hi)) = hi
+            __half2 ph, pl, nsel;
+            if (NSPLIT) {
+                ph = u32_as_h2(__byte_perm(php, 0u, t ? 0x3232 : 0x1010));   // (ph_t, ph_t)
+                pl = u32_as_h2(__byte_perm(plp, 0u, t ? 0x3244 : 0x1044));   // (0, pl_t)
+                nsel = u32_as_h2(0xBC000000u);                               // (0, -1): the hi slot keeps hi, the lo slot gets the residual
+            } else {
+                ph = u32_as_h2(pack_hi(p[t][0], p[t][kE - 1]));
+                pl = u32_as_h2(pack_lo(p[t][0], p[t][kE - 1]));
+                nsel = u32_as_h2(0xBC00BC00u);
+            }
             const uint2 vsr = lds64_o<kSD + t * 64>(bS);   // V scale row of token n + 8t
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
                 const __half2 sv = __habs2(u32_as_h2(__byte_perm(b < 2 ? vsr.x : vsr.y, 0u, (b & 1) ? 0x3232 : 0x1010)));   // (s, s)
                 const __half2 hi = __hmul2(ph, sv);
-                const __half2 nhi = NSPLIT ? __hmul2(hi, nsel) : __hneg2(hi);
-                const __half2 lo = __hfma2(pl, sv, __hfma2(ph, sv, nhi));
+                const __half2 lo = __hfma2(pl, sv, __hfma2(ph, sv, NSPLIT ? __hmul2(hi, nsel) : __hneg2(hi)));
                 if (NSPLIT) {
-                    pq[0][b][t] = movmatrix_trans(h2_as_u32(lo));
+                    pq[0][b][t] = movmatrix_trans(h2_as_u32(lo));   // (hi', lo') of head j
                 } else {
                     pq[0][b][t] = movmatrix_trans(h2_as_u32(hi));
                     pq[NSPLIT ? 0 : 1][b][t] = movmatrix_trans(h2_as_u32(lo));
@@ -778,13 +801,13 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
 
     // ---- merge the four warps (scores are in log2 units; partials are stored in natural units) ----
 #pragma unroll
-    for (int e = 0; e < 2; ++e) {
+    for (int e = 0; e < kE; ++e) {
         float l = l_run[e];   // sum over the lane groups n (each holds two tokens per step)
         l += __shfl_xor_sync(0xffffffffu, l, 4);
         l += __shfl_xor_sync(0xffffffffu, l, 8);
         l += __shfl_xor_sync(0xffffffffu, l, 16);
-        if (n == 0 && (!NSPLIT || j < 2)) {
-            const int h = (NSPLIT ? 2 * (j & 1) : 2 * j) + e;
+        if (n == 0) {
+            const int h = NSPLIT ? j : 2 * j + e;
             s_m[warp][h] = m_run[e];
             s_l[warp][h] = l;
         }
@@ -811,8 +834,7 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
             for (int w = 0; w < kWarps; ++w) {
                 const float e = ex2(s_m[w][hh] - M);
                 L = fmaf(s_l[w][hh], e, L);
-                float ov = s_o[w][hh][d];
-                if (NSPLIT) ov += s_o[w][hh + 4][d];
+                const float ov = NSPLIT ? s_o[w][2 * hh][d] + s_o[w][2 * hh + 1][d] : s_o[w][hh][d];
                 O = fmaf(ov, e, O);
             }
             const size_t pi = (size_t)(kvh * g + hh) * a.num_partitions + part;
