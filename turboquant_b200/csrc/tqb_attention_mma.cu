@@ -353,14 +353,15 @@ __device__ __forceinline__ FillPlan make_plan(const MmaArgs& a, size_t row0, int
 // shared address `st`, then moves the pointers on by `stride` tokens.  In the final group of a sequence rows
 // past the last valid token re-read the last token (they are masked later).
 template <int BITS>
-__device__ __forceinline__ void stage_fill(FillPlan& f, bool issue, int stride, int gs, int last, uint32_t st) {
+__device__ __forceinline__ void stage_fill(FillPlan& f, bool issue, bool ragged, int stride, int gs, int last, uint32_t st) {
     using G = Geo<BITS>;
+    const bool has1 = BITS == 4 || f.has1;   // 64 pieces of a 4-bit stage: two per lane
     if (issue) {
-        if (gs + kGroup <= last + 1) {
+        if (!ragged) {
             const uint32_t d0 = st + f.dst0, d1 = st + f.dst1;
             cp_async16_o<0, 0>(d0, f.k);
             cp_async16_o<G::kIdxB, 0>(d0, f.v);
-            if (f.has1) {
+            if (has1) {
                 cp_async16_o<0, 512>(d1, f.k);
                 cp_async16_o<G::kIdxB, 512>(d1, f.v);
             }
@@ -371,7 +372,7 @@ __device__ __forceinline__ void stage_fill(FillPlan& f, bool issue, int stride, 
             const long long bs = (long long)(min(gs + f.ts, last) - (gs + f.ts)) * 4;
             cp_async16(st + f.dst0, f.k + b0);
             cp_async16(st + G::kIdxB + f.dst0, f.v + b0);
-            if (f.has1) {
+            if (has1) {
                 cp_async16(st + f.dst1, f.k + 512 + b1);
                 cp_async16(st + G::kIdxB + f.dst1, f.v + 512 + b1);
             }
@@ -484,7 +485,7 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
     } else {
 #pragma unroll
         for (int i = 0; i < kStages - 1; ++i) {
-            stage_fill<BITS>(plan, i < ngroups, stride, first + i * stride, last, ring + i * G::kStageB);
+            stage_fill<BITS>(plan, i < ngroups, first + i * stride + kGroup > last + 1, stride, first + i * stride, last, ring + i * G::kStageB);
             cp_async_commit();
         }
     }
@@ -587,8 +588,13 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
 #pragma unroll
             for (int i = 0; i < 4; ++i) o[b][m][i] = 0.0f;
 
+    // Loop control in terms of iteration numbers fixed before the loop: the last step that still refills a
+    // stage, the step whose refill is the (only possibly) ragged last group, and the first step with tokens to mask.
+    const int fill_end = ngroups - (kStages - 1);                                    // refill while it < fill_end
+    const int rag_fill_it = (first + (ngroups - 1) * stride + kGroup > last + 1) ? fill_end - 1 : -1;
+    const int rag_from = (t_end - kGroup - first < 0) ? 0 : (t_end - kGroup - first) / stride + 1;
+    uint32_t st_prev = ring + (kStages - 1) * kPitch;   // cp.async: the stage consumed one step ago is the one refilled now
     for (int it = 0; it < nsteps; ++it) {
-        const int gs = first + it * stride;
         if (TMA) {
             // A warp whose 16 rows of the tile lie past the end of the partition runs the step on them all
             // the same: every such token is masked below and contributes exactly nothing.
@@ -605,9 +611,8 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
                 break;
             }
         } else {
-            stage_fill<BITS>(plan, it + kStages - 1 < ngroups, stride, gs + (kStages - 1) * stride, last, st_fill);
+            stage_fill<BITS>(plan, it < fill_end, it == rag_fill_it, stride, first + (it + kStages - 1) * stride, last, st_prev);
             cp_async_commit();
-            st_fill = (st_fill + G::kStageB == ring + G::kRingB) ? ring : st_fill + G::kStageB;
             cp_async_wait<kStages - 1>();
             __syncwarp();
         }
@@ -664,7 +669,8 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
                 for (int e = 0; e < kE; ++e) sc[t][e] = s[t][e];
             }
         }
-        if (gs + kGroup > t_end) {   // ragged tail: tokens past the end (of the sequence, or of the partition) get zero weight
+        if (it >= rag_from) {   // ragged tail: tokens past the end (of the sequence, or of the partition) get zero weight
+            const int gs = first + it * stride;
             if (TMA) {
                 // the tensor copies brought whatever lies behind the last token: clear those scale rows, so
                 // that a zero probability never meets an Inf or NaN scale
@@ -786,6 +792,7 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
             }
         });
         __syncwarp();   // every lane is done with this stage before it is refilled
+        st_prev = st;
         st = (st + kPitch == ring + kStages * kPitch) ? ring : st + kPitch;
         if (TMA) {
             if (lane == 0) mbar_arrive(empty0 + boff);   // this warp releases its rows of the tile
