@@ -720,41 +720,40 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
         // ---- P' = p |s_v| as an exact f16 pair, in half2 arithmetic, then transposed for the next MMA ----
         // p = ph + pl (f16 each).  hi = rn(ph s) and ph s - hi are both f16 values (the product of two 11-bit
         // significands has 22 bits), so hi + lo with lo = fma(pl, s, fma(ph, s, -hi)) equals p s up to 2^-22
-        // relative.  A register holds the lane's two columns of one token row - NSPLIT: (hi, lo) of head j,
-        // otherwise the hi (or lo) parts of heads 2j, 2j+1; movmatrix turns each 8 x 8 matrix (token rows,
+        // relative.  movmatrix takes registers holding the lane's two columns of one token row - NSPLIT: (hi, lo)
+        // of head j, otherwise the hi (or lo) parts of heads 2j, 2j+1 - and turns each 8 x 8 matrix (token rows,
         // columns) into the B fragment (tokens 2j, 2j+1 of column n) of O^T = V^T P'.
         uint32_t pq[NSPLIT ? 1 : 2][4][2];   // [hi | lo][block][octet]
-        uint32_t php = 0, plp = 0;           // NSPLIT: (ph, pl) of the lane's head for tokens (n, n + 8), packed
         if (NSPLIT) {
-            php = pack_hi(p[0][0], p[1][0]);
-            plp = pack_lo(p[0][0], p[1][0]);
-        }
-        static_for<0, 2>([&](auto t_) {
-            constexpr int t = decltype(t_)::value;
-            __half2 ph, pl, nsel;
-            if (NSPLIT) {
-                ph = u32_as_h2(__byte_perm(php, 0u, t ? 0x3232 : 0x1010));   // (ph_t, ph_t)
-                pl = u32_as_h2(__byte_perm(plp, 0u, t ? 0x3244 : 0x1044));   // (0, pl_t)
-                nsel = u32_as_h2(0xBC000000u);                               // (0, -1): the hi slot keeps hi, the lo slot gets the residual
-            } else {
-                ph = u32_as_h2(pack_hi(p[t][0], p[t][kE - 1]));
-                pl = u32_as_h2(pack_lo(p[t][0], p[t][kE - 1]));
-                nsel = u32_as_h2(0xBC00BC00u);
-            }
-            const uint2 vsr = lds64_o<kSD + t * 64>(bS);   // V scale row of token n + 8t
+            // one head per lane: the half2 lanes run over the two tokens (n, n + 8); three instructions per
+            // block give (hi', hi') and (lo', lo') of both tokens, two PRMTs re-pair them per token
+            const __half2 ph = u32_as_h2(pack_hi(p[0][0], p[1][0])), pl = u32_as_h2(pack_lo(p[0][0], p[1][0]));
+            const uint2 vs0 = lds64_o<kSD>(bS), vs1 = lds64_o<kSD + 64>(bS);   // V scale rows of tokens n, n + 8
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
-                const __half2 sv = __habs2(u32_as_h2(__byte_perm(b < 2 ? vsr.x : vsr.y, 0u, (b & 1) ? 0x3232 : 0x1010)));   // (s, s)
+                const __half2 sv = __habs2(u32_as_h2(__byte_perm(b < 2 ? vs0.x : vs0.y, b < 2 ? vs1.x : vs1.y, (b & 1) ? 0x7632 : 0x5410)));
                 const __half2 hi = __hmul2(ph, sv);
-                const __half2 lo = __hfma2(pl, sv, __hfma2(ph, sv, NSPLIT ? __hmul2(hi, nsel) : __hneg2(hi)));
-                if (NSPLIT) {
-                    pq[0][b][t] = movmatrix_trans(h2_as_u32(lo));   // (hi', lo') of head j
-                } else {
+                const __half2 lo = __hfma2(pl, sv, __hfma2(ph, sv, __hneg2(hi)));
+                pq[0][b][0] = movmatrix_trans(__byte_perm(h2_as_u32(hi), h2_as_u32(lo), 0x5410));   // token n: (hi', lo') of head j
+                pq[0][b][1] = movmatrix_trans(__byte_perm(h2_as_u32(hi), h2_as_u32(lo), 0x7632));   // token n + 8
+            }
+        } else {
+            static_for<0, 2>([&](auto t_) {
+                constexpr int t = decltype(t_)::value;
+                const __half2 ph = u32_as_h2(pack_hi(p[t][0], p[t][kE - 1]));
+                const __half2 pl = u32_as_h2(pack_lo(p[t][0], p[t][kE - 1]));
+                const uint2 vsr = lds64_o<kSD + t * 64>(bS);   // V scale row of token n + 8t
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    const __half2 svw = u32_as_h2(b < 2 ? vsr.x : vsr.y);
+                    const __half2 sv = __habs2((b & 1) ? __high2half2(svw) : __low2half2(svw));   // (s, s)
+                    const __half2 hi = __hmul2(ph, sv);
+                    const __half2 lo = __hfma2(pl, sv, __hfma2(ph, sv, __hneg2(hi)));
                     pq[0][b][t] = movmatrix_trans(h2_as_u32(hi));
                     pq[NSPLIT ? 0 : 1][b][t] = movmatrix_trans(h2_as_u32(lo));
                 }
-            }
-        });
+            });
+        }
         // ---- O^T += V^T P' ----
         uint32_t vw[2][4];   // 4-bit: codes 4n..4n+3 of (token 2j | token 2j+1 << 16), indexed like kw
         if (BITS == 4) {
