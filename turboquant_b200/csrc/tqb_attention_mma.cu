@@ -594,6 +594,7 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
     const int rag_fill_it = (first + (ngroups - 1) * stride + kGroup > last + 1) ? fill_end - 1 : -1;
     const int rag_from = (t_end - kGroup - first < 0) ? 0 : (t_end - kGroup - first) / stride + 1;
     uint32_t st_prev = ring + (kStages - 1) * kPitch;   // cp.async: the stage consumed one step ago is the one refilled now
+#pragma unroll 2
     for (int it = 0; it < nsteps; ++it) {
         if (TMA) {
             // A warp whose 16 rows of the tile lie past the end of the partition runs the step on them all
