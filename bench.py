@@ -37,7 +37,9 @@ import torch  # noqa: E402
 CFG = dict(layers=32, hq=32, hkv=8, head_dim=128, batch=64, ctx=8192, bits=4)
 WORKLOAD = "llama3-8b-shaped PQO4 batched decode: 32 layers, 32 q heads, 8 kv heads, head_dim 128, batch 64, ctx 8192"
 METRIC = "decode_attn_effective_hbm_gbps"
-BYTES_PER_TOKEN_HEAD = 2 * (CFG["head_dim"] * CFG["bits"] // 8 + (CFG["head_dim"] // 32) * 2)  # 144 B
+def bytes_per_token_head():
+    """Algorithmic bytes of one (token, KV head): packed K and V codes plus their four f16 scales each (144 B for PQO4)."""
+    return 2 * (CFG["head_dim"] * CFG["bits"] // 8 + (CFG["head_dim"] // 32) * 2)
 
 
 def peaks():
@@ -160,7 +162,7 @@ def run_ours(args):
 
     def bytes_of_steps(first_len, nsteps):
         # each step attends over the cache after its own append
-        return sum(L * B * HKV * (first_len + 1 + s) * BYTES_PER_TOKEN_HEAD for s in range(nsteps))
+        return sum(L * B * HKV * (first_len + 1 + s) * bytes_per_token_head() for s in range(nsteps))
 
     # ---- value: device-resident steps ----
     for i in range(args.warmup):
@@ -234,7 +236,7 @@ def run_ours(args):
             if rep == 1:
                 durs.append(s0.elapsed_time(s1))
     launch_ms = float(np.mean(durs))
-    launch_bytes = nheads * kv_len * BYTES_PER_TOKEN_HEAD
+    launch_bytes = nheads * kv_len * bytes_per_token_head()
     peak, peak_src = peaks()
 
     # ---- max over ranks ----
@@ -295,7 +297,7 @@ class CpuSample:
         self.kp = np.ascontiguousarray(np.tile(kp.reshape(CFG["hkv"], ctx, -1), (seqs, 1, 1)))
         self.ks = np.ascontiguousarray(np.tile(ks.reshape(CFG["hkv"], ctx, -1), (seqs, 1, 1)))
         self.q = (rng.standard_normal((hq, D)) / np.sqrt(D)).astype(np.float32)
-        self.bytes = hkv * ctx * BYTES_PER_TOKEN_HEAD
+        self.bytes = hkv * ctx * bytes_per_token_head()
 
     def run(self):
         t0 = time.perf_counter()
@@ -358,9 +360,11 @@ def main():
     ap.add_argument("--profile-case", action="store_true",
                     help="small case for profiler captures: 2 layers, batch 16 (151 MB of packed cache per launch, "
                          "above the L2 size, 0.4 GB on the device); its numbers are not bench values")
+    ap.add_argument("--profile-bits", type=int, default=4, choices=[3, 4],
+                    help="with --profile-case: code width of the small case (3 = PQO3, 4 = PQO4)")
     args = ap.parse_args()
     if args.profile_case:
-        CFG.update(layers=2, batch=16)
+        CFG.update(layers=2, batch=16, bits=args.profile_bits)
         args.no_cpu = True
     if args.impl == "reference":
         run_reference(args)
