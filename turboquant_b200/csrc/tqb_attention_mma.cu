@@ -358,12 +358,14 @@ __device__ __forceinline__ void stage_fill(FillPlan& f, bool issue, bool ragged,
     const bool has1 = BITS == 4 || f.has1;   // 64 pieces of a 4-bit stage: two per lane
     if (issue) {
         if (!ragged) {
-            const uint32_t d0 = st + f.dst0, d1 = st + f.dst1;
+            // the lane's second piece sits 512 bytes further, in global memory and (the swizzle of row t + 8
+            // equals that of row t) in the stage
+            const uint32_t d0 = st + f.dst0;
             cp_async16_o<0, 0>(d0, f.k);
             cp_async16_o<G::kIdxB, 0>(d0, f.v);
             if (has1) {
-                cp_async16_o<0, 512>(d1, f.k);
-                cp_async16_o<G::kIdxB, 512>(d1, f.v);
+                cp_async16_o<512, 512>(d0, f.k);
+                cp_async16_o<G::kIdxB + 512, 512>(d0, f.v);
             }
             cp_async8(st + f.dsts, f.sc);
         } else {
@@ -654,17 +656,22 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
                 const __half2 pa = u32_as_h2(b < 2 ? sca.x : sca.y), pb = u32_as_h2(b < 2 ? scb.x : scb.y);
                 const float ka = fabsf((b & 1) ? __high2float(pa) : __low2float(pa));
                 const float kb = fabsf((b & 1) ? __high2float(pb) : __low2float(pb));
-                s[0][0] = fmaf(ka, acc[0], s[0][0]);
-                s[0][1] = fmaf(ka, acc[1], s[0][1]);
-                s[1][0] = fmaf(kb, acc[2], s[1][0]);
-                s[1][1] = fmaf(kb, acc[3], s[1][1]);
+                if (NSPLIT) {   // columns 2j, 2j+1 are the hi and lo part of one head: one running sum per token
+                    s[0][0] = fmaf(ka, acc[1], fmaf(ka, acc[0], s[0][0]));
+                    s[1][0] = fmaf(kb, acc[3], fmaf(kb, acc[2], s[1][0]));
+                } else {
+                    s[0][0] = fmaf(ka, acc[0], s[0][0]);
+                    s[0][1] = fmaf(ka, acc[1], s[0][1]);
+                    s[1][0] = fmaf(kb, acc[2], s[1][0]);
+                    s[1][1] = fmaf(kb, acc[3], s[1][1]);
+                }
             });
         }
         float sc[2][kE];   // scores [token n | n + 8][head]
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
             if (NSPLIT) {
-                sc[t][0] = s[t][0] + s[t][1];   // hi column + lo column of head j
+                sc[t][0] = s[t][0];
             } else {
 #pragma unroll
                 for (int e = 0; e < kE; ++e) sc[t][e] = s[t][e];
