@@ -303,20 +303,42 @@ __global__ void scores_kernel(const float* __restrict__ q, const float* __restri
     const long long warp_id = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
     const int nwords = pb >> 2;
-    for (long long i = warp_id; i < n; i += nwarps) {
-        const uint32_t word = lane < nwords ? __ldg(reinterpret_cast<const uint32_t*>(packed + i * pb) + lane) : 0u;
-        const uint32_t sw = lane < W ? __ldg(reinterpret_cast<const uint32_t*>(signs + i * (D / 8)) + lane) : 0u;
-        float base = 0.0f, corr = 0.0f;
+    // kU keys per warp step: their loads and the two shuffle reductions per key are independent chains, which
+    // hides the latency that a one-key-at-a-time loop exposes
+    constexpr int kU = 4;
+    for (long long i0 = warp_id * kU; i0 < n; i0 += nwarps * kU) {
+        uint32_t word[kU], sw[kU];
+        float sc[kU], rn[kU];
 #pragma unroll
-        for (int k = 0; k < EPL; ++k) {
-            base = fmaf(qr[k], s_c[code_at(word, lane + 32 * k, bits)], base);
-            const uint32_t w = __shfl_sync(0xffffffffu, sw, k);
-            corr = fmaf(rqv[k], ((w >> lane) & 1u) ? 1.0f : -1.0f, corr);
+        for (int u = 0; u < kU; ++u) {
+            const long long i = i0 + u < n ? i0 + u : n - 1;
+            word[u] = lane < nwords ? __ldg(reinterpret_cast<const uint32_t*>(packed + i * pb) + lane) : 0u;
+            sw[u] = lane < W ? __ldg(reinterpret_cast<const uint32_t*>(signs + i * (D / 8)) + lane) : 0u;
+            sc[u] = f16_bits_to_f32(__ldg(scales + i));
+            rn[u] = f16_bits_to_f32(__ldg(rnorms + i));
         }
-        base = warp_sum(base) * f16_bits_to_f32(__ldg(scales + i));
-        corr = warp_sum(corr);
-        const float cc = (f16_bits_to_f32(__ldg(rnorms + i)) * 1.2533141f) / sqrt_d;  // qjl.rs:263-265
-        if (lane == 0) scores[i] = base + cc * corr;
+        float base[kU], corr[kU];
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+            base[u] = 0.0f;
+            corr[u] = 0.0f;
+#pragma unroll
+            for (int k = 0; k < EPL; ++k) {
+                base[u] = fmaf(qr[k], s_c[code_at(word[u], lane + 32 * k, bits)], base[u]);
+                const uint32_t w = __shfl_sync(0xffffffffu, sw[u], k);
+                corr[u] = fmaf(rqv[k], ((w >> lane) & 1u) ? 1.0f : -1.0f, corr[u]);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+            base[u] = warp_sum(base[u]) * sc[u];
+            corr[u] = warp_sum(corr[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+            const float cc = (rn[u] * 1.2533141f) / sqrt_d;  // qjl.rs:263-265
+            if (lane == 0 && i0 + u < n) scores[i0 + u] = base[u] + cc * corr[u];
+        }
     }
 }
 
@@ -338,11 +360,23 @@ __global__ void weighted_values_partial_kernel(const float* __restrict__ w, cons
     float acc[EPL];
 #pragma unroll
     for (int k = 0; k < EPL; ++k) acc[k] = 0.0f;
-    for (long long i = (long long)blockIdx.x * warps + warp; i < n; i += (long long)gridDim.x * warps) {
-        const uint32_t word = lane < nwords ? __ldg(reinterpret_cast<const uint32_t*>(packed + i * pb) + lane) : 0u;
-        const float ws = __ldg(w + i) * f16_bits_to_f32(__ldg(scales + i));
+    // four values per warp step (independent loads); each lane still adds its elements in value order, so the
+    // result does not depend on the grouping
+    constexpr int kU = 4;
+    const long long wid = (long long)blockIdx.x * warps + warp, nw = (long long)gridDim.x * warps;
+    for (long long i0 = wid * kU; i0 < n; i0 += nw * kU) {
+        uint32_t word[kU];
+        float ws[kU];
 #pragma unroll
-        for (int k = 0; k < EPL; ++k) acc[k] = fmaf(ws, s_c[code_at(word, lane + 32 * k, bits)], acc[k]);
+        for (int u = 0; u < kU; ++u) {
+            const long long i = i0 + u < n ? i0 + u : n - 1;
+            word[u] = lane < nwords ? __ldg(reinterpret_cast<const uint32_t*>(packed + i * pb) + lane) : 0u;
+            ws[u] = i0 + u < n ? __ldg(w + i) * f16_bits_to_f32(__ldg(scales + i)) : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < kU; ++u)
+#pragma unroll
+            for (int k = 0; k < EPL; ++k) acc[k] = fmaf(ws[u], s_c[code_at(word[u], lane + 32 * k, bits)], acc[k]);
     }
 #pragma unroll
     for (int k = 0; k < EPL; ++k) s_acc[warp][lane + 32 * k] = acc[k];
