@@ -143,6 +143,31 @@ def test_config2_scores_and_weighted_output():
     assert np.abs(out - o.weighted_values(3, 128, 42, w, vp, vs)).max() < 1e-5   # far inside 2e-3
 
 
+@pytest.mark.parametrize("bits,dim,n", [(3, 128, 9001), (4, 128, 8195), (3, 64, 4100), (4, 256, 4097), (4, 64, 5003), (3, 256, 4096)])
+def test_long_lists_scores_and_weighted_values(bits, dim, n):
+    # lists of 4,096 entries and more run on the tabulated-query / lane-per-32-elements kernels
+    rng = np.random.default_rng(bits * 1000 + dim + n)
+    keys = rng.standard_normal((n, dim)).astype(np.float32)
+    keys[:: 97] *= 30.0
+    keys[5] = 0.0
+    q = (rng.standard_normal(dim) / np.sqrt(dim)).astype(np.float32)
+    cfg = tq.TurboQuantConfig(bits, dim).with_seed(11)
+    p, s, sg, rn = tq.qjl_quantize_batch(cfg, dev(keys), 77)
+    rq = tq.query_projections(dev(q), dim, 77)
+    got = tq.qjl_attention_scores(cfg, dev(q), rq.reshape(-1), p, s, sg, rn).cpu().numpy()
+    want = o.attention_scores(bits, dim, 11, 77, q, p.cpu().numpy(), u16(s), sg.cpu().numpy(), u16(rn), nthreads=8)
+    scale = np.abs(want).max()
+    assert np.abs(got - want).max() < 2e-6 * max(scale, 1.0) + 1e-5
+    # the short-list kernel on a prefix agrees too
+    short = tq.qjl_attention_scores(cfg, dev(q), rq.reshape(-1), p[:1000], s[:1000], sg[:1000], rn[:1000]).cpu().numpy()
+    assert np.abs(short - want[:1000]).max() < 2e-6 * max(scale, 1.0) + 1e-5
+    w = rng.random(n).astype(np.float32)
+    w /= w.sum()
+    out = tq.weighted_values(cfg, dev(w), p, s).cpu().numpy()
+    ref = o.weighted_values(bits, dim, 11, w, p.cpu().numpy(), u16(s))
+    assert np.abs(out - ref).max() < 1e-5 * max(np.abs(ref).max(), 1.0)
+
+
 def test_kv_cache_push_batch_equals_push_and_ranges():
     # src/attention.rs:1375-1430 (push_batch == repeated push, bit for bit), :1221-1296 (ranges)
     rng = np.random.default_rng(1)

@@ -259,6 +259,13 @@ template <typename T, int BITS>
 __global__ void __launch_bounds__(kThreads)
 block_quantize_pqo_kernel(QuantArgs a, Codebook cb) {
     if (blockIdx.y != 0) { a.x = a.x2; a.indices = a.indices2; a.scales = a.scales2; }
+    __shared__ float2 s_lut[BITS == 3 ? 256 : 1];
+    const float2* lut = nullptr;
+    if (BITS == 3) {
+        build_cell_table(cb, 7, s_lut, threadIdx.x, kThreads);
+        __syncthreads();
+        lut = s_lut;
+    }
     const unsigned total = (unsigned)(a.n_rows * a.nblk);
     const unsigned nblk = (unsigned)a.nblk;
     const long long xrow = a.x_row_stride ? a.x_row_stride : (long long)a.nblk * kBlock;
@@ -267,7 +274,7 @@ block_quantize_pqo_kernel(QuantArgs a, Codebook cb) {
         const unsigned row = blk / nblk, bv = blk - row * nblk;
         uint32_t w[4];
         const float scale = pqo_quantize_block<T, BITS>(reinterpret_cast<const T*>(a.x) + (long long)row * xrow + bv * kBlock, cb,
-                                                        a.outer_centroid, w);
+                                                        a.outer_centroid, w, lut);
         long long orow = row;
         if (a.map.rows_per_group != 0) {   // 32-bit division: row and rows_per_group are below 2^31 here
             const unsigned rpg = (unsigned)a.map.rows_per_group;

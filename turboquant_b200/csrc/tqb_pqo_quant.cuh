@@ -62,10 +62,36 @@ __device__ __forceinline__ void butterfly32_regs(float (&v)[32]) {
 constexpr uint32_t kSignMask = 0xB1A6D4B2u;   // bit j set <=> sign j is -1 (precomputed/rotation.rs:16-20)
 
 
+// Cell table for the 3-bit boundary search: cell c = round(t * kCellScale + kCellHalf); the 256 cells are far narrower
+// than the gap between two boundaries, so a cell (widened by kCellSlop on both sides to absorb the rounding
+// of the cell index) holds at most one boundary:  code = below + (t > bnd), exactly the count of
+// boundaries below t.  .x = that boundary (FLT_MAX when the cell has none), .y = bit pattern of the number
+// of boundaries under the cell.  |t| <= outer centroid (2.1520 for the 3-bit table) < 2.2 by construction
+// of the MaxNorm scale, so the index never leaves the table.
+constexpr float kCellScale = 58.0f;
+constexpr float kCellHalf = 128.0f;   // an integer, so that kCellHalf + 1.5 * 2^23 is exact
+constexpr float kCellSlop = 1e-3f;
+__device__ __forceinline__ void build_cell_table(const Codebook& cb, int n_bnd, float2* lut, int tid, int nthreads) {
+    for (int c = tid; c < 256; c += nthreads) {
+        const float lo = ((float)c - 0.5f - kCellHalf) / kCellScale - kCellSlop;
+        const float hi = ((float)c + 0.5f - kCellHalf) / kCellScale + kCellSlop;
+        float bnd = 3.0e38f;
+        unsigned below = 0;
+        for (int k = 0; k < n_bnd; ++k) {
+            const float b = cb.b[k];
+            if (b < lo) ++below;
+            else if (b <= hi) bnd = b;
+        }
+        lut[c] = make_float2(bnd, __uint_as_float(below));
+    }
+}
+
 // x: the block's 32 input values (16-byte aligned).  w: packed codes (4 * BITS bytes, LSB-first), returns the
-// f32 scale (before the outlier sign).  cb: the outlier codebook of BITS bits.
+// f32 scale (before the outlier sign).  cb: the outlier codebook of BITS bits.  lut: the 3-bit cell table in
+// shared memory (build_cell_table), or nullptr for the register bisection.
 template <typename T, int BITS>
-__device__ __forceinline__ float pqo_quantize_block(const T* x, const Codebook& cb, float outer_centroid, uint32_t (&w)[4]) {
+__device__ __forceinline__ float pqo_quantize_block(const T* x, const Codebook& cb, float outer_centroid, uint32_t (&w)[4],
+                                                    const float2* lut = nullptr) {
     const float inv_sqrt = 1.0f / sqrtf((float)kBlock);
     const float R = cb.c[(1 << BITS) - 1];
     const float inv_step = 15.0f / (2.0f * R);
@@ -111,12 +137,19 @@ __device__ __forceinline__ float pqo_quantize_block(const T* x, const Codebook& 
             const float q = rot * r;
             const float rem = fmaf(-q, scale, rot);
             const float t = fmaf(rem, r, q);           // == rot / scale, correctly rounded
-            // bisection over the 7 boundaries (constant bank operands)
-            const bool p1 = t > cb.b[3];
-            const bool p2 = t > (p1 ? cb.b[5] : cb.b[1]);
-            const float t3 = p1 ? (p2 ? cb.b[6] : cb.b[4]) : (p2 ? cb.b[2] : cb.b[0]);
-            const bool p3 = t > t3;
-            const unsigned c = (p1 ? 4u : 0u) + (p2 ? 2u : 0u) + (p3 ? 1u : 0u);
+            unsigned c;
+            if (lut != nullptr) {
+                const float y = fmaf(q, kCellScale, kCellHalf + 12582912.0f);   // round to nearest cell
+                const float2 e = lut[__float_as_uint(y) & 255u];
+                c = __float_as_uint(e.y) + (t > e.x ? 1u : 0u);
+            } else {
+                // bisection over the 7 boundaries (constant bank operands)
+                const bool p1 = t > cb.b[3];
+                const bool p2 = t > (p1 ? cb.b[5] : cb.b[1]);
+                const float t3 = p1 ? (p2 ? cb.b[6] : cb.b[4]) : (p2 ? cb.b[2] : cb.b[0]);
+                const bool p3 = t > t3;
+                c = (p1 ? 4u : 0u) + (p2 ? 2u : 0u) + (p3 ? 1u : 0u);
+            }
             const int bit = 3 * i;
             w[bit >> 5] += c << (bit & 31);
             if ((bit & 31) > 29) w[(bit >> 5) + 1] += c >> (32 - (bit & 31));

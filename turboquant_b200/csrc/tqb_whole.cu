@@ -343,6 +343,7 @@ __global__ void scores_kernel(const float* __restrict__ q, const float* __restri
 }
 
 constexpr int kWvBlocks = 296;  // two CTAs per SM
+constexpr long long kListMin = 4096;   // shorter lists stay on the warp-per-key kernels (no table build)
 
 // weighted_values (src/attention.rs:371-408), accumulated in the rotated domain:
 // sum_t w_t s_t sigma .* H(c_t)/sqrt(d) = sigma .* H(sum_t w_t s_t c_t)/sqrt(d).
@@ -389,20 +390,208 @@ __global__ void weighted_values_partial_kernel(const float* __restrict__ w, cons
 }
 
 template <int EPL>
-__global__ void weighted_values_final_kernel(const float* __restrict__ partial, int nparts, float* __restrict__ out,
-                                             uint64_t seed, float inv_sqrt_d) {
+__global__ void __launch_bounds__(256)
+weighted_values_final_kernel(const float* __restrict__ partial, int nparts, float* __restrict__ out, uint64_t seed,
+                             float inv_sqrt_d) {
     constexpr int D = 32 * EPL;
-    const int lane = threadIdx.x & 31;
+    __shared__ float s_part[8][D];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     float v[EPL];
+#pragma unroll
+    for (int k = 0; k < EPL; ++k) v[k] = 0.0f;
+    for (int p = warp; p < nparts; p += 8) {
+#pragma unroll
+        for (int k = 0; k < EPL; ++k) v[k] += partial[(size_t)p * D + lane + 32 * k];
+    }
+#pragma unroll
+    for (int k = 0; k < EPL; ++k) s_part[warp][lane + 32 * k] = v[k];
+    __syncthreads();
+    if (warp != 0) return;
 #pragma unroll
     for (int k = 0; k < EPL; ++k) {
         float s = 0.0f;
-        for (int p = 0; p < nparts; ++p) s += partial[(size_t)p * D + lane + 32 * k];
+#pragma unroll
+        for (int ww = 0; ww < 8; ++ww) s += s_part[ww][lane + 32 * k];
         v[k] = s;
     }
     wht_lanes<EPL>(v, lane);
 #pragma unroll
     for (int k = 0; k < EPL; ++k) out[lane + 32 * k] = (v[k] * inv_sqrt_d) * sign_of(seed, lane + 32 * k);
+}
+
+// ---- long key / value lists: one lane per 32 consecutive elements ---------------------------------------
+// The warp-per-key kernels above spend ~170 instructions per key (cross-lane code extraction, two warp
+// reductions), which is all that matters once a list holds more than a few thousand entries.  Here a key is
+// shared by EPL lanes, each owning 32 consecutive elements = PB packed words + one sign word that it loads
+// itself, and a warp works on 32 / EPL keys at a time.
+//
+// Scores: the query is fixed for the launch, so the dot products are tabulated once per CTA.
+//   t_base[pos][v] = sum_m q~[CH*pos + m] * c[code m of chunk value v]    (chunk = CH codes: one byte of four
+//                    2-bit codes, or six bits of two 3-bit codes)
+//   t_sign[pos][b] = sum_m Rq[8*pos + m] * (bit m of b ? +1 : -1)
+// A key then costs one look-up and one add per chunk and per sign byte.
+template <int PB> struct ChunkGeo;
+template <> struct ChunkGeo<2> { static constexpr int kCodes = 4, kEntries = 256; };
+template <> struct ChunkGeo<3> { static constexpr int kCodes = 2, kEntries = 64; };
+
+template <int PB>
+__device__ __forceinline__ void load_words(const uint8_t* packed, long long key, int pb, int sub, uint32_t (&w)[PB]) {
+    const uint32_t* p = reinterpret_cast<const uint32_t*>(packed + key * pb) + sub * PB;
+#pragma unroll
+    for (int k = 0; k < PB; ++k) w[k] = __ldg(p + k);
+}
+constexpr int kListThreads = 512;
+
+template <int EPL, int PB>
+__global__ void __launch_bounds__(kListThreads, 2)
+scores_table_kernel(const float* __restrict__ q, const float* __restrict__ rq, const uint8_t* __restrict__ packed,
+                    const uint16_t* __restrict__ scales, const uint8_t* __restrict__ signs,
+                    const uint16_t* __restrict__ rnorms, long long n, float* __restrict__ scores, Codebook cb, int pb,
+                    uint64_t seed, float inv_sqrt_d, float sqrt_d) {
+    constexpr int D = 32 * EPL, CH = ChunkGeo<PB>::kCodes, ENT = ChunkGeo<PB>::kEntries, NPOS = D / CH;
+    constexpr int KPW = 32 / EPL;   // keys per warp step
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    float* t_base = reinterpret_cast<float*>(smem_raw);   // [NPOS][ENT]
+    float* t_sign = t_base + NPOS * ENT;                  // [D / 8][256]
+    float* s_q = t_sign + (D / 8) * 256;                  // rotated query
+    float* s_rq = s_q + D;
+    float* s_c = s_rq + D;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x < 16) s_c[threadIdx.x] = cb.c[threadIdx.x];
+    if (warp == 0) {
+        float qr[EPL];
+#pragma unroll
+        for (int k = 0; k < EPL; ++k) qr[k] = q[lane + 32 * k] * sign_of(seed, lane + 32 * k);
+        wht_lanes<EPL>(qr, lane);
+#pragma unroll
+        for (int k = 0; k < EPL; ++k) {
+            s_q[lane + 32 * k] = qr[k] * inv_sqrt_d;
+            s_rq[lane + 32 * k] = rq[lane + 32 * k];
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < NPOS * ENT; idx += kListThreads) {
+        const int pos = idx / ENT, v = idx % ENT;
+        float sum = 0.0f;
+#pragma unroll
+        for (int m = 0; m < CH; ++m) sum = fmaf(s_q[pos * CH + m], s_c[(v >> (PB * m)) & ((1 << PB) - 1)], sum);
+        t_base[idx] = sum;
+    }
+    for (int idx = threadIdx.x; idx < (D / 8) * 256; idx += kListThreads) {
+        const int pos = idx >> 8, b = idx & 255;
+        float sum = 0.0f;
+#pragma unroll
+        for (int m = 0; m < 8; ++m) {
+            const float r = s_rq[pos * 8 + m];
+            sum += ((b >> m) & 1) ? r : -r;
+        }
+        t_sign[idx] = sum;
+    }
+    __syncthreads();
+
+    const int sub = lane % EPL, kin = lane / EPL;
+    const float* tb = t_base + sub * (32 / CH) * ENT;
+    const float* ts = t_sign + sub * 4 * 256;
+    const float cfac = 1.2533141f / sqrt_d;
+    constexpr int kU = 4;
+    const long long wid = (long long)blockIdx.x * (kListThreads / 32) + warp;
+    const long long nw = (long long)gridDim.x * (kListThreads / 32);
+    for (long long i0 = wid * (kU * KPW); i0 < n; i0 += nw * (kU * KPW)) {
+        uint32_t w[kU][PB], sw[kU];
+        float sc[kU], rn[kU];
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+            long long i = i0 + u * KPW + kin;
+            if (i >= n) i = n - 1;
+            load_words<PB>(packed, i, pb, sub, w[u]);
+            sw[u] = __ldg(reinterpret_cast<const uint32_t*>(signs + i * (D / 8)) + sub);
+            sc[u] = f16_bits_to_f32(__ldg(scales + i));
+            rn[u] = f16_bits_to_f32(__ldg(rnorms + i));
+        }
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+            float base = 0.0f, corr = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 32 / CH; ++j) {
+                uint32_t v;
+                if constexpr (PB == 2) v = (w[u][j >> 2] >> (8 * (j & 3))) & 255u;
+                else {
+                    const int pos = 6 * j, k = pos >> 5, sh = pos & 31;
+                    v = (sh + 6 <= 32 ? (w[u][k] >> sh) : __funnelshift_r(w[u][k], w[u][k + 1 < PB ? k + 1 : k], sh)) & 63u;
+                }
+                base += tb[j * ENT + v];
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) corr += ts[j * 256 + ((sw[u] >> (8 * j)) & 255u)];
+            // qjl.rs:263-265: sqrt(pi/2) / sqrt(d) * ||residual||
+            float val = fmaf(rn[u] * cfac, corr, base * sc[u]);
+#pragma unroll
+            for (int o = 1; o < EPL; o <<= 1) val += __shfl_xor_sync(0xffffffffu, val, o);
+            const long long i = i0 + u * KPW + kin;
+            if (sub == 0 && i < n) scores[i] = val;
+        }
+    }
+}
+
+// Weighted sum of values: each lane keeps 32 running sums (its elements) over the keys of its lane group;
+// a pair of codes indexes a table of centroid pairs.  Lane groups are added at the end.
+template <int EPL, int PB>
+__global__ void __launch_bounds__(kListThreads, 2)
+weighted_values_lane_kernel(const float* __restrict__ w, const uint8_t* __restrict__ packed,
+                            const uint16_t* __restrict__ scales, long long n, float* __restrict__ partial, Codebook cb,
+                            int pb) {
+    constexpr int D = 32 * EPL, KPW = 32 / EPL, NP = 1 << (2 * PB);
+    __shared__ float2 s_pair[NP];
+    __shared__ float s_acc[kListThreads / 32][D];
+    for (int i = threadIdx.x; i < NP; i += kListThreads)
+        s_pair[i] = make_float2(cb.c[i & ((1 << PB) - 1)], cb.c[i >> PB]);
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int sub = lane % EPL, kin = lane / EPL;
+    float acc[32];
+#pragma unroll
+    for (int e = 0; e < 32; ++e) acc[e] = 0.0f;
+    constexpr int kU = 4;
+    const long long wid = (long long)blockIdx.x * (kListThreads / 32) + warp;
+    const long long nw = (long long)gridDim.x * (kListThreads / 32);
+    for (long long i0 = wid * (kU * KPW); i0 < n; i0 += nw * (kU * KPW)) {
+        uint32_t cw[kU][PB];
+        float ws[kU];
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+            const long long i = i0 + u * KPW + kin;
+            const long long ic = i < n ? i : n - 1;
+            load_words<PB>(packed, ic, pb, sub, cw[u]);
+            ws[u] = i < n ? __ldg(w + ic) * f16_bits_to_f32(__ldg(scales + ic)) : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+#pragma unroll
+            for (int p = 0; p < 16; ++p) {
+                const int pos = 2 * PB * p, k = pos >> 5, sh = pos & 31;
+                const uint32_t v = (sh + 2 * PB <= 32 ? (cw[u][k] >> sh)
+                                                      : __funnelshift_r(cw[u][k], cw[u][k + 1 < PB ? k + 1 : k], sh)) & (NP - 1);
+                const float2 c = s_pair[v];
+                acc[2 * p] = fmaf(ws[u], c.x, acc[2 * p]);
+                acc[2 * p + 1] = fmaf(ws[u], c.y, acc[2 * p + 1]);
+            }
+        }
+    }
+#pragma unroll
+    for (int o = EPL; o < 32; o <<= 1) {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], o);
+    }
+    if (kin == 0) {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) s_acc[warp][sub * 32 + e] = acc[e];
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < D; e += kListThreads) {
+        float sum = 0.0f;
+        for (int ww = 0; ww < kListThreads / 32; ++ww) sum += s_acc[ww][e];
+        partial[(size_t)blockIdx.x * D + e] = sum;
+    }
 }
 
 // compute_qjl_signs_and_norms of the block-32 TQ cache (src/cache/tq.rs:380-411): residual =
@@ -648,6 +837,26 @@ int tqb_qjl_attention_scores(const tqb_config* cfg, const float* q, const float*
     if (!whole_codebook(polar.bits, polar.dim, cb)) return TQB_ERR_UNSUPPORTED;
     const int pb = (int)tqb_packed_bytes(polar.bits, polar.dim);
     cudaStream_t s = as_stream(stream);
+    if (n >= kListMin && (polar.bits == 2 || polar.bits == 3) && cfg->dim >= 64) {
+        // long lists: tabulated query, one lane per 32 elements
+        const int dim = cfg->dim, ch = polar.bits == 2 ? 4 : 2, ent = polar.bits == 2 ? 256 : 64;
+        const size_t smem = sizeof(float) * ((size_t)(dim / ch) * ent + (size_t)(dim / 8) * 256 + 2 * dim + 16);
+        const long long per_cta = (long long)(kListThreads / 32) * 4 * (32 / (dim / 32));
+        long long g = (n + per_cta - 1) / per_cta;
+        const long long gmax = smem > 100 * 1024 ? 148 : 296;
+        if (g > gmax) g = gmax;
+#define TQB_SCORES_TABLE(PB)                                                                                          \
+    TQB_DISPATCH_EPL(dim, {                                                                                           \
+        cudaError_t e = cudaFuncSetAttribute(scores_table_kernel<EPL, PB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        if (e != cudaSuccess) { set_cuda_error(e); return TQB_ERR_CUDA; }                                             \
+        scores_table_kernel<EPL, PB><<<(int)g, kListThreads, smem, s>>>(q, rq, packed, scales, signs, rnorms, n, scores, cb, pb, \
+                                                                         cfg->rotation_seed, host_inv_sqrt(dim),     \
+                                                                         sqrtf((float)dim));                         \
+    })
+        if (polar.bits == 2) { TQB_SCORES_TABLE(2); } else { TQB_SCORES_TABLE(3); }
+#undef TQB_SCORES_TABLE
+        return check_launch(s);
+    }
     const int grid = grid_warps(n, 8);
     TQB_DISPATCH_EPL(cfg->dim, (scores_kernel<EPL><<<grid, 256, 0, s>>>(
         q, rq, packed, scales, signs, rnorms, n, scores, cb, polar.bits, pb, cfg->rotation_seed,
@@ -680,9 +889,23 @@ int tqb_weighted_values(const tqb_config* cfg, const float* w, const uint8_t* pa
     if (nparts > kWvBlocks) nparts = kWvBlocks;
     if (nparts < 1) nparts = 1;
     float* partial = reinterpret_cast<float*>(scratch);
+    if (n >= kListMin && (polar.bits == 2 || polar.bits == 3) && cfg->dim >= 64) {
+        const long long per_cta = (long long)(kListThreads / 32) * 4 * (32 / (cfg->dim / 32));
+        long long g = (n + per_cta - 1) / per_cta;
+        if (g > kWvBlocks) g = kWvBlocks;
+        nparts = (int)g;
+#define TQB_WV_LANE(PB)                                                                                               \
+    TQB_DISPATCH_EPL(cfg->dim, {                                                                                      \
+        weighted_values_lane_kernel<EPL, PB><<<nparts, kListThreads, 0, s>>>(w, packed, scales, n, partial, cb, pb);  \
+        weighted_values_final_kernel<EPL><<<1, 256, 0, s>>>(partial, nparts, out, cfg->rotation_seed, host_inv_sqrt(cfg->dim)); \
+    })
+        if (polar.bits == 2) { TQB_WV_LANE(2); } else { TQB_WV_LANE(3); }
+#undef TQB_WV_LANE
+        return check_launch(s);
+    }
     TQB_DISPATCH_EPL(cfg->dim, {
         weighted_values_partial_kernel<EPL><<<nparts, 256, 0, s>>>(w, packed, scales, n, partial, cb, polar.bits, pb);
-        weighted_values_final_kernel<EPL><<<1, 32, 0, s>>>(partial, nparts, out, cfg->rotation_seed, host_inv_sqrt(cfg->dim));
+        weighted_values_final_kernel<EPL><<<1, 256, 0, s>>>(partial, nparts, out, cfg->rotation_seed, host_inv_sqrt(cfg->dim));
     });
     return check_launch(s);
 }
