@@ -13,6 +13,7 @@
 #include <float.h>
 
 #include "tqb_common.cuh"
+#include <type_traits>
 
 namespace tqb {
 namespace {
@@ -426,13 +427,24 @@ weighted_values_final_kernel(const float* __restrict__ partial, int nparts, floa
 // itself, and a warp works on 32 / EPL keys at a time.
 //
 // Scores: the query is fixed for the launch, so the dot products are tabulated once per CTA.
-//   t_base[pos][v] = sum_m q~[CH*pos + m] * c[code m of chunk value v]    (chunk = CH codes: one byte of four
-//                    2-bit codes, or six bits of two 3-bit codes)
-//   t_sign[pos][b] = sum_m Rq[8*pos + m] * (bit m of b ? +1 : -1)
-// A key then costs one look-up and one add per chunk and per sign byte.
+//   t_base[j][v][lane] = sum_m q~[32*sub + CH*j + m] * c[code m of chunk value v]   (chunk = two 2-bit codes
+//                        or one 3-bit code; sub = lane % EPL)
+//   t_sign[j][b][lane] = sum_m Rq[32*sub + 4*j + m] * (bit m of b ? +1 : -1)         (b = four sign bits)
+// A key then costs one look-up and one add per chunk and per sign nibble.  The lane index is the innermost
+// dimension: every lane reads its own bank, so a look-up of 32 random entries is one shared-memory
+// wavefront (tables of 64 or 256 entries without the per-lane copies cost ~3.5 wavefronts per look-up and
+// were the bound of the kernel).
+template <int I, int N, typename F>
+__device__ __forceinline__ void static_loop(F&& f) {   // f(integral_constant<int, I>) for I in [I, N): compile-time indices
+    if constexpr (I < N) {
+        f(std::integral_constant<int, I>{});
+        static_loop<I + 1, N>(f);
+    }
+}
+
 template <int PB> struct ChunkGeo;
-template <> struct ChunkGeo<2> { static constexpr int kCodes = 4, kEntries = 256; };
-template <> struct ChunkGeo<3> { static constexpr int kCodes = 2, kEntries = 64; };
+template <> struct ChunkGeo<2> { static constexpr int kCodes = 2, kBits = 4, kEntries = 16; };
+template <> struct ChunkGeo<3> { static constexpr int kCodes = 1, kBits = 3, kEntries = 8; };
 
 template <int PB>
 __device__ __forceinline__ void load_words(const uint8_t* packed, long long key, int pb, int sub, uint32_t (&w)[PB]) {
@@ -442,18 +454,26 @@ __device__ __forceinline__ void load_words(const uint8_t* packed, long long key,
 }
 constexpr int kListThreads = 512;
 
+// byte offset of entry (x >> SH) & (ENT - 1) in a [ENT][32 lanes] float table
+template <int SH, int ENT>
+__device__ __forceinline__ uint32_t entry_offset(uint32_t x) {
+    if constexpr (SH >= 7) return (x >> (SH - 7)) & ((ENT - 1) << 7);
+    else return (x << (7 - SH)) & ((ENT - 1) << 7);
+}
+
 template <int EPL, int PB>
 __global__ void __launch_bounds__(kListThreads, 2)
 scores_table_kernel(const float* __restrict__ q, const float* __restrict__ rq, const uint8_t* __restrict__ packed,
                     const uint16_t* __restrict__ scales, const uint8_t* __restrict__ signs,
                     const uint16_t* __restrict__ rnorms, long long n, float* __restrict__ scores, Codebook cb, int pb,
                     uint64_t seed, float inv_sqrt_d, float sqrt_d) {
-    constexpr int D = 32 * EPL, CH = ChunkGeo<PB>::kCodes, ENT = ChunkGeo<PB>::kEntries, NPOS = D / CH;
+    constexpr int D = 32 * EPL, CH = ChunkGeo<PB>::kCodes, CB = ChunkGeo<PB>::kBits, ENT = ChunkGeo<PB>::kEntries;
+    constexpr int NJ = 32 / CH;
     constexpr int KPW = 32 / EPL;   // keys per warp step
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    float* t_base = reinterpret_cast<float*>(smem_raw);   // [NPOS][ENT]
-    float* t_sign = t_base + NPOS * ENT;                  // [D / 8][256]
-    float* s_q = t_sign + (D / 8) * 256;                  // rotated query
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    float* t_base = reinterpret_cast<float*>(smem_raw);   // [NJ][ENT][32]
+    float* t_sign = t_base + NJ * ENT * 32;               // [8][16][32]
+    float* s_q = t_sign + 8 * 16 * 32;                    // rotated query
     float* s_rq = s_q + D;
     float* s_c = s_rq + D;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -470,28 +490,30 @@ scores_table_kernel(const float* __restrict__ q, const float* __restrict__ rq, c
         }
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < NPOS * ENT; idx += kListThreads) {
-        const int pos = idx / ENT, v = idx % ENT;
+    for (int idx = threadIdx.x; idx < NJ * ENT * 32; idx += kListThreads) {
+        const int j = idx / (ENT * 32), v = (idx >> 5) % ENT;
+        const int e0 = (lane % EPL) * 32 + j * CH;   // idx & 31 == lane: kListThreads is a multiple of 32
         float sum = 0.0f;
 #pragma unroll
-        for (int m = 0; m < CH; ++m) sum = fmaf(s_q[pos * CH + m], s_c[(v >> (PB * m)) & ((1 << PB) - 1)], sum);
+        for (int m = 0; m < CH; ++m) sum = fmaf(s_q[e0 + m], s_c[(v >> (PB * m)) & ((1 << PB) - 1)], sum);
         t_base[idx] = sum;
     }
-    for (int idx = threadIdx.x; idx < (D / 8) * 256; idx += kListThreads) {
-        const int pos = idx >> 8, b = idx & 255;
+    for (int idx = threadIdx.x; idx < 8 * 16 * 32; idx += kListThreads) {
+        const int j = idx / (16 * 32), b = (idx >> 5) & 15;
+        const int e0 = (lane % EPL) * 32 + j * 4;
         float sum = 0.0f;
 #pragma unroll
-        for (int m = 0; m < 8; ++m) {
-            const float r = s_rq[pos * 8 + m];
-            sum += ((b >> m) & 1) ? r : -r;
+        for (int m = 0; m < 4; ++m) {
+            const float x = s_rq[e0 + m];
+            sum += ((b >> m) & 1) ? x : -x;
         }
         t_sign[idx] = sum;
     }
     __syncthreads();
 
     const int sub = lane % EPL, kin = lane / EPL;
-    const float* tb = t_base + sub * (32 / CH) * ENT;
-    const float* ts = t_sign + sub * 4 * 256;
+    const unsigned char* tb = reinterpret_cast<const unsigned char*>(t_base + lane);
+    const unsigned char* ts = reinterpret_cast<const unsigned char*>(t_sign + lane);
     const float cfac = 1.2533141f / sqrt_d;
     constexpr int kU = 4;
     const long long wid = (long long)blockIdx.x * (kListThreads / 32) + warp;
@@ -510,21 +532,20 @@ scores_table_kernel(const float* __restrict__ q, const float* __restrict__ rq, c
         }
 #pragma unroll
         for (int u = 0; u < kU; ++u) {
-            float base = 0.0f, corr = 0.0f;
-#pragma unroll
-            for (int j = 0; j < 32 / CH; ++j) {
-                uint32_t v;
-                if constexpr (PB == 2) v = (w[u][j >> 2] >> (8 * (j & 3))) & 255u;
-                else {
-                    const int pos = 6 * j, k = pos >> 5, sh = pos & 31;
-                    v = (sh + 6 <= 32 ? (w[u][k] >> sh) : __funnelshift_r(w[u][k], w[u][k + 1 < PB ? k + 1 : k], sh)) & 63u;
-                }
-                base += tb[j * ENT + v];
-            }
-#pragma unroll
-            for (int j = 0; j < 4; ++j) corr += ts[j * 256 + ((sw[u] >> (8 * j)) & 255u)];
+            float base[2] = {0.0f, 0.0f}, corr = 0.0f;
+            static_loop<0, NJ>([&](auto j_) {
+                constexpr int j = decltype(j_)::value, pos = CB * j, k = pos >> 5, sh = pos & 31;
+                uint32_t off;
+                if constexpr (sh + CB <= 32) off = entry_offset<sh, ENT>(w[u][k]);
+                else off = entry_offset<0, ENT>(__funnelshift_r(w[u][k], w[u][k + 1 < PB ? k + 1 : k], sh));
+                base[j & 1] += *reinterpret_cast<const float*>(tb + j * (ENT * 128) + off);
+            });
+            static_loop<0, 8>([&](auto j_) {
+                constexpr int j = decltype(j_)::value;
+                corr += *reinterpret_cast<const float*>(ts + j * (16 * 128) + entry_offset<4 * j, 16>(sw[u]));
+            });
             // qjl.rs:263-265: sqrt(pi/2) / sqrt(d) * ||residual||
-            float val = fmaf(rn[u] * cfac, corr, base * sc[u]);
+            float val = fmaf(rn[u] * cfac, corr, (base[0] + base[1]) * sc[u]);
 #pragma unroll
             for (int o = 1; o < EPL; o <<= 1) val += __shfl_xor_sync(0xffffffffu, val, o);
             const long long i = i0 + u * KPW + kin;
@@ -839,8 +860,8 @@ int tqb_qjl_attention_scores(const tqb_config* cfg, const float* q, const float*
     cudaStream_t s = as_stream(stream);
     if (n >= kListMin && (polar.bits == 2 || polar.bits == 3) && cfg->dim >= 64) {
         // long lists: tabulated query, one lane per 32 elements
-        const int dim = cfg->dim, ch = polar.bits == 2 ? 4 : 2, ent = polar.bits == 2 ? 256 : 64;
-        const size_t smem = sizeof(float) * ((size_t)(dim / ch) * ent + (size_t)(dim / 8) * 256 + 2 * dim + 16);
+        const int dim = cfg->dim;
+        const size_t smem = sizeof(float) * (8192 + 4096 + 2 * dim + 16);   // [chunks][entries][32] + [8][16][32]
         const long long per_cta = (long long)(kListThreads / 32) * 4 * (32 / (dim / 32));
         long long g = (n + per_cta - 1) / per_cta;
         const long long gmax = smem > 100 * 1024 ? 148 : 296;
