@@ -13,6 +13,7 @@
 #include <float.h>
 
 #include "tqb_common.cuh"
+#include "tqb_pqo_quant.cuh"
 #include <type_traits>
 
 namespace tqb {
@@ -217,6 +218,94 @@ __global__ void whole_quantize_kernel(WholeArgs a, Codebook cb) {
         for (int i = lane; i < nwords; i += 32) gout[i] = sst[i];
         if (lane < nv) a.scales[v0 + lane] = f32_to_f16_bits(norm < kMinNorm ? 0.0f : norm);  // select_scale
         __syncwarp();
+    }
+}
+
+// quantize_vec for batches (no QJL outputs): EPL lanes share a vector, each owning 32 consecutive elements
+// that it loads itself, so the first five butterfly stages run in registers and only log2(EPL) stages
+// cross lanes; a warp works on 32 / EPL vectors at a time.  Same arithmetic, in the same order, as
+// whole_quantize_kernel: the sum of squares runs left to right (the lanes of a vector take turns), the
+// sign flip is folded into the exact multiplication by +-1/norm, and the boundary count comes from a cell
+// table: cell = round(255 * sat(t + 0.5)); each cell, widened by kWholeSlop, holds at most one boundary
+// (the host checks the table's gaps), so code = boundaries under the cell + (t > the cell's boundary).
+constexpr float kWholeSlop = 2e-4f;
+constexpr float kWholeMinGap = 1.0f / 255.0f + 4.0f * kWholeSlop;   // smallest boundary gap the cell table can take
+
+template <int EPL, int BITS>
+__global__ void __launch_bounds__(256)
+whole_quantize_lane_kernel(WholeArgs a, Codebook cb) {
+    constexpr int D = 32 * EPL, KPW = 32 / EPL, NB = (1 << BITS) - 1;
+    __shared__ float2 s_cell[256];
+    for (int c = threadIdx.x; c < 256; c += blockDim.x) {
+        const float lo = c == 0 ? -FLT_MAX : ((float)c - 0.5f) / 255.0f - 0.5f - kWholeSlop;
+        const float hi = c == 255 ? FLT_MAX : ((float)c + 0.5f) / 255.0f - 0.5f + kWholeSlop;
+        float bnd = FLT_MAX;
+        unsigned below = 0;
+        for (int k = 0; k < NB; ++k) {
+            const float b = cb.b[k];
+            if (b < lo) ++below;
+            else if (b <= hi) bnd = b;
+        }
+        s_cell[c] = make_float2(bnd, __uint_as_float(below));
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    const int sub = lane % EPL, kin = lane / EPL;
+    const bool seed_odd = (a.seed & 1ULL) != 0;
+    const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const long long nw = ((long long)gridDim.x * blockDim.x) >> 5;
+    for (long long v0 = wid * KPW; v0 < a.n; v0 += nw * KPW) {
+        const long long vi = v0 + kin;
+        const bool live = vi < a.n;
+        const long long vc = live ? vi : a.n - 1;
+        float v[32];
+        load32<float>(a.x + vc * D + sub * 32, v);
+        // l2_norm (quantize.rs:51-53): s = s + x*x, left to right over the whole vector
+        float s = 0.0f;
+#pragma unroll
+        for (int p = 0; p < EPL; ++p) {
+            if (sub == p) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) s = s + v[j] * v[j];
+            }
+            s = __shfl_sync(0xffffffffu, s, (lane & ~(EPL - 1)) | p);
+        }
+        const float norm = __fsqrt_rn(s);
+        const bool tiny = norm < kMinNorm;
+        // normalize_inplace (quantize.rs:60-72) and the sign flip (rotation.rs:139-142): (x * inv) * (+-1)
+        const float inv = tiny ? 0.0f : __fdiv_rn(1.0f, norm);
+        const float inv_even = seed_odd ? -inv : inv, inv_odd = -inv_even;   // element 32*sub + j has the parity of seed + j
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = v[j] * ((j & 1) ? inv_odd : inv_even);
+        butterfly32_regs(v);
+#pragma unroll
+        for (int hs = 1; hs < EPL; hs <<= 1) {
+            const bool upper = (sub & hs) != 0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const float other = __shfl_xor_sync(0xffffffffu, v[j], hs);
+                v[j] = upper ? (other - v[j]) : (v[j] + other);
+            }
+        }
+        uint32_t w[BITS];
+#pragma unroll
+        for (int k = 0; k < BITS; ++k) w[k] = 0u;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const float t = v[j] * a.inv_sqrt_d;
+            const float y = fmaf(__saturatef(t + 0.5f), 255.0f, 12582912.0f);
+            const float2 e = s_cell[__float_as_uint(y) & 255u];
+            const uint32_t c = __float_as_uint(e.y) + (t > e.x ? 1u : 0u);
+            const int bit = BITS * j;
+            w[bit >> 5] += c << (bit & 31);
+            if ((bit & 31) + BITS > 32) w[(bit >> 5) + 1] += c >> (32 - (bit & 31));
+        }
+        if (live) {
+            uint32_t* out = reinterpret_cast<uint32_t*>(a.packed + vi * a.pb) + sub * BITS;
+#pragma unroll
+            for (int k = 0; k < BITS; ++k) out[k] = w[k];
+            if (sub == 0) a.scales[vi] = f32_to_f16_bits(tiny ? 0.0f : norm);   // select_scale
+        }
     }
 }
 
@@ -720,8 +809,41 @@ int launch_quant(const WholeArgs& a, const Codebook& cb, cudaStream_t s) {
     return check_launch(s);
 }
 
+template <int EPL>
+int launch_quant_lane(const WholeArgs& a, const Codebook& cb, cudaStream_t s) {
+    constexpr int kpw = 32 / EPL;
+    long long grid = (a.n + 8 * kpw - 1) / (8 * kpw);
+    if (grid > 148 * 8) grid = 148 * 8;
+    switch (a.bits) {
+        case 2: whole_quantize_lane_kernel<EPL, 2><<<(int)grid, 256, 0, s>>>(a, cb); break;
+        case 3: whole_quantize_lane_kernel<EPL, 3><<<(int)grid, 256, 0, s>>>(a, cb); break;
+        case 4: whole_quantize_lane_kernel<EPL, 4><<<(int)grid, 256, 0, s>>>(a, cb); break;
+        default: return TQB_ERR_UNSUPPORTED_BITS;
+    }
+    return check_launch(s);
+}
+
+// The cell table of whole_quantize_lane_kernel needs every boundary inside (-0.5, 0.5) and gaps wider than a cell.
+bool cell_table_fits(const Codebook& cb, int bits) {
+    const int nb = (1 << bits) - 1;
+    for (int k = 0; k < nb; ++k) {
+        if (!(fabsf(cb.b[k]) < 0.49f)) return false;
+        if (k > 0 && !(cb.b[k] - cb.b[k - 1] > kWholeMinGap)) return false;
+    }
+    return true;
+}
+
 template <bool QJL>
 int dispatch_quant(const WholeArgs& a, const Codebook& cb, cudaStream_t s) {
+    if (!QJL && a.bits >= 2 && a.bits <= 4 && ((uintptr_t)a.x % 16) == 0 && cell_table_fits(cb, a.bits)) {
+        switch (a.dim) {
+            case 32: return launch_quant_lane<1>(a, cb, s);
+            case 64: return launch_quant_lane<2>(a, cb, s);
+            case 128: return launch_quant_lane<4>(a, cb, s);
+            case 256: return launch_quant_lane<8>(a, cb, s);
+            default: return TQB_ERR_UNSUPPORTED;
+        }
+    }
     switch (a.dim) {
         case 32: return launch_quant<1, QJL>(a, cb, s);
         case 64: return launch_quant<2, QJL>(a, cb, s);
