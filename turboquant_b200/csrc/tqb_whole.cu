@@ -229,16 +229,27 @@ __global__ void whole_quantize_kernel(WholeArgs a, Codebook cb) {
 // table: cell = round(255 * sat(t + 0.5)); each cell, widened by kWholeSlop, holds at most one boundary
 // (the host checks the table's gaps), so code = boundaries under the cell + (t > the cell's boundary).
 constexpr float kWholeSlop = 2e-4f;
-constexpr float kWholeMinGap = 1.0f / 255.0f + 4.0f * kWholeSlop;   // smallest boundary gap the cell table can take
+constexpr int kWholeCells = 128;
+constexpr float kWholeMinGap = 1.0f / (kWholeCells - 1) + 4.0f * kWholeSlop;   // smallest boundary gap the cell table can take
+constexpr int kWholeWarps = 8;
+constexpr int kWholeRowB = 32 * 4 + 16;   // a lane's 32 staged floats + 16 bytes: rows 9 x 16 bytes apart read without bank conflicts
+constexpr size_t kWholeSmem = (size_t)kWholeCells * 32 * sizeof(float2) + (size_t)kWholeWarps * 32 * kWholeRowB;
 
+// Input staging: a warp's 32 / EPL vectors are 4 KB of consecutive floats.  They are copied to shared memory
+// in 16-byte pieces, 512 consecutive bytes per warp instruction, and each lane then reads its own 128 bytes
+// (one lane per 128-byte line straight from global memory costs 32 L1 wavefronts per load instruction).
+// The cell table is stored [cell][lane], so the 32 look-ups of a warp instruction touch 32 different bank pairs.
 template <int EPL, int BITS>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(kWholeWarps * 32, 3)
 whole_quantize_lane_kernel(WholeArgs a, Codebook cb) {
     constexpr int D = 32 * EPL, KPW = 32 / EPL, NB = (1 << BITS) - 1;
-    __shared__ float2 s_cell[256];
-    for (int c = threadIdx.x; c < 256; c += blockDim.x) {
-        const float lo = c == 0 ? -FLT_MAX : ((float)c - 0.5f) / 255.0f - 0.5f - kWholeSlop;
-        const float hi = c == 255 ? FLT_MAX : ((float)c + 0.5f) / 255.0f - 0.5f + kWholeSlop;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    float2* s_cell = reinterpret_cast<float2*>(smem_raw);   // [kWholeCells][32]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    unsigned char* stage = smem_raw + (size_t)kWholeCells * 32 * sizeof(float2) + (size_t)warp * 32 * kWholeRowB;
+    for (int c = warp; c < kWholeCells; c += kWholeWarps) {
+        const float lo = c == 0 ? -FLT_MAX : ((float)c - 0.5f) / (kWholeCells - 1) - 0.5f - kWholeSlop;
+        const float hi = c == kWholeCells - 1 ? FLT_MAX : ((float)c + 0.5f) / (kWholeCells - 1) - 0.5f + kWholeSlop;
         float bnd = FLT_MAX;
         unsigned below = 0;
         for (int k = 0; k < NB; ++k) {
@@ -246,20 +257,36 @@ whole_quantize_lane_kernel(WholeArgs a, Codebook cb) {
             if (b < lo) ++below;
             else if (b <= hi) bnd = b;
         }
-        s_cell[c] = make_float2(bnd, __uint_as_float(below));
+        s_cell[c * 32 + lane] = make_float2(bnd, __uint_as_float(below));
     }
     __syncthreads();
-    const int lane = threadIdx.x & 31;
+    const float2* cell_l = s_cell + lane;
     const int sub = lane % EPL, kin = lane / EPL;
     const bool seed_odd = (a.seed & 1ULL) != 0;
-    const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const long long nw = ((long long)gridDim.x * blockDim.x) >> 5;
+    const long long wid = (long long)blockIdx.x * kWholeWarps + warp;
+    const long long nw = (long long)gridDim.x * kWholeWarps;
+    const uint32_t stage_s = (uint32_t)__cvta_generic_to_shared(stage);
     for (long long v0 = wid * KPW; v0 < a.n; v0 += nw * KPW) {
         const long long vi = v0 + kin;
         const bool live = vi < a.n;
-        const long long vc = live ? vi : a.n - 1;
+        // piece q = 32 * i + lane of the warp's 256 pieces belongs to lane q / 8 (vector q / (8 * EPL))
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int q = 32 * i + lane;
+            long long vec = v0 + q / (8 * EPL);
+            if (vec >= a.n) vec = a.n - 1;
+            const float* src = a.x + vec * D + (q % (8 * EPL)) * 4;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(stage_s + (q >> 3) * kWholeRowB + (q & 7) * 16), "l"(src) : "memory");
+        }
+        asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
+        __syncwarp();
         float v[32];
-        load32<float>(a.x + vc * D + sub * 32, v);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const float4 f = *reinterpret_cast<const float4*>(stage + lane * kWholeRowB + k * 16);
+            v[4 * k] = f.x; v[4 * k + 1] = f.y; v[4 * k + 2] = f.z; v[4 * k + 3] = f.w;
+        }
+        __syncwarp();   // the rows are free for the next pass
         // l2_norm (quantize.rs:51-53): s = s + x*x, left to right over the whole vector
         float s = 0.0f;
 #pragma unroll
@@ -280,11 +307,11 @@ whole_quantize_lane_kernel(WholeArgs a, Codebook cb) {
         butterfly32_regs(v);
 #pragma unroll
         for (int hs = 1; hs < EPL; hs <<= 1) {
-            const bool upper = (sub & hs) != 0;
+            const uint32_t flip = (sub & hs) ? 0x80000000u : 0u;   // upper half: other - v, lower half: v + other
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
                 const float other = __shfl_xor_sync(0xffffffffu, v[j], hs);
-                v[j] = upper ? (other - v[j]) : (v[j] + other);
+                v[j] = other + __uint_as_float(__float_as_uint(v[j]) ^ flip);
             }
         }
         uint32_t w[BITS];
@@ -293,8 +320,8 @@ whole_quantize_lane_kernel(WholeArgs a, Codebook cb) {
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
             const float t = v[j] * a.inv_sqrt_d;
-            const float y = fmaf(__saturatef(t + 0.5f), 255.0f, 12582912.0f);
-            const float2 e = s_cell[__float_as_uint(y) & 255u];
+            const float y = fmaf(__saturatef(t + 0.5f), (float)(kWholeCells - 1), 12582912.0f);
+            const float2 e = cell_l[(__float_as_uint(y) & (kWholeCells - 1)) * 32];
             const uint32_t c = __float_as_uint(e.y) + (t > e.x ? 1u : 0u);
             const int bit = BITS * j;
             w[bit >> 5] += c << (bit & 31);
@@ -809,18 +836,26 @@ int launch_quant(const WholeArgs& a, const Codebook& cb, cudaStream_t s) {
     return check_launch(s);
 }
 
+template <int EPL, int BITS>
+int launch_quant_lane_bits(const WholeArgs& a, const Codebook& cb, cudaStream_t s) {
+    constexpr int kpw = 32 / EPL;
+    long long grid = (a.n + kWholeWarps * kpw - 1) / (kWholeWarps * kpw);
+    if (grid > 148 * 3) grid = 148 * 3;
+    cudaError_t e = cudaFuncSetAttribute(whole_quantize_lane_kernel<EPL, BITS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)kWholeSmem);
+    if (e != cudaSuccess) { set_cuda_error(e); return TQB_ERR_CUDA; }
+    whole_quantize_lane_kernel<EPL, BITS><<<(int)grid, kWholeWarps * 32, kWholeSmem, s>>>(a, cb);
+    return check_launch(s);
+}
+
 template <int EPL>
 int launch_quant_lane(const WholeArgs& a, const Codebook& cb, cudaStream_t s) {
-    constexpr int kpw = 32 / EPL;
-    long long grid = (a.n + 8 * kpw - 1) / (8 * kpw);
-    if (grid > 148 * 8) grid = 148 * 8;
     switch (a.bits) {
-        case 2: whole_quantize_lane_kernel<EPL, 2><<<(int)grid, 256, 0, s>>>(a, cb); break;
-        case 3: whole_quantize_lane_kernel<EPL, 3><<<(int)grid, 256, 0, s>>>(a, cb); break;
-        case 4: whole_quantize_lane_kernel<EPL, 4><<<(int)grid, 256, 0, s>>>(a, cb); break;
+        case 2: return launch_quant_lane_bits<EPL, 2>(a, cb, s);
+        case 3: return launch_quant_lane_bits<EPL, 3>(a, cb, s);
+        case 4: return launch_quant_lane_bits<EPL, 4>(a, cb, s);
         default: return TQB_ERR_UNSUPPORTED_BITS;
     }
-    return check_launch(s);
 }
 
 // The cell table of whole_quantize_lane_kernel needs every boundary inside (-0.5, 0.5) and gaps wider than a cell.
