@@ -365,6 +365,77 @@ __global__ void whole_dequantize_kernel(const uint8_t* __restrict__ packed, cons
     }
 }
 
+// The same for batches with the lane layout of whole_quantize_lane_kernel: a lane decodes its 32 codes
+// through a [code][lane] centroid table (one bank per lane), runs five butterfly stages in registers and
+// log2(EPL) across lanes, and the warp's 32 / EPL output vectors (4 KB of consecutive floats) leave
+// through shared memory as 512 consecutive bytes per store instruction.  Values are bit-identical to
+// whole_dequantize_kernel (same operations in the same order; the sign flip is an exact negation).
+template <int EPL, int BITS>
+__global__ void __launch_bounds__(kWholeWarps * 32, 3)
+whole_dequantize_lane_kernel(const uint8_t* __restrict__ packed, const uint16_t* __restrict__ scales, long long n,
+                             float* __restrict__ out, Codebook cb, int pb, uint64_t seed, float inv_sqrt_d,
+                             int rotated_only) {
+    constexpr int D = 32 * EPL, KPW = 32 / EPL;
+    __shared__ float s_tab[(1 << BITS) * 32];
+    __shared__ __align__(16) unsigned char s_stage[kWholeWarps * 32 * kWholeRowB];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int i = threadIdx.x; i < (1 << BITS) * 32; i += kWholeWarps * 32) s_tab[i] = cb.c[i >> 5];
+    __syncthreads();
+    const float* tab = s_tab + lane;
+    unsigned char* stage = s_stage + warp * 32 * kWholeRowB;
+    const int sub = lane % EPL, kin = lane / EPL;
+    const bool seed_odd = (seed & 1ULL) != 0;
+    const float m_even = seed_odd ? -inv_sqrt_d : inv_sqrt_d, m_odd = -m_even;   // (v * inv_sqrt_d) * (+-1)
+    const long long wid = (long long)blockIdx.x * kWholeWarps + warp;
+    const long long nw = (long long)gridDim.x * kWholeWarps;
+    for (long long v0 = wid * KPW; v0 < n; v0 += nw * KPW) {
+        const long long vi = v0 + kin;
+        const long long vc = vi < n ? vi : n - 1;
+        uint32_t w[BITS];
+        {
+            const uint32_t* p = reinterpret_cast<const uint32_t*>(packed + vc * pb) + sub * BITS;
+#pragma unroll
+            for (int k = 0; k < BITS; ++k) w[k] = __ldg(p + k);
+        }
+        const float sc = f16_bits_to_f32(__ldg(scales + vc));
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const int bit = BITS * j, k = bit >> 5, sh = bit & 31;
+            const uint32_t code = (sh + BITS <= 32 ? (w[k] >> sh) : __funnelshift_r(w[k], w[k + 1 < BITS ? k + 1 : k], sh)) &
+                                  ((1u << BITS) - 1u);
+            v[j] = tab[code * 32];
+        }
+        if (!rotated_only) {
+            butterfly32_regs(v);
+#pragma unroll
+            for (int hs = 1; hs < EPL; hs <<= 1) {
+                const uint32_t flip = (sub & hs) ? 0x80000000u : 0u;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const float other = __shfl_xor_sync(0xffffffffu, v[j], hs);
+                    v[j] = other + __uint_as_float(__float_as_uint(v[j]) ^ flip);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = v[j] * ((j & 1) ? m_odd : m_even);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            *reinterpret_cast<float4*>(stage + lane * kWholeRowB + k * 16) =
+                make_float4(v[4 * k] * sc, v[4 * k + 1] * sc, v[4 * k + 2] * sc, v[4 * k + 3] * sc);
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int q = 32 * i + lane;
+            const long long vec = v0 + q / (8 * EPL);
+            const float4 f = *reinterpret_cast<const float4*>(stage + (q >> 3) * kWholeRowB + (q & 7) * 16);
+            if (vec < n) *reinterpret_cast<float4*>(out + vec * D + (q % (8 * EPL)) * 4) = f;
+        }
+        __syncwarp();
+    }
+}
+
 // precompute_query_projections (src/qjl.rs:488-492); one warp per query.
 template <int EPL>
 __global__ void projections_kernel(const float* __restrict__ q, long long nq, const uint32_t* __restrict__ rbits,
@@ -963,6 +1034,17 @@ static int dequant_common(const tqb_config* cfg, const uint8_t* packed, const ui
     if (!whole_codebook(cfg->bits, cfg->dim, cb)) return TQB_ERR_UNSUPPORTED;
     const int pb = (int)tqb_packed_bytes(cfg->bits, cfg->dim);
     cudaStream_t s = as_stream(stream);
+    if (((uintptr_t)out % 16) == 0 && cfg->bits >= 2 && cfg->bits <= 4) {
+        const long long per_cta = (long long)kWholeWarps * (32 / (cfg->dim / 32));
+        long long g = (n + per_cta - 1) / per_cta;
+        if (g > 148 * 3) g = 148 * 3;
+#define TQB_DEQ_LANE(BITS)                                                                                            \
+    TQB_DISPATCH_EPL(cfg->dim, (whole_dequantize_lane_kernel<EPL, BITS><<<(int)g, kWholeWarps * 32, 0, s>>>(            \
+        packed, scales, n, out, cb, pb, cfg->rotation_seed, host_inv_sqrt(cfg->dim), rotated_only)))
+        if (cfg->bits == 2) { TQB_DEQ_LANE(2); } else if (cfg->bits == 3) { TQB_DEQ_LANE(3); } else { TQB_DEQ_LANE(4); }
+#undef TQB_DEQ_LANE
+        return check_launch(s);
+    }
     const int grid = grid_warps(n, 8);
     TQB_DISPATCH_EPL(cfg->dim, (whole_dequantize_kernel<EPL><<<grid, 256, 0, s>>>(
         packed, scales, n, out, cb, cfg->bits, pb, cfg->rotation_seed, host_inv_sqrt(cfg->dim), rotated_only)));
