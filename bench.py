@@ -350,6 +350,56 @@ def run_reference(args):
     }))
 
 
+def run_whole_vector(args):
+    """Secondary report (not the contract line): the whole-vector (core crate) kernels on synthetic N(0,1) data,
+    CUDA-event times against the measured HBM peak.  Also the small case for profiler captures of these kernels."""
+    import numpy as np
+    import torch
+    import turboquant_b200 as tq
+    peak = peaks()[0]
+    dev = "cuda"
+    n, m, keys, dim = 1 << 19, 1 << 16, 1 << 21, 128
+
+    def timed(fn):
+        ts = []
+        for _ in range(args.warmup + args.steps):
+            e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
+            e0.record()
+            fn()
+            e1.record()
+            e1.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return float(np.median(ts[args.warmup:]))
+
+    x = torch.randn((n, dim), device=dev)
+    rows = []
+
+    def row(name, units, bytes_per_unit, ms):
+        gbs = units * bytes_per_unit / ms / 1e6
+        rows.append({"kernel": name, "units": units, "bytes_per_unit": bytes_per_unit, "ms": round(ms, 4),
+                     "GB/s": round(gbs, 1), "frac_of_measured_peak": round(gbs / peak, 3)})
+
+    for bits in (3, 4):
+        cfg = tq.TurboQuantConfig(bits, dim).with_seed(42)
+        pb = tq.packed_bytes(bits, dim)
+        row(f"quantize_batch TQ{bits}", n, 4 * dim + pb + 2, timed(lambda: tq.quantize_batch(cfg, x)))
+        p, s = tq.quantize_batch(cfg, x)
+        row(f"dequantize_batch TQ{bits}", n, 4 * dim + pb + 2, timed(lambda: tq.dequantize_batch(cfg, p, s)))
+        qpb = tq.packed_bytes(bits - 1, dim)
+        row(f"qjl_quantize_batch TQ{bits}", m, 4 * dim + qpb + 2 + dim // 8 + 2,
+            timed(lambda: tq.qjl_quantize_batch(cfg, x[:m], 42)))
+        pk, sc, sg, rn = [t.repeat((keys // m,) + (1,) * (t.dim() - 1)) for t in tq.qjl_quantize_batch(cfg, x[:m], 42)]
+        q = torch.randn(dim, device=dev) / dim ** 0.5
+        rq = tq.query_projections(q, dim, 42).reshape(-1)
+        row(f"qjl_attention_scores TQ{bits}", keys, qpb + 2 + dim // 8 + 2,
+            timed(lambda: tq.qjl_attention_scores(cfg, q, rq, pk, sc, sg, rn)))
+        w = torch.rand(keys, device=dev)
+        row(f"weighted_values TQ{bits}", keys, qpb + 2 + 4, timed(lambda: tq.weighted_values(cfg, w, pk, sc)))
+    print(json.dumps({"report": "whole-vector kernels", "dim": dim, "peak_GB/s": peak, "peak_source": peaks()[1],
+                      "timing": "CUDA events, median of %d after %d warm-up calls (python call included)" % (args.steps, args.warmup),
+                      "rows": rows}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -362,7 +412,13 @@ def main():
                          "above the L2 size, 0.4 GB on the device); its numbers are not bench values")
     ap.add_argument("--profile-bits", type=int, default=4, choices=[3, 4],
                     help="with --profile-case: code width of the small case (3 = PQO3, 4 = PQO4)")
+    ap.add_argument("--whole-vector", action="store_true",
+                    help="secondary report: the whole-vector (core crate) kernels, 2^19 vectors / 2^21 keys of d = 128 "
+                         "(0.3 GB on the device); also the small case for profiler captures of those kernels")
     args = ap.parse_args()
+    if args.whole_vector:
+        run_whole_vector(args)
+        return
     if args.profile_case:
         CFG.update(layers=2, batch=16, bits=args.profile_bits)
         args.no_cpu = True

@@ -230,7 +230,8 @@ __global__ void whole_quantize_kernel(WholeArgs a, Codebook cb) {
 // (the host checks the table's gaps), so code = boundaries under the cell + (t > the cell's boundary).
 constexpr float kWholeSlop = 2e-4f;
 constexpr int kWholeCells = 128;
-constexpr float kWholeMinGap = 1.0f / (kWholeCells - 1) + 4.0f * kWholeSlop;   // smallest boundary gap the cell table can take
+constexpr float kWholeFine = 256.0f * kWholeCells - 1.0f;   // sat(t + 0.5) in [0, 1] -> k in [0, 256 * cells - 1]
+constexpr float kWholeMinGap = 256.0f / kWholeFine + 4.0f * kWholeSlop;   // smallest boundary gap the cell table can take
 constexpr int kWholeWarps = 8;
 constexpr int kWholeRowB = 32 * 4 + 16;   // a lane's 32 staged floats + 16 bytes: rows 9 x 16 bytes apart read without bank conflicts
 constexpr size_t kWholeSmem = (size_t)kWholeCells * 32 * sizeof(float2) + (size_t)kWholeWarps * 32 * kWholeRowB;
@@ -247,9 +248,10 @@ whole_quantize_lane_kernel(WholeArgs a, Codebook cb) {
     float2* s_cell = reinterpret_cast<float2*>(smem_raw);   // [kWholeCells][32]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     unsigned char* stage = smem_raw + (size_t)kWholeCells * 32 * sizeof(float2) + (size_t)warp * 32 * kWholeRowB;
+    // cell of t: k = round(sat(t + 0.5) * kWholeFine) (an integer in the mantissa after the 1.5 * 2^23 add), cell = k >> 8
     for (int c = warp; c < kWholeCells; c += kWholeWarps) {
-        const float lo = c == 0 ? -FLT_MAX : ((float)c - 0.5f) / (kWholeCells - 1) - 0.5f - kWholeSlop;
-        const float hi = c == kWholeCells - 1 ? FLT_MAX : ((float)c + 0.5f) / (kWholeCells - 1) - 0.5f + kWholeSlop;
+        const float lo = c == 0 ? -FLT_MAX : (256.0f * c - 0.5f) / kWholeFine - 0.5f - kWholeSlop;
+        const float hi = c == kWholeCells - 1 ? FLT_MAX : (256.0f * c + 255.5f) / kWholeFine - 0.5f + kWholeSlop;
         float bnd = FLT_MAX;
         unsigned below = 0;
         for (int k = 0; k < NB; ++k) {
@@ -260,7 +262,6 @@ whole_quantize_lane_kernel(WholeArgs a, Codebook cb) {
         s_cell[c * 32 + lane] = make_float2(bnd, __uint_as_float(below));
     }
     __syncthreads();
-    const float2* cell_l = s_cell + lane;
     const int sub = lane % EPL, kin = lane / EPL;
     const bool seed_odd = (a.seed & 1ULL) != 0;
     const long long wid = (long long)blockIdx.x * kWholeWarps + warp;
@@ -270,13 +271,21 @@ whole_quantize_lane_kernel(WholeArgs a, Codebook cb) {
         const long long vi = v0 + kin;
         const bool live = vi < a.n;
         // piece q = 32 * i + lane of the warp's 256 pieces belongs to lane q / 8 (vector q / (8 * EPL))
+        const uint32_t dst0 = stage_s + (lane >> 3) * kWholeRowB + (lane & 7) * 16;   // + i * 4 rows
+        if (v0 + KPW <= a.n) {
+            const float* src0 = a.x + v0 * D + lane * 4;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int q = 32 * i + lane;
-            long long vec = v0 + q / (8 * EPL);
-            if (vec >= a.n) vec = a.n - 1;
-            const float* src = a.x + vec * D + (q % (8 * EPL)) * 4;
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(stage_s + (q >> 3) * kWholeRowB + (q & 7) * 16), "l"(src) : "memory");
+            for (int i = 0; i < 8; ++i)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst0 + i * 4 * kWholeRowB), "l"(src0 + i * 128) : "memory");
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int q = 32 * i + lane;
+                long long vec = v0 + q / (8 * EPL);
+                if (vec >= a.n) vec = a.n - 1;
+                const float* src = a.x + vec * D + (q % (8 * EPL)) * 4;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst0 + i * 4 * kWholeRowB), "l"(src) : "memory");
+            }
         }
         asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
         __syncwarp();
@@ -320,8 +329,9 @@ whole_quantize_lane_kernel(WholeArgs a, Codebook cb) {
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
             const float t = v[j] * a.inv_sqrt_d;
-            const float y = fmaf(__saturatef(t + 0.5f), (float)(kWholeCells - 1), 12582912.0f);
-            const float2 e = cell_l[(__float_as_uint(y) & (kWholeCells - 1)) * 32];
+            const float y = fmaf(__saturatef(t + 0.5f), kWholeFine, 12582912.0f);
+            // byte offset of [cell][lane]: cell * 256 + lane * 8
+            const float2 e = *reinterpret_cast<const float2*>(smem_raw + ((__float_as_uint(y) & ((kWholeCells - 1) << 8)) | (lane << 3)));
             const uint32_t c = __float_as_uint(e.y) + (t > e.x ? 1u : 0u);
             const int bit = BITS * j;
             w[bit >> 5] += c << (bit & 31);
