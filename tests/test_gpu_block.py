@@ -38,7 +38,7 @@ def test_golden_fixture(bits, nm, ob, tag):
     assert np.array_equal(deq, CASES[f"block_deq_{tag}"])
 
 
-@pytest.mark.parametrize("bits,nm,ob,tag", MODES)
+@pytest.mark.parametrize("bits,nm,ob,tag", MODES + [(4, 0, 0, "pq4")])
 @pytest.mark.parametrize("head_dim,n", [(128, 4099), (64, 17), (256, 5), (32, 3)])
 def test_random_vs_oracle_bit_exact(bits, nm, ob, tag, head_dim, n):
     rng = np.random.default_rng(n)
@@ -79,7 +79,7 @@ def test_append_row_mapping():
     assert np.array_equal(u16(sc)[:, off:off + new].reshape(-1, 4), os_)
 
 
-@pytest.mark.parametrize("bits,nm,ob", [(4, 0, -1), (3, 0, -1), (3, 1, -1), (4, 0, 2)])
+@pytest.mark.parametrize("bits,nm,ob", [(4, 0, -1), (3, 0, -1), (3, 1, -1), (4, 0, 2), (3, 0, 0), (4, 0, 0)])
 def test_pair_launch_equals_two_single_launches(bits, nm, ob):
     # K and V of one append in one launch, with the append row mapping
     heads, new, cap, off = 4, 3, 8, 2

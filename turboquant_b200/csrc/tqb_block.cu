@@ -255,14 +255,16 @@ block_quantize_kernel(QuantArgs a, Codebook normal, Codebook outlier) {
 //   an approximate u (one FMA from W_i) by the 1.5*2^23 magic add.  Only when u lies within 2e-5 of
 //   a half-integer could the approximation disagree with the table comparison; such lanes redo
 //   their block with exact division and the f32 boundary table.
-template <typename T, int BITS>
+// NORMAL: every block is on the narrower "normal" codebook (cb, cb.n levels) stored at BITS width, scale sign +
+// (the TQ cache layout, outlier_blocks = 0): the cell table serves any sorted boundary set.
+template <typename T, int BITS, bool NORMAL>
 __global__ void __launch_bounds__(kThreads)
 block_quantize_pqo_kernel(QuantArgs a, Codebook cb) {
     if (blockIdx.y != 0) { a.x = a.x2; a.indices = a.indices2; a.scales = a.scales2; }
-    __shared__ float2 s_lut[BITS == 3 ? 256 : 1];
+    __shared__ float2 s_lut[(BITS == 3 || NORMAL) ? 256 : 1];
     const float2* lut = nullptr;
-    if (BITS == 3) {
-        build_cell_table(cb, 7, s_lut, threadIdx.x, kThreads);
+    if (BITS == 3 || NORMAL) {
+        build_cell_table(cb, cb.n - 1, s_lut, threadIdx.x, kThreads);
         __syncthreads();
         lut = s_lut;
     }
@@ -273,7 +275,7 @@ block_quantize_pqo_kernel(QuantArgs a, Codebook cb) {
     for (unsigned blk = blockIdx.x * kThreads + threadIdx.x; blk < total; blk += gridDim.x * kThreads) {
         const unsigned row = blk / nblk, bv = blk - row * nblk;
         uint32_t w[4];
-        const float scale = pqo_quantize_block<T, BITS>(reinterpret_cast<const T*>(a.x) + (long long)row * xrow + bv * kBlock, cb,
+        const float scale = pqo_quantize_block<T, BITS, NORMAL>(reinterpret_cast<const T*>(a.x) + (long long)row * xrow + bv * kBlock, cb,
                                                         a.outer_centroid, w, lut);
         long long orow = row;
         if (a.map.rows_per_group != 0) {   // 32-bit division: row and rows_per_group are below 2^31 here
@@ -288,7 +290,7 @@ block_quantize_pqo_kernel(QuantArgs a, Codebook cb) {
             uint32_t* wp = reinterpret_cast<uint32_t*>(bp);
             wp[0] = w[0]; wp[1] = w[1]; wp[2] = w[2];
         }
-        a.scales[orow * a.nblk + bv] = f32_to_f16_bits(scale * a.scale_sign_outlier);
+        a.scales[orow * a.nblk + bv] = f32_to_f16_bits(scale * (NORMAL ? a.scale_sign_normal : a.scale_sign_outlier));
     }
 }
 
@@ -401,14 +403,19 @@ int grid_for(long long work_items) {
 template <typename T>
 int launch_quant(int bits, const QuantArgs& a, const Codebook& n, const Codebook& o, cudaStream_t s) {
     const long long blocks = a.n_rows * a.nblk;
-    const bool pqo = a.norm_mode == TQB_MAXNORM && !a.pre_rotated && a.dev_boundaries == nullptr &&
-                     a.outlier_blocks >= a.nblk && (bits == 3 || bits == 4) && blocks < (1LL << 31) &&
-                     a.map.rows_per_group < (1LL << 31) &&
-                     ((uintptr_t)a.indices % 16) == 0 && ((uintptr_t)a.indices2 % 16) == 0;
-    if (pqo) {
+    const bool one_table = a.norm_mode == TQB_MAXNORM && !a.pre_rotated && a.dev_boundaries == nullptr &&
+                           (bits == 3 || bits == 4) && blocks < (1LL << 31) && a.map.rows_per_group < (1LL << 31) &&
+                           ((uintptr_t)a.indices % 16) == 0 && ((uintptr_t)a.indices2 % 16) == 0;
+    if (one_table && a.outlier_blocks >= a.nblk) {   // every block on the outlier codebook
         const dim3 grid(grid_for(blocks), a.x2 ? 2 : 1);
-        if (bits == 4) block_quantize_pqo_kernel<T, 4><<<grid, kThreads, 0, s>>>(a, o);
-        else block_quantize_pqo_kernel<T, 3><<<grid, kThreads, 0, s>>>(a, o);
+        if (bits == 4) block_quantize_pqo_kernel<T, 4, false><<<grid, kThreads, 0, s>>>(a, o);
+        else block_quantize_pqo_kernel<T, 3, false><<<grid, kThreads, 0, s>>>(a, o);
+        return check_launch(s);
+    }
+    if (one_table && a.outlier_blocks == 0) {        // every block on the normal codebook
+        const dim3 grid(grid_for(blocks), a.x2 ? 2 : 1);
+        if (bits == 4) block_quantize_pqo_kernel<T, 4, true><<<grid, kThreads, 0, s>>>(a, n);
+        else block_quantize_pqo_kernel<T, 3, true><<<grid, kThreads, 0, s>>>(a, n);
         return check_launch(s);
     }
     const long long lanes = a.n_rows * a.nblk * 4;

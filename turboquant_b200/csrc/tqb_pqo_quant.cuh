@@ -88,8 +88,9 @@ __device__ __forceinline__ void build_cell_table(const Codebook& cb, int n_bnd, 
 
 // x: the block's 32 input values (16-byte aligned).  w: packed codes (4 * BITS bytes, LSB-first), returns the
 // f32 scale (before the outlier sign).  cb: the outlier codebook of BITS bits.  lut: the 3-bit cell table in
-// shared memory (build_cell_table), or nullptr for the register bisection.
-template <typename T, int BITS>
+// shared memory (build_cell_table), or nullptr for the register bisection.  TABLE: the codebook is not the
+// 4-bit uniform grid even when BITS = 4 (codes of a narrower codebook stored at BITS width); needs lut.
+template <typename T, int BITS, bool TABLE = false>
 __device__ __forceinline__ float pqo_quantize_block(const T* x, const Codebook& cb, float outer_centroid, uint32_t (&w)[4],
                                                     const float2* lut = nullptr) {
     const float inv_sqrt = 1.0f / sqrtf((float)kBlock);
@@ -106,7 +107,7 @@ __device__ __forceinline__ float pqo_quantize_block(const T* x, const Codebook& 
     const float scale = raw > kMinNorm ? raw : kMinNorm;
     const float r = __frcp_rn(scale);
     w[0] = w[1] = w[2] = w[3] = 0u;
-    if (BITS == 4) {
+    if (BITS == 4 && !TABLE) {
         const float cpos = (inv_sqrt * r) * inv_step, cneg = -cpos;
         const float kMagic = 12582912.0f;          // 1.5 * 2^23
         bool near = false;
@@ -150,9 +151,9 @@ __device__ __forceinline__ float pqo_quantize_block(const T* x, const Codebook& 
                 const bool p3 = t > t3;
                 c = (p1 ? 4u : 0u) + (p2 ? 2u : 0u) + (p3 ? 1u : 0u);
             }
-            const int bit = 3 * i;
+            const int bit = BITS * i;
             w[bit >> 5] += c << (bit & 31);
-            if ((bit & 31) > 29) w[(bit >> 5) + 1] += c >> (32 - (bit & 31));
+            if ((bit & 31) + BITS > 32) w[(bit >> 5) + 1] += c >> (32 - (bit & 31));
         }
     }
     return scale;
