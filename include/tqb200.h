@@ -288,6 +288,18 @@ int32_t tqb_decode_num_partitions(int32_t num_kv_heads, int32_t kv_len);
 size_t tqb_decode_scratch_bytes(int32_t num_q_heads, int32_t head_dim, int32_t num_partitions);
 int tqb_decode_attention(const tqb_decode_params *p, tqb_stream_t stream);
 
+/* Causal attention of a chunk of q_len query tokens over the packed cache (the chunk's own K/V rows already
+ * stored, e.g. by tqb_block_quantize_pair or tqb_pqo_cache_prefill).  No counterpart kernel in the reference:
+ * its prefill dequantizes the whole cache and hands it to the engine's attention (src/cache/pqo.rs:184-200,
+ * src/cache/common.rs:16-62).
+ *   q, out   [q_len, num_q_heads, head_dim] (token-major); query token i attends to the first
+ *            kv_len - q_len + i + 1 tokens, so p->kv_len counts the chunk and must be >= q_len.
+ *   scratch  >= tqb_decode_scratch_bytes(num_q_heads * q_len, head_dim, P), with P = p->num_partitions or
+ *            tqb_decode_num_partitions(num_kv_heads * q_len, kv_len) when that is 0.
+ *   lse_out  [q_len, num_q_heads][2] when given; append_k / append_v must be NULL; rq (QJL) is
+ *            [q_len, num_q_heads, head_dim].  All other fields as for tqb_decode_attention. */
+int tqb_chunk_attention(const tqb_decode_params *p, int32_t q_len, tqb_stream_t stream);
+
 /* tqb_decode_attention for callers that cannot allocate device memory.  No counterpart in the
  * reference (there the caller always allocates the partial buffers, src/cache/cuda/attention.rs:65-77).
  * Meant for hosts that have given all free device memory to their own pool at start-up, or that must

@@ -382,3 +382,44 @@ def test_packed_shard_merge_equals_plain_shard_merge():
     assert lib.tqb_lse_combine_packed(packed.data_ptr(), S, hq, D, got.data_ptr(), 0, None) == 0
     torch.cuda.synchronize()
     assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("bits,hq,hkv,past,q_len,dtype,general", [
+    (4, 8, 2, 300, 17, torch.bfloat16, False),     # tensor-core kernel, g = 4
+    (3, 4, 2, 0, 33, torch.float32, False),        # no past: the first query sees one token; empty partitions
+    (4, 16, 2, 1000, 5, torch.float16, False),     # g = 8
+    (4, 4, 4, 64, 9, torch.float32, True),         # general kernel
+    (3, 6, 2, 129, 12, torch.bfloat16, False),     # g = 3
+])
+def test_chunk_attention_is_causal_decode_per_query_token(bits, hq, hkv, past, q_len, dtype, general):
+    # prefill chunk over the packed cache: query token i must equal a decode step that sees past + i + 1 tokens
+    rng = np.random.default_rng(bits * 100 + hq + past + q_len)
+    kv_len, stride, d = past + q_len, past + q_len + 7, 128
+    k = rng.standard_normal((hkv * stride, d)).astype(np.float32)
+    v = rng.standard_normal((hkv * stride, d)).astype(np.float32)
+    ki, ks = tq.block_quantize(dev(k), bits)
+    vi, vs = tq.block_quantize(dev(v), bits)
+    ki, ks, vi, vs = (t.view(hkv, stride, -1) for t in (ki, ks, vi, vs))
+    q = torch.from_numpy((rng.standard_normal((q_len, hq, d)) / np.sqrt(d)).astype(np.float32)).to(dtype)
+    scale = 1.0 / np.sqrt(d)
+    got = tq.chunk_attention(q.cuda(), ki, ks, vi, vs, kv_len, bits, scale, out_dtype=torch.float32,
+                             force_general=general).cpu().numpy()
+    assert got.shape == (q_len, hq, d)
+    kin, ksn, vin, vsn = ki.cpu().numpy(), u16(ks), vi.cpu().numpy(), u16(vs)
+    qf = q.float().numpy()
+    for i in range(q_len):
+        want = o.block_attention(bits, d, 0, -1, qf[i], kin, ksn, vin, vsn, past + i + 1, scale, nthreads=4)
+        assert np.abs(got[i] - want).max() < 2e-3, (i, np.abs(got[i] - want).max())
+        assert np.abs(got[i] - want).max() < 1e-4     # measured: a few 1e-5
+    # a chunk of one token is a decode step
+    one = tq.chunk_attention(q[-1:].cuda(), ki, ks, vi, vs, kv_len, bits, scale, out_dtype=torch.float32).cpu().numpy()
+    dec = tq.decode_attention(q[-1].cuda(), ki, ks, vi, vs, kv_len, bits, scale, out_dtype=torch.float32).cpu().numpy()
+    assert np.array_equal(one[0], dec)
+
+
+def test_chunk_attention_argument_errors():
+    ki = torch.zeros((2, 16, 64), dtype=torch.uint8, device="cuda")
+    ks = torch.zeros((2, 16, 4), dtype=torch.int16, device="cuda")
+    q = torch.zeros((9, 4, 128), device="cuda")
+    with pytest.raises(tq.RangeOutOfBounds):
+        tq.chunk_attention(q, ki, ks, ki, ks, 8, 4, 0.1)     # fewer tokens stored than the chunk holds

@@ -549,6 +549,36 @@ def decode_attention(q, k_idx, k_sc, v_idx, v_sc, kv_len, bits, softmax_scale, n
     return (out, lse) if return_lse else out
 
 
+def chunk_attention(q, k_idx, k_sc, v_idx, v_sc, kv_len, bits, softmax_scale, norm_mode=QuantNormMode.MaxNorm,
+                    outlier_blocks=ALL_BLOCKS, num_partitions=0, out_dtype=None, qjl=None, force_general=False):
+    """Causal attention of a chunk of query tokens over the packed cache (tqb_chunk_attention).
+
+    q [q_len, Hq, D]; the cache arrays as for decode_attention, with the chunk's own K/V rows already stored;
+    query token i attends to the first kv_len - q_len + i + 1 tokens.  Returns [q_len, Hq, D]."""
+    q_len, hq, d = q.shape
+    hkv, stride = k_idx.shape[0], k_idx.shape[1]
+    q = q.contiguous()
+    out_dtype = out_dtype or q.dtype
+    out = torch.empty((q_len, hq, d), dtype=out_dtype, device=q.device)
+    parts = num_partitions or int(lib.tqb_decode_num_partitions(hkv * q_len, kv_len))
+    sbytes = int(lib.tqb_decode_scratch_bytes(hq * q_len, d, parts))
+    scratch = torch.empty((max(sbytes, 16),), dtype=torch.uint8, device=q.device)
+    p = TqbDecodeParams()
+    p.q, p.k_indices, p.k_scales, p.v_indices, p.v_scales = (q.data_ptr(), k_idx.data_ptr(), k_sc.data_ptr(),
+                                                             v_idx.data_ptr(), v_sc.data_ptr())
+    p.out, p.lse_out = out.data_ptr(), None
+    p.scratch, p.scratch_bytes = scratch.data_ptr(), scratch.numel()
+    if qjl is not None:
+        p.qjl_signs, p.qjl_norms, p.rq, p.qjl_enabled = qjl[0].data_ptr(), qjl[1].data_ptr(), qjl[2].data_ptr(), 1
+    p.q_dtype, p.out_dtype = _dtype_code(q.dtype), _dtype_code(out_dtype)
+    p.bits, p.head_dim, p.norm_mode, p.outlier_blocks = bits, d, int(norm_mode), outlier_blocks
+    p.num_q_heads, p.num_kv_heads, p.kv_len, p.kv_stride = hq, hkv, kv_len, stride
+    p.num_partitions, p.softmax_scale = parts, softmax_scale
+    p.flags = 2 if force_general else 0
+    check(lib.tqb_chunk_attention(ctypes.byref(p), q_len, _stream()))
+    return out
+
+
 def lse_combine(partial_out, partial_lse, out_dtype=torch.float32):
     """Merge shard-local (un-normalised output, (max, sum)) pairs: [S, Hq, D], [S, Hq, 2]."""
     s, hq, d = partial_out.shape

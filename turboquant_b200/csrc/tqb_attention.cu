@@ -25,7 +25,7 @@ namespace tqb {
 int block_cfg_check(int bits, int head_dim, int norm_mode);
 int launch_decode_mma(const tqb_decode_params* p, int num_partitions, float* partial_out, float* partial_max,
                       float* partial_sum, float sign_mag, unsigned* counters, bool counters_clean, cudaStream_t s,
-                      const int* gate = nullptr, int gate_want = 0, const float* dev_signs = nullptr);
+                      const int* gate = nullptr, int gate_want = 0, const float* dev_signs = nullptr, int alias_heads = 0);
 
 namespace {
 
@@ -54,6 +54,9 @@ struct DecodeArgs {
     float softmax_scale;
     float sign_mag;
     const int* gate;     // reference entry point: run only if *gate == 0 (the caller's tables are not the standard ones)
+    // causal chunk: grid head x = query position x / alias_heads on cache head x % alias_heads with
+    // kv_len0 + x / alias_heads tokens (0: off)
+    int alias_heads, kv_len0;
 };
 
 __device__ __forceinline__ float warp_sum(float v) {
@@ -103,12 +106,18 @@ decode_general_kernel(DecodeArgs a, Codebook normal, Codebook outlier) {
     }
     __syncthreads();
 
+    int kv_len = a.kv_len, cache_head = kvh;
+    if (a.alias_heads > 0) {
+        const int pos = kvh / a.alias_heads;
+        cache_head = kvh - pos * a.alias_heads;
+        kv_len = a.kv_len0 + pos;
+    }
     const int t0 = part * a.part_size;
-    const int t1 = min(t0 + a.part_size, a.kv_len);
+    const int t1 = min(t0 + a.part_size, kv_len);
     const float inv_sqrt = 1.0f / sqrtf((float)kBlock);
     const float qjl_c = 1.2533141f * (1.0f / sqrtf((float)D));  // tq_attention_kernel.cu:225
 
-    const size_t row0 = (size_t)kvh * a.kv_stride;
+    const size_t row0 = (size_t)cache_head * a.kv_stride;
     const uint32_t* kw = reinterpret_cast<const uint32_t*>(a.k_idx);
     const uint32_t* vw = reinterpret_cast<const uint32_t*>(a.v_idx);
 
@@ -422,7 +431,8 @@ size_t tqb_decode_scratch_bytes(int32_t num_q_heads, int32_t head_dim, int32_t n
     return ticket_bytes(num_q_heads) + sizeof(float) * (size_t)num_q_heads * num_partitions * ((size_t)head_dim + 2);
 }
 
-int tqb_decode_attention(const tqb_decode_params* p, tqb_stream_t stream) {
+// alias_heads > 0: p is a causal chunk folded into heads (see tqb_chunk_attention)
+static int decode_impl(const tqb_decode_params* p, int alias_heads, tqb_stream_t stream) {
     if (!p) return TQB_ERR_NULL_POINTER;
     int st = block_cfg_check(p->bits, p->head_dim, p->norm_mode);
     if (st != TQB_OK) return st;
@@ -457,6 +467,8 @@ int tqb_decode_attention(const tqb_decode_params* p, tqb_stream_t stream) {
     a.hq = p->num_q_heads; a.hkv = p->num_kv_heads; a.head_dim = p->head_dim; a.nblk = p->head_dim / kBlock;
     a.bits = p->bits; a.packed_dim = p->head_dim * p->bits / 8;
     a.kv_len = p->kv_len; a.kv_stride = p->kv_stride; a.num_partitions = P;
+    a.alias_heads = alias_heads;
+    a.kv_len0 = alias_heads > 0 ? p->kv_len - p->num_kv_heads / alias_heads + 1 : p->kv_len;
     a.part_size = ((p->kv_len + P - 1) / P + kWarps - 1) / kWarps * kWarps;
     if (a.part_size < kWarps) a.part_size = kWarps;
     const int ob = p->outlier_blocks < 0 || p->outlier_blocks >= a.nblk ? a.nblk : p->outlier_blocks;
@@ -478,7 +490,8 @@ int tqb_decode_attention(const tqb_decode_params* p, tqb_stream_t stream) {
         // tensor-core kernels for the shapes they cover; everything else takes the general kernel
         // (the merge runs inside the kernel, in the CTA that finishes a KV head last)
         st = launch_decode_mma(&local, P, a.partial_out, a.partial_max, a.partial_sum, a.sign_mag,
-                               partials_only ? nullptr : tickets, (p->flags & TQB_DECODE_TICKETS_ZERO) != 0, as_stream(stream));
+                               partials_only ? nullptr : tickets, (p->flags & TQB_DECODE_TICKETS_ZERO) != 0, as_stream(stream),
+                               nullptr, 0, nullptr, alias_heads);
         if (st == TQB_ERR_UNSUPPORTED && local.append_k != nullptr) {
             st = append_separately();
             if (st != TQB_OK) return st;
@@ -492,6 +505,25 @@ int tqb_decode_attention(const tqb_decode_params* p, tqb_stream_t stream) {
         if (st != TQB_OK) return st;
     }
     return run_decode(a, cn, co, p->q_dtype, p->out, p->out_dtype, p->lse_out, as_stream(stream), partials_only);
+}
+
+int tqb_decode_attention(const tqb_decode_params* p, tqb_stream_t stream) { return decode_impl(p, 0, stream); }
+
+// Causal attention of a chunk of q_len consecutive query tokens over the packed cache.  Query position i is
+// run as one more "sequence" of a batched decode whose cache rows are those of the one real sequence: grid
+// head (i, kv head) reads cache head `kv head` and stops after kv_len - q_len + i + 1 tokens.  The chunk
+// re-reads the cache once per query position, mostly from L2.
+int tqb_chunk_attention(const tqb_decode_params* p, int32_t q_len, tqb_stream_t stream) {
+    if (!p) return TQB_ERR_NULL_POINTER;
+    if (q_len <= 0) return TQB_ERR_INVALID_ARGUMENT;
+    if (p->append_k != nullptr || p->append_v != nullptr) return TQB_ERR_INVALID_ARGUMENT;   // the chunk is stored first
+    if (p->kv_len < q_len) return TQB_ERR_RANGE_OUT_OF_BOUNDS;
+    if (p->num_q_heads <= 0 || p->num_kv_heads <= 0) return TQB_ERR_INVALID_ARGUMENT;
+    if ((long long)p->num_q_heads * q_len > (1 << 24)) return TQB_ERR_TOO_LARGE;
+    tqb_decode_params f = *p;
+    f.num_q_heads = p->num_q_heads * q_len;
+    f.num_kv_heads = p->num_kv_heads * q_len;
+    return decode_impl(&f, p->num_kv_heads, stream);
 }
 
 static int lse_combine_impl(const float* po, const float* lse, size_t po_stride, size_t lse_stride, int32_t num_shards,

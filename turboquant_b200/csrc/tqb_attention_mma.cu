@@ -81,6 +81,9 @@ struct MmaArgs {
     const int* gate;
     int gate_want;
     const float* dev_signs;   // with a gate: the caller's sign pattern (its magnitude replaces sign_mag)
+    // causal chunk: "KV head" x of the grid is query position x / alias_heads on cache head x % alias_heads and
+    // sees kv_len0 + x / alias_heads tokens (0: off, every head has its own rows and kv_len tokens)
+    int alias_heads, kv_len0;
 };
 
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -427,10 +430,16 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
     const int g = a.g;
 
     // ---- start streaming the first stages before anything else: the copies do not depend on q ----
+    int kv_len = a.kv_len, cache_head = kvh;
+    if (a.alias_heads > 0) {
+        const int pos = kvh / a.alias_heads;
+        cache_head = kvh - pos * a.alias_heads;
+        kv_len = a.kv_len0 + pos;
+    }
     const int t_begin = part * a.part_size;
-    const int t_end = min(t_begin + a.part_size, a.kv_len);
-    const size_t row0 = (size_t)kvh * a.kv_stride;
-    const int last = a.kv_len - 1;
+    const int t_end = min(t_begin + a.part_size, kv_len);
+    const size_t row0 = (size_t)cache_head * a.kv_stride;
+    const int last = kv_len - 1;
     const int first = t_begin + warp * kGroup;
     const int stride = kWarps * kGroup;
     const int ngroups = first < t_end ? (t_end - first + stride - 1) / stride : 0;
@@ -991,7 +1000,7 @@ int launch(const MmaArgs& a, int g, int q_dtype, bool allow_tma, const Codebook&
 // caller vouches for them (counters_clean).
 int launch_decode_mma(const tqb_decode_params* p, int num_partitions, float* partial_out, float* partial_max,
                       float* partial_sum, float sign_mag, unsigned* counters, bool counters_clean, cudaStream_t s,
-                      const int* gate, int gate_want, const float* dev_signs) {
+                      const int* gate, int gate_want, const float* dev_signs, int alias_heads) {
     const int g = p->num_q_heads / p->num_kv_heads;
     const int nblk = p->head_dim / kBlock;
     const bool all_outlier = p->outlier_blocks < 0 || p->outlier_blocks >= nblk;
@@ -1028,6 +1037,9 @@ int launch_decode_mma(const tqb_decode_params* p, int num_partitions, float* par
     a.gate = gate;
     a.gate_want = gate_want;
     a.dev_signs = dev_signs;
+    a.alias_heads = alias_heads;
+    a.kv_len0 = alias_heads > 0 ? p->kv_len - p->num_kv_heads / alias_heads + 1 : p->kv_len;
+    if (alias_heads > 0 && p->append_k != nullptr) return TQB_ERR_UNSUPPORTED;
     a.counters = counters;
     a.out = p->out;
     a.lse_out = p->lse_out;
@@ -1037,7 +1049,7 @@ int launch_decode_mma(const tqb_decode_params* p, int num_partitions, float* par
         if (e != cudaSuccess) { set_cuda_error(e); return TQB_ERR_CUDA; }
     }
     dim3 grid(p->num_kv_heads, num_partitions);
-    const bool allow_tma = (p->flags & TQB_DECODE_TMA) != 0;
+    const bool allow_tma = (p->flags & TQB_DECODE_TMA) != 0 && alias_heads == 0;   // the tensor maps assume one row range per grid head
     const float log2e = 1.4426950408889634f;
     if (pqo4) {
         const float R = 2.1573f;
