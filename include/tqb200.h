@@ -355,6 +355,14 @@ int tqb_pqo_cache_decode(tqb_pqo_cache *c, int32_t layer, const void *k, const v
  * kernels of neighbouring calls; the host `out` buffers are complete once this call returns (it blocks the
  * calling thread on the last outstanding result copy). */
 int tqb_pqo_cache_host_sync(tqb_pqo_cache *c);
+/* Prefill with attention inside the cache: quantize and append the chunk (as tqb_pqo_cache_prefill), then causal
+ * attention of its new_tokens queries over everything stored (tqb_chunk_attention).  The reference's prefill
+ * (pqo.rs:184-200) returns the dequantized cache for the engine's own attention instead.  Device buffers:
+ * k, v [batch, num_kv_heads, new_tokens, head_dim]; q, out [new_tokens, batch * num_q_heads, head_dim]. */
+int tqb_pqo_cache_prefill_attend(tqb_pqo_cache *c, int32_t layer, const void *k, const void *v, const void *q,
+                                 int32_t dtype, int32_t new_tokens, int32_t num_q_heads, float softmax_scale,
+                                 void *out, tqb_stream_t stream);
+
 /* dequantize_full (pqo.rs:176-180): [batch, num_kv_heads, seq_len, head_dim] of `dtype`. */
 int tqb_pqo_cache_dequantize_full(tqb_pqo_cache *c, int32_t layer, void *k_out, void *v_out, int32_t dtype,
                                   int32_t host_buffers, tqb_stream_t stream);

@@ -423,3 +423,38 @@ def test_chunk_attention_argument_errors():
     q = torch.zeros((9, 4, 128), device="cuda")
     with pytest.raises(tq.RangeOutOfBounds):
         tq.chunk_attention(q, ki, ks, ki, ks, 8, 4, 0.1)     # fewer tokens stored than the chunk holds
+
+
+@pytest.mark.parametrize("bits", [3, 4])
+def test_pqo_cache_prefill_attend_two_chunks_then_decode(bits):
+    # batch 2, two prefill chunks with attention inside the cache, then a decode step: every query token equals
+    # oracle attention over the oracle-quantized cache truncated at that token (causal)
+    b, hkv, hq, d, scale = 2, 2, 8, 128, 0.0884
+    cfg = tq.CacheConfig(bits=bits, head_dim=d, num_kv_heads=hkv, num_layers=1, batch=b)
+    cache = tq.PqoCache(cfg)
+    g = torch.Generator().manual_seed(bits)
+    ks_all, vs_all = [], []
+    for t in (37, 20):
+        k = torch.randn((b, hkv, t, d), generator=g).bfloat16()
+        v = torch.randn((b, hkv, t, d), generator=g).bfloat16()
+        q = (torch.randn((b, hq, t, d), generator=g) / d ** 0.5).bfloat16()
+        past = cache.seq_len(0)
+        out = cache.prefill_attend(0, k.cuda(), v.cuda(), q.cuda(), tq.AttendConfig(softmax_scale=scale, n_kv_groups=hq // hkv))
+        assert out.shape == (b, hq, t, d) and cache.seq_len(0) == past + t
+        ks_all.append(k)
+        vs_all.append(v)
+        allk = torch.cat(ks_all, dim=2).float().numpy()
+        allv = torch.cat(vs_all, dim=2).float().numpy()
+        n = allk.shape[2]
+        kp, ksc = o.block_quantize(bits, d, 0, -1, allk.reshape(-1, d))
+        vp, vsc = o.block_quantize(bits, d, 0, -1, allv.reshape(-1, d))
+        kp, ksc, vp, vsc = (a.reshape(b * hkv, n, -1) for a in (kp, ksc, vp, vsc))
+        got = out.float().cpu().numpy()
+        for i in (0, t // 2, t - 1):
+            want = o.block_attention(bits, d, 0, -1, q[:, :, i].float().numpy().reshape(b * hq, d), kp, ksc, vp, vsc,
+                                     past + i + 1, scale)
+            assert np.abs(got[:, :, i].reshape(b * hq, d) - want).max() < 1e-2   # bf16 output
+    k1 = torch.randn((b, hkv, 1, d), generator=g).bfloat16().cuda()
+    q1 = (torch.randn((b, hq, 1, d), generator=g) / d ** 0.5).bfloat16().cuda()
+    dec = cache.decode(0, k1, k1, q1, tq.AttendConfig(softmax_scale=scale, n_kv_groups=hq // hkv))
+    assert dec.is_fused() and cache.seq_len(0) == 58 and torch.isfinite(dec.fused.float()).all()

@@ -96,6 +96,7 @@ def _declare(lib):
         "tqb_pqo_cache_destroy": (None, [P]),
         "tqb_pqo_cache_prefill": (c_int, [P, I, P, P, I, I, P, P, I, P]),
         "tqb_pqo_cache_decode": (c_int, [P, I, P, P, P, I, I, F, P, I, P]),
+        "tqb_pqo_cache_prefill_attend": (c_int, [P, I, P, P, P, I, I, I, F, P, P]),
         "tqb_pqo_cache_host_sync": (c_int, [P]),
         "tqb_pqo_cache_dequantize_full": (c_int, [P, I, P, P, I, I, P]),
         "tqb_pqo_cache_seq_len": (L, [P, I]),

@@ -658,6 +658,18 @@ class PqoCache:
                                        config.softmax_scale, _ptr(out), self._host(k), _stream()))
         return DecodeOutput(fused=out)
 
+    def prefill_attend(self, layer, k, v, q, config):
+        """Prefill with the attention done over the packed cache (no counterpart in pqo.rs, whose prefill returns the
+        dequantized cache): stores the chunk, then causal attention of its queries over everything stored.
+        k, v [batch, Hkv, T, D]; q [batch, Hq, T, D] (device tensors); returns [batch, Hq, T, D]."""
+        k, v = k.contiguous(), v.contiguous()
+        b, hq, t, d = q.shape
+        qt = q.permute(2, 0, 1, 3).contiguous()            # [T, batch * Hq, D]
+        out = torch.empty_like(qt)
+        check(lib.tqb_pqo_cache_prefill_attend(self._h, layer, _ptr(k), _ptr(v), _ptr(qt), _dtype_code(k.dtype), t, hq,
+                                               config.softmax_scale, _ptr(out), _stream()))
+        return out.view(t, b, hq, d).permute(1, 2, 0, 3).contiguous()
+
     def host_sync(self):
         """Blocks until the results of earlier decode() calls with host tensors have reached the host."""
         check(lib.tqb_pqo_cache_host_sync(self._h))

@@ -245,6 +245,31 @@ struct tqb_pqo_cache {
         p.append_v = append_v;
         return tqb_decode_attention(&p, s);
     }
+    // Causal attention of the last q_len stored tokens' queries over the layer (q, out: [q_len, batch * Hq, D]).
+    int attend_chunk(int layer, const void* q_dev, int dtype, int num_q_heads, int q_len, float softmax_scale, void* out_dev,
+                     cudaStream_t s) {
+        Layer& l = layers[layer];
+        tqb_decode_params p{};
+        p.q = q_dev;
+        p.k_indices = l.ki; p.k_scales = l.ks; p.v_indices = l.vi; p.v_scales = l.vs;
+        p.out = out_dev;
+        p.q_dtype = dtype;
+        p.out_dtype = dtype;
+        p.bits = cfg.bits; p.head_dim = cfg.head_dim; p.norm_mode = cfg.norm_mode; p.outlier_blocks = cfg.outlier_blocks;
+        p.num_q_heads = cfg.batch * num_q_heads;
+        p.num_kv_heads = heads;
+        p.kv_len = (int32_t)l.len;
+        p.kv_stride = (int32_t)l.cap;
+        p.num_partitions = tqb_decode_num_partitions(heads * q_len, (int32_t)l.len);
+        p.softmax_scale = softmax_scale;
+        const int folded = p.num_q_heads * q_len;
+        const size_t need = tqb_decode_scratch_bytes(folded, cfg.head_dim, p.num_partitions);
+        TQB_TRY(prepare_scratch(scratch, ticket_heads, need, folded, cfg.head_dim, p.num_partitions, s));
+        p.scratch = scratch.p;
+        p.scratch_bytes = scratch.bytes;
+        p.flags = TQB_DECODE_TICKETS_ZERO;
+        return tqb_chunk_attention(&p, q_len, s);
+    }
     int ticket_heads = -1;   // head count the zeroed ticket area of `scratch` was sized for
 };
 
@@ -308,6 +333,19 @@ int tqb_pqo_cache_prefill(tqb_pqo_cache* c, int32_t layer, const void* k, const 
     // pqo.rs:194-199: the first prefill hands back the original tensors
     if (old_len > 0 && k_out && v_out) TQB_TRY(c->dequantize_full(layer, k_out, v_out, dtype, host_buffers != 0, s));
     return TQB_OK;
+}
+
+int tqb_pqo_cache_prefill_attend(tqb_pqo_cache* c, int32_t layer, const void* k, const void* v, const void* q, int32_t dtype,
+                                 int32_t new_tokens, int32_t num_q_heads, float softmax_scale, void* out,
+                                 tqb_stream_t stream) {
+    TQB_TRY(check_layer(c, layer));
+    if (new_tokens <= 0) return TQB_ERR_INVALID_ARGUMENT;
+    if (dtype != TQB_F32 && dtype != TQB_F16 && dtype != TQB_BF16) return TQB_ERR_INVALID_ARGUMENT;
+    if (num_q_heads <= 0 || num_q_heads % c->cfg.num_kv_heads != 0) return TQB_ERR_INVALID_ARGUMENT;
+    if (!k || !v || !q || !out) return TQB_ERR_NULL_POINTER;
+    cudaStream_t s = as_stream(stream);
+    TQB_TRY(c->quantize_and_store(layer, k, v, dtype, new_tokens, s));
+    return c->attend_chunk(layer, q, dtype, num_q_heads, new_tokens, softmax_scale, out, s);
 }
 
 int tqb_pqo_cache_decode(tqb_pqo_cache* c, int32_t layer, const void* k, const void* v, const void* q, int32_t dtype,
