@@ -241,24 +241,10 @@ __device__ __forceinline__ uint4 lds128_volatile_o(uint32_t base) {
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(base), "n"(OFF));
     return v;
 }
-__device__ __forceinline__ uint4 lds128_volatile(uint32_t addr) {
-    uint4 v;   // volatile: re-read where it is used instead of being kept in registers across the loop
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-    return v;
-}
-__device__ __forceinline__ uint2 lds64(uint32_t addr) {
-    uint2 v;
-    asm("ld.shared.v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(addr) : "memory");
-    return v;
-}
 
 // Four 8x8 matrices of 16-bit elements; lane l supplies the address of row l & 7 of matrix l >> 3.
 // Plain: lane (n, j) receives elements 2j, 2j+1 of row n (one 32-bit word).  Transposed: it receives
 // element n of rows 2j and 2j+1.
-__device__ __forceinline__ void ldsm4(uint32_t addr, uint32_t (&r)[4]) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr) : "memory");
-}
 template <int OFF>
 __device__ __forceinline__ void ldsm4_o(uint32_t base, uint32_t (&r)[4]) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4+%5];\n"
@@ -268,10 +254,6 @@ template <int OFF>
 __device__ __forceinline__ void ldsm4t_o(uint32_t base, uint32_t (&r)[4]) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4+%5];\n"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(base), "n"(OFF) : "memory");
-}
-__device__ __forceinline__ void ldsm4t(uint32_t addr, uint32_t (&r)[4]) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr) : "memory");
 }
 
 // Transpose of an 8x8 matrix of 16-bit elements held one row per lane group: lane (n, j) gives elements

@@ -244,7 +244,7 @@ template <int EPL, int BITS>
 __global__ void __launch_bounds__(kWholeWarps * 32, 3)
 whole_quantize_lane_kernel(WholeArgs a, Codebook cb) {
     constexpr int D = 32 * EPL, KPW = 32 / EPL, NB = (1 << BITS) - 1;
-    extern __shared__ __align__(128) unsigned char smem_raw[];
+    extern __shared__ __align__(16) unsigned char smem_raw[];
     float2* s_cell = reinterpret_cast<float2*>(smem_raw);   // [kWholeCells][32]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     unsigned char* stage = smem_raw + (size_t)kWholeCells * 32 * sizeof(float2) + (size_t)warp * 32 * kWholeRowB;
@@ -667,7 +667,7 @@ scores_table_kernel(const float* __restrict__ q, const float* __restrict__ rq, c
     constexpr int D = 32 * EPL, CH = ChunkGeo<PB>::kCodes, CB = ChunkGeo<PB>::kBits, ENT = ChunkGeo<PB>::kEntries;
     constexpr int NJ = 32 / CH;
     constexpr int KPW = 32 / EPL;   // keys per warp step
-    extern __shared__ __align__(128) unsigned char smem_raw[];
+    extern __shared__ __align__(16) unsigned char smem_raw[];
     float* t_base = reinterpret_cast<float*>(smem_raw);   // [NJ][ENT][32]
     float* t_sign = t_base + NJ * ENT * 32;               // [8][16][32]
     float* s_q = t_sign + 8 * 16 * 32;                    // rotated query
