@@ -865,7 +865,7 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
             m.dev_signs = nullptr; m.out = a.out; m.lse_out = a.lse_out;
             m.head_dim = kD; m.nblk = kD / 32; m.num_partitions = a.num_partitions; m.rotate = 1;
             m.out_dtype = a.out_dtype; m.sign_mag = a.sign_mag;
-            for (int hh = 0; hh < g; ++hh) merge_head(m, kvh * g + hh, lane, warp, kWarps);
+            for (int hh = warp; hh < g; hh += kWarps) merge_head(m, kvh * g + hh, lane, 0, 1);   // one warp per query head
             if (tid == 0) a.counters[kvh] = 0u;   // ready for the next launch
         }
     }

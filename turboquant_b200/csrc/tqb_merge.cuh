@@ -51,21 +51,40 @@ __device__ __forceinline__ void merge_head(const MergeArgs& a, int head, int lan
     const int D = a.head_dim, P = a.num_partitions;
     const float* pm = a.partial_max + (size_t)head * P;
     const float* ps = a.partial_sum + (size_t)head * P;
-    float M = -FLT_MAX;
-    for (int p = lane; p < P; p += 32) M = fmaxf(M, __ldcg(pm + p));
+    // Lane p keeps (max, sum) of partition p; both loads are issued before either is used, and the partial
+    // outputs below are fetched eight at a time, so the merge costs a few trips to L2, not one per partition.
+    float pmv = -FLT_MAX, psv = 0.0f;
+    if (lane < P) {
+        pmv = __ldcg(pm + lane);
+        psv = __ldcg(ps + lane);
+    }
+    float M = pmv;
+    for (int p = lane + 32; p < P; p += 32) M = fmaxf(M, __ldcg(pm + p));
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-    float L = 0.0f;
-    for (int p = lane; p < P; p += 32) L += __ldcg(ps + p) * expf(__ldcg(pm + p) - M);
+    const float wl = lane < P ? expf(pmv - M) : 0.0f;   // weight of partition `lane`
+    float L = lane < P ? psv * wl : 0.0f;
+    for (int p = lane + 32; p < P; p += 32) L += __ldcg(ps + p) * expf(__ldcg(pm + p) - M);
     L = sum32(L);
     const float inv_sqrt = 1.0f / sqrtf((float)kBlock);
     const uint32_t neg = 0xB1A6D4B2u;   // src/cache/precomputed/rotation.rs:16-20
     const float sg = a.dev_signs ? a.dev_signs[lane] : (((neg >> lane) & 1u) ? -a.sign_mag : a.sign_mag);
     const float inv_l = L > 0.0f ? 1.0f / L : 0.0f;
     for (int b = warp; b < a.nblk; b += nwarps) {
-        float acc = 0.0f;
-        for (int p = 0; p < P; ++p)
-            acc = fmaf(__ldcg(a.partial_out + ((size_t)head * P + p) * D + b * 32 + lane), expf(__ldcg(pm + p) - M), acc);
+        const float* po = a.partial_out + (size_t)head * P * D + b * 32 + lane;
+        float acc = 0.0f;   // sum over partitions in ascending order
+        if (P <= 32) {
+            for (int p0 = 0; p0 < P; p0 += 8) {
+                float v[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = p0 + i < P ? __ldcg(po + (size_t)(p0 + i) * D) : 0.0f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    if (p0 + i < P) acc = fmaf(v[i], __shfl_sync(0xffffffffu, wl, p0 + i), acc);
+            }
+        } else {
+            for (int p = 0; p < P; ++p) acc = fmaf(__ldcg(po + (size_t)p * D), expf(__ldcg(pm + p) - M), acc);
+        }
         if (a.rotate) acc = wht32(acc * sg, lane) * inv_sqrt;
         if (a.lse_out == nullptr) acc *= inv_l;
         store_out(a.out, a.out_dtype, (size_t)head * D + b * 32 + lane, acc);
