@@ -400,6 +400,43 @@ def run_whole_vector(args):
                       "rows": rows}))
 
 
+def run_chunk(args):
+    """Secondary report (not the contract line): causal prefill-chunk attention over the packed cache
+    (tqb_chunk_attention), Llama-3-8B head geometry, PQO4, bf16 queries; CUDA-event times."""
+    import numpy as np
+    import torch
+    import turboquant_b200 as tq
+    peak = peaks()[0]
+    dev, hkv, hq, d, bits = "cuda", 8, 32, 128, 4
+    rows = []
+    for past, q_len in ((8192 - 128, 128), (8192 - 512, 512), (32768 - 256, 256), (0, 512)):
+        n = past + q_len
+        k = torch.randn((hkv * n, d), device=dev, dtype=torch.bfloat16)
+        v = torch.randn_like(k)
+        ki, ks = tq.block_quantize(k, bits)
+        vi, vs = tq.block_quantize(v, bits)
+        ki, ks, vi, vs = (t.view(hkv, n, -1) for t in (ki, ks, vi, vs))
+        q = (torch.randn((q_len, hq, d), device=dev) / d ** 0.5).bfloat16()
+        ts = []
+        for _ in range(args.warmup + args.steps):
+            e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
+            e0.record()
+            tq.chunk_attention(q, ki, ks, vi, vs, n, bits, 1.0 / d ** 0.5)
+            e1.record()
+            e1.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        ms = float(np.median(ts[args.warmup:]))
+        attended = sum(past + i + 1 for i in range(q_len))          # (query token, key token) pairs per KV head group
+        rows.append({"past_tokens": past, "q_len": q_len, "ms": round(ms, 4),
+                     "cache_MB": round(n * hkv * bytes_per_token_head() / 1e6, 1),
+                     "attended_GB/s": round(attended * hkv * bytes_per_token_head() / ms / 1e6, 1),
+                     "attended_frac_of_measured_hbm_peak": round(attended * hkv * bytes_per_token_head() / ms / 1e6 / peak, 3),
+                     "attention_TFLOP/s": round(attended * hq * d * 4 / ms / 1e9, 1)})
+    print(json.dumps({"report": "prefill-chunk attention over the packed cache", "heads": [hq, hkv], "format": "PQO4",
+                      "note": "the cache is re-read once per query token, mostly from L2; attended bytes = what one decode "
+                              "step per query token would stream", "rows": rows}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -415,7 +452,12 @@ def main():
     ap.add_argument("--whole-vector", action="store_true",
                     help="secondary report: the whole-vector (core crate) kernels, 2^19 vectors / 2^21 keys of d = 128 "
                          "(0.3 GB on the device); also the small case for profiler captures of those kernels")
+    ap.add_argument("--chunk", action="store_true",
+                    help="secondary report: causal prefill-chunk attention over the packed cache (tqb_chunk_attention)")
     args = ap.parse_args()
+    if args.chunk:
+        run_chunk(args)
+        return
     if args.whole_vector:
         run_whole_vector(args)
         return
