@@ -275,7 +275,7 @@ typedef struct tqb_decode_params {
 #define TQB_DECODE_TICKETS_ZERO 4
 /* flags: stage the packed tiles with the tensor copy engine (TMA: 2-D tiled maps with the 64-byte swizzle for
  * the index arrays, 1-D maps for the scale rows, one 64-token tile per CTA and stage) instead of per-warp
- * cp.async rings.  Same bits; measured 5 % slower on B200, so it is opt-in.  Falls back to cp.async by itself
+ * cp.async rings.  Same bits; measured 5 to 13 % slower on B200, so it is opt-in.  Falls back to cp.async by itself
  * when kv_stride is odd or a cache array is not 16-byte aligned. */
 #define TQB_DECODE_TMA 8
 
