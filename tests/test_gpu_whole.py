@@ -218,3 +218,20 @@ def test_estimate_inner_product_single_block():
     p, s, sg, rn = o.qjl_quantize_batch(3, 128, 42, 777, x[None])
     want = o.attention_scores(3, 128, 42, 777, q, p, s, sg, rn)[0]
     assert abs(tq.estimate_inner_product(q, rq, blk, cfg) - want) < 1e-4
+
+
+def test_unaligned_input_takes_the_warp_tile_kernel_with_the_same_bits():
+    # the lane-layout batch kernel wants 16-byte aligned rows; a 4-byte aligned view falls back to the
+    # warp-per-tile kernel, and both must agree with the oracle
+    n = 300
+    x = np.random.default_rng(5).standard_normal((n, 128)).astype(np.float32)
+    buf = torch.zeros(n * 128 + 1, device="cuda")
+    buf[1:] = torch.from_numpy(x).reshape(-1).cuda()
+    view = buf[1:].view(n, 128)
+    assert view.data_ptr() % 16 == 4
+    for bits in (2, 3, 4):
+        cfg = tq.TurboQuantConfig(bits, 128).with_seed(42)
+        op, os_ = o.quantize_batch(bits, 128, 42, x, nthreads=4)
+        for inp in (view, dev(x)):
+            p, s = tq.quantize_batch(cfg, inp)
+            assert np.array_equal(p.cpu().numpy(), op) and np.array_equal(u16(s), os_)
