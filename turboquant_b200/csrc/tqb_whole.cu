@@ -718,14 +718,32 @@ scores_table_kernel(const float* __restrict__ q, const float* __restrict__ rq, c
     for (long long i0 = wid * (kU * KPW); i0 < n; i0 += nw * (kU * KPW)) {
         uint32_t w[kU][PB], sw[kU];
         float sc[kU], rn[kU];
+        if (i0 + kU * KPW <= n) {
+            // full step: one base address per array, every key of the step at a compile-time offset from it
+            constexpr int PBW = D * PB / 32;   // packed words per key (pb == 4 * PBW)
+            const long long ib = i0 + kin;
+            const uint32_t* pw = reinterpret_cast<const uint32_t*>(packed) + ib * PBW + sub * PB;
+            const uint32_t* pg = reinterpret_cast<const uint32_t*>(signs) + ib * EPL + sub;
+            const uint16_t* pc = scales + ib;
+            const uint16_t* pr = rnorms + ib;
 #pragma unroll
-        for (int u = 0; u < kU; ++u) {
-            long long i = i0 + u * KPW + kin;
-            if (i >= n) i = n - 1;
-            load_words<PB>(packed, i, pb, sub, w[u]);
-            sw[u] = __ldg(reinterpret_cast<const uint32_t*>(signs + i * (D / 8)) + sub);
-            sc[u] = f16_bits_to_f32(__ldg(scales + i));
-            rn[u] = f16_bits_to_f32(__ldg(rnorms + i));
+            for (int u = 0; u < kU; ++u) {
+#pragma unroll
+                for (int k = 0; k < PB; ++k) w[u][k] = __ldg(pw + u * KPW * PBW + k);
+                sw[u] = __ldg(pg + u * KPW * EPL);
+                sc[u] = f16_bits_to_f32(__ldg(pc + u * KPW));
+                rn[u] = f16_bits_to_f32(__ldg(pr + u * KPW));
+            }
+        } else {
+#pragma unroll
+            for (int u = 0; u < kU; ++u) {
+                long long i = i0 + u * KPW + kin;
+                if (i >= n) i = n - 1;
+                load_words<PB>(packed, i, pb, sub, w[u]);
+                sw[u] = __ldg(reinterpret_cast<const uint32_t*>(signs + i * (D / 8)) + sub);
+                sc[u] = f16_bits_to_f32(__ldg(scales + i));
+                rn[u] = f16_bits_to_f32(__ldg(rnorms + i));
+            }
         }
 #pragma unroll
         for (int u = 0; u < kU; ++u) {
