@@ -307,13 +307,17 @@ int tqb_chunk_attention(const tqb_decode_params *p, int32_t q_len, tqb_stream_t 
  * partials go into a fixed 8 MiB array inside the library image (held by every GPU that loads the
  * library, until exit), and the call performs no allocation of any kind.
  *   - p->scratch and p->scratch_bytes are ignored; inputs and outputs are still the caller's.
+ *     TQB_DECODE_PARTIALS_ONLY is refused (TQB_ERR_INVALID_ARGUMENT): the partials would be left in an array
+ *     the caller cannot address.
  *   - Shapes whose partials need more than tqb_decode_static_scratch_capacity() bytes
  *     (tqb_decode_scratch_bytes(num_q_heads, head_dim, partitions)) are refused with TQB_ERR_TOO_LARGE.
  *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress with
  *     that device current); make that first call before starting any stream capture.
- *   - All calls on a device share the one array and it keeps the previous call's contents; the kernels
- *     overwrite every slot they later read, so nothing needs clearing, but two calls that overlap on
- *     the GPU (different streams, no ordering) race on it.  Order them on one stream or with events. */
+ *   - All calls on a device share the one array and it keeps the previous call's contents.  Every call
+ *     clears the merge tickets at its start on the stream (TQB_DECODE_TICKETS_ZERO is ignored) and the
+ *     kernels overwrite every partial slot they later read, so the caller clears nothing; but two calls
+ *     that overlap on the GPU (different streams, no ordering) race on the array.  Order them on one
+ *     stream or with events. */
 size_t tqb_decode_static_scratch_capacity(void);
 int tqb_decode_attention_static(const tqb_decode_params *p, tqb_stream_t stream);
 

@@ -7,11 +7,14 @@
 //
 // Parity status: the reference's own Rust code cannot be built without a Rust toolchain,
 // so this restatement is pinned against (a) the reference's host-compilable header
-// `src/cache/cuda/kernels/tq_common.h` (bit packing, sign pattern, Rademacher hash) and
-// (b) the known-answer facts asserted by the reference's tests (see tests/).  Two items
-// stay "parity unpinned" because their arithmetic lives in the un-vendored `candle-core`
-// dependency: the summation order of the block-32 forward rotation (a matmul in the
-// reference, a butterfly here) and softmax/SDPA for the non-fused path.
+// `src/cache/cuda/kernels/tq_common.h` (bit packing, sign pattern, Rademacher hash), (b) the
+// reference's own block-32 quantize and dequantize CUDA kernels (tq_quant_kernel.cu:204-262,
+// tq_dequant_kernel.cu:38-98), compiled from the reference checkout and run on the GPU beside
+// this file's block_quantize_one / block_dequantize_one on the same rotated blocks, and (c) the
+// known-answer facts asserted by the reference's tests (see tests/).  Two items stay "parity
+// unpinned" because their arithmetic lives in the un-vendored `candle-core` dependency: the
+// summation order of the block-32 forward rotation (a matmul in the reference, a butterfly
+// here) and softmax/SDPA for the non-fused path.
 //
 // Build: g++ -O3 -march=native -ffp-contract=off -shared -fPIC (see Makefile).
 // -ffp-contract=off matters: Rust never fuses a*b+c, so neither may this file.
@@ -332,6 +335,13 @@ bool make_block_cfg(BlockCfg& c, int bits, int head_dim, int norm_mode, int outl
 // (scale = max(amax / outer_centroid, 1e-10); scaled = rotated / scale).
 // The first `outlier_blocks` blocks of each vector use the outlier codebook and store a
 // negated scale (src/cache/precomputed/mod.rs:103-115).
+// Mixed configurations (0 < outlier_blocks < num_blocks) are ORACLE-DEFINED, not reference-pinned: the
+// reference contradicts itself there.  Its scale signs mark the first `outlier_blocks` blocks of EACH vector
+// (precomputed/mod.rs:102-114), but bucketize_blocks (quantize_tensor.rs:118-158) gives the outlier codebook
+// to the first n * outlier_blocks ROWS of the flattened [n * num_blocks, 32] tensor, i.e. to whole leading
+// vectors when n > 1.  This restatement follows the per-vector reading for both, the only one under which
+// dequantize (which goes by the sign of the scale) inverts quantize.  The two documented modes, all blocks
+// (PQO) and none (PQ / TQ), are unaffected.
 void block_quantize_one(const BlockCfg& c, const float* x, uint8_t* packed, uint16_t* scales) {
     std::vector<uint8_t> idx(c.head_dim);
     for (int b = 0; b < c.nblk; ++b) {
@@ -604,6 +614,13 @@ int tqo_block_codebook(int cb_bits, int norm_mode, float* centroids, float* boun
     return cb.n;
 }
 void tqo_block_signs(float* out) { std::copy(kBlockSigns, kBlockSigns + 32, out); }
+
+// The forward rotation alone (normalize_and_rotate of the MaxNorm branch, src/cache/quantize_tensor.rs:104):
+// n_blocks 32-blocks in, their rotated values out.  This is what the reference hands to its
+// tq_quant_maxnorm_batch launcher (src/cache/cuda/quantize.rs:111-127).
+void tqo_block_rotate(const float* x, int64_t n_blocks, float* out) {
+    for (int64_t i = 0; i < n_blocks; ++i) rotate_block_fwd(x + i * kBlock, out + i * kBlock);
+}
 
 int tqo_block_quantize(int bits, int head_dim, int norm_mode, int outlier_blocks, const float* x, int64_t n,
                        uint8_t* packed, uint16_t* scales, int nthreads) {

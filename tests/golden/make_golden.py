@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Generates the golden fixtures in this directory.
 
-Two sources:
+Three sources:
   * ref_primitives.npz -- outputs of the REFERENCE's own code: its host-compilable header
     src/cache/cuda/kernels/tq_common.h, compiled by `make -C oracle ref` into
     oracle/_ref/libtqref.so (bit packing for 2/3/4 bits, the parity sign pattern, the
@@ -10,8 +10,13 @@ Two sources:
   * oracle_cases.npz -- outputs of the CPU oracle (oracle/liboracle.so) on small seeded
     inputs, so the CUDA path can be compared against committed numbers and so that an
     accidental change of the oracle shows up as a diff.
+  * ref_cuda_block.npz -- outputs of the REFERENCE's own block-32 CUDA kernels
+    (tq_quant_maxnorm_kernel, tq_dequant_kernel; compiled from the reference checkout by
+    `make -C oracle refcuda`, see tests/ref_cuda.py) on small seeded inputs.  Needs a GPU and the
+    compiled kernels: `python tests/golden/make_golden.py --ref-cuda <output.npz>`; the file is then
+    copied here.  It pins the oracle's Format-B quantize / dequantize on machines without a GPU.
 
-Usage: python tests/golden/make_golden.py
+Usage: python tests/golden/make_golden.py [--ref-cuda <output.npz>]
 """
 import ctypes
 import os
@@ -107,7 +112,34 @@ def oracle_cases():
     np.savez_compressed(os.path.join(HERE, "oracle_cases.npz"), **out)
 
 
+def ref_cuda_block(path):
+    """Runs the reference's quantize and dequantize kernels (IEEE build and the --use_fast_math build the
+    reference ships) on 128 vectors of each synthetic K/V style; the rotated input is the oracle's."""
+    import ref_cuda
+    out = {}
+    for style in ref_cuda_styles():
+        x = ref_cuda.synthetic_kv(style, 128, 31)
+        rot = o.block_rotate(x)
+        out[f"x_{style}"] = x
+        out[f"rot_{style}"] = rot
+        for bits in (3, 4):
+            for variant in ("ieee", "fastmath"):
+                p, s = ref_cuda.quant_maxnorm(rot, bits, variant)
+                out[f"packed_{style}_{bits}_{variant}"], out[f"scales_{style}_{bits}_{variant}"] = p, s
+            p, s = out[f"packed_{style}_{bits}_ieee"], out[f"scales_{style}_{bits}_ieee"]
+            for variant in ("ieee", "fastmath"):
+                out[f"deq_{style}_{bits}_{variant}"] = ref_cuda.dequant(p, s, bits, variant)
+    np.savez_compressed(path, **out)
+
+
+def ref_cuda_styles():
+    return ("outlier", "lognormal")
+
+
 if __name__ == "__main__":
+    if len(sys.argv) == 3 and sys.argv[1] == "--ref-cuda":
+        ref_cuda_block(sys.argv[2])
+        sys.exit(0)
     if os.path.exists(os.path.join(o.ORACLE_DIR, "_ref", "libtqref.so")):
         ref_primitives()
     else:

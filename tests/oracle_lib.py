@@ -197,6 +197,14 @@ def block_signs():
     return out
 
 
+def block_rotate(x):
+    """Forward rotation of 32-blocks (the input the reference hands to tq_quant_maxnorm_batch)."""
+    x = np.ascontiguousarray(x, np.float32).reshape(-1, 32)
+    out = np.zeros_like(x)
+    _o.tqo_block_rotate(P(x), i64(len(x)), P(out))
+    return out
+
+
 def _ob(outlier_blocks, head_dim):
     return head_dim // 32 if outlier_blocks < 0 else outlier_blocks
 

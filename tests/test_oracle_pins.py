@@ -3,6 +3,8 @@
 Sources of truth, in order of strength:
   * tests/golden/ref_primitives.npz -- produced by the reference's own header
     src/cache/cuda/kernels/tq_common.h (see tests/golden/make_golden.py);
+  * tests/golden/ref_cuda_block.npz -- produced on a B200 by the reference's own block-32 quantize
+    and dequantize CUDA kernels, compiled from the reference checkout (tests/ref_cuda.py);
   * facts asserted by the reference's test-suite, cited per test;
   * tests/golden/oracle_cases.npz -- the oracle's own committed outputs (regression guard).
 """
@@ -38,6 +40,40 @@ def test_rademacher_matches_reference_header(seed):
     for row in range(0, 128, 5):
         got = np.array([o.rademacher_sign(seed, row, c) for c in range(128)])
         assert np.array_equal(got, m[row].astype(np.float32))
+
+
+# ---- against the reference's own block-32 CUDA kernels (outputs frozen on a B200) ---------
+REFCUDA = np.load(os.path.join(GOLD, "ref_cuda_block.npz"))
+
+
+@pytest.mark.parametrize("style", ["outlier", "lognormal"])
+@pytest.mark.parametrize("bits", [3, 4])
+def test_block_quantize_matches_reference_cuda_kernel(bits, style):
+    # tq_quant_maxnorm_kernel (tq_quant_kernel.cu:204-262) on the oracle's rotated blocks, IEEE build:
+    # packed codes and f16 scales bit for bit
+    x = REFCUDA[f"x_{style}"]
+    assert np.array_equal(o.block_rotate(x), REFCUDA[f"rot_{style}"])
+    packed, scales = o.block_quantize(bits, 128, 0, -1, x)
+    assert np.array_equal(packed.reshape(-1, 4 * bits), REFCUDA[f"packed_{style}_{bits}_ieee"])
+    assert np.array_equal(scales.reshape(-1), REFCUDA[f"scales_{style}_{bits}_ieee"])
+    # the --use_fast_math build the reference ships divides approximately: codes may differ only where a
+    # coordinate sits on a decision boundary (none does in this slice), scales by one f16 ulp
+    fm_codes = o.unpack_indices(bits, REFCUDA[f"packed_{style}_{bits}_fastmath"].reshape(-1), x.size)
+    assert int((fm_codes != o.unpack_indices(bits, packed.reshape(-1), x.size)).sum()) <= 2
+    fm_sc = REFCUDA[f"scales_{style}_{bits}_fastmath"].astype(np.int32)
+    assert np.abs(fm_sc - scales.reshape(-1).astype(np.int32)).max() <= 1
+
+
+@pytest.mark.parametrize("variant", ["ieee", "fastmath"])
+@pytest.mark.parametrize("style", ["outlier", "lognormal"])
+@pytest.mark.parametrize("bits", [3, 4])
+def test_block_dequantize_matches_reference_cuda_kernel(bits, style, variant):
+    # tq_dequant_kernel (tq_dequant_kernel.cu:38-98) multiplies by rsqrtf(32) where the CPU path
+    # (src/cache/wht_tensor.rs:38) multiplies by 1/sqrt(32): equal to 1e-5 relative, not bit for bit
+    packed, scales = REFCUDA[f"packed_{style}_{bits}_ieee"], REFCUDA[f"scales_{style}_{bits}_ieee"]
+    got = o.block_dequantize(bits, 128, 0, -1, packed.reshape(128, -1), scales.reshape(128, 4)).reshape(-1, 32)
+    want = REFCUDA[f"deq_{style}_{bits}_{variant}"]
+    assert float((np.abs(got - want) / np.maximum(np.abs(want), 1e-30)).max()) <= 1e-5
 
 
 # ---- facts asserted by the reference's tests ---------------------------------------------

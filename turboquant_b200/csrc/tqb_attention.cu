@@ -677,6 +677,8 @@ size_t tqb_decode_static_scratch_capacity(void) { return kStaticScratchBytes; }
 int tqb_decode_attention_static(const tqb_decode_params* p, tqb_stream_t stream) {
     if (!p) return TQB_ERR_NULL_POINTER;
     if (p->num_q_heads <= 0 || p->num_kv_heads <= 0 || p->head_dim <= 0) return TQB_ERR_INVALID_ARGUMENT;
+    // the partials would stay in the library's array, whose address the caller cannot obtain
+    if (p->flags & TQB_DECODE_PARTIALS_ONLY) return TQB_ERR_INVALID_ARGUMENT;
     const int P = p->num_partitions > 0 ? p->num_partitions : tqb_decode_num_partitions(p->num_kv_heads, p->kv_len);
     const size_t need = tqb_decode_scratch_bytes(p->num_q_heads, p->head_dim, P);
     if (need == 0 || need > kStaticScratchBytes) return TQB_ERR_TOO_LARGE;   // refuse, never spill past the array

@@ -145,25 +145,33 @@ struct tqb_pqo_cache {
             free_layer(nl);
             return cuda_fail(e);
         }
-        TQB_CUDA(cudaMemsetAsync(nl.ki, 0, ib, s));
-        TQB_CUDA(cudaMemsetAsync(nl.vi, 0, ib, s));
-        TQB_CUDA(cudaMemsetAsync(nl.ks, 0, sb, s));
-        TQB_CUDA(cudaMemsetAsync(nl.vs, 0, sb, s));
-        if (l.len > 0) {
-            const size_t iw = (size_t)l.len * packed_dim, sw = (size_t)l.len * nblk * 2;
-            TQB_CUDA(cudaMemcpy2DAsync(nl.ki, (size_t)new_cap * packed_dim, l.ki, (size_t)l.cap * packed_dim, iw, heads,
-                                       cudaMemcpyDeviceToDevice, s));
-            TQB_CUDA(cudaMemcpy2DAsync(nl.vi, (size_t)new_cap * packed_dim, l.vi, (size_t)l.cap * packed_dim, iw, heads,
-                                       cudaMemcpyDeviceToDevice, s));
-            TQB_CUDA(cudaMemcpy2DAsync(nl.ks, (size_t)new_cap * nblk * 2, l.ks, (size_t)l.cap * nblk * 2, sw, heads,
-                                       cudaMemcpyDeviceToDevice, s));
-            TQB_CUDA(cudaMemcpy2DAsync(nl.vs, (size_t)new_cap * nblk * 2, l.vs, (size_t)l.cap * nblk * 2, sw, heads,
-                                       cudaMemcpyDeviceToDevice, s));
+        // on any failure from here on the new buffers are released and the layer is left as it was
+        auto fill = [&]() -> cudaError_t {
+            cudaError_t r;
+            if ((r = cudaMemsetAsync(nl.ki, 0, ib, s)) != cudaSuccess) return r;
+            if ((r = cudaMemsetAsync(nl.vi, 0, ib, s)) != cudaSuccess) return r;
+            if ((r = cudaMemsetAsync(nl.ks, 0, sb, s)) != cudaSuccess) return r;
+            if ((r = cudaMemsetAsync(nl.vs, 0, sb, s)) != cudaSuccess) return r;
+            if (l.len > 0) {
+                const size_t iw = (size_t)l.len * packed_dim, sw = (size_t)l.len * nblk * 2;
+                if ((r = cudaMemcpy2DAsync(nl.ki, (size_t)new_cap * packed_dim, l.ki, (size_t)l.cap * packed_dim, iw, heads,
+                                           cudaMemcpyDeviceToDevice, s)) != cudaSuccess) return r;
+                if ((r = cudaMemcpy2DAsync(nl.vi, (size_t)new_cap * packed_dim, l.vi, (size_t)l.cap * packed_dim, iw, heads,
+                                           cudaMemcpyDeviceToDevice, s)) != cudaSuccess) return r;
+                if ((r = cudaMemcpy2DAsync(nl.ks, (size_t)new_cap * nblk * 2, l.ks, (size_t)l.cap * nblk * 2, sw, heads,
+                                           cudaMemcpyDeviceToDevice, s)) != cudaSuccess) return r;
+                if ((r = cudaMemcpy2DAsync(nl.vs, (size_t)new_cap * nblk * 2, l.vs, (size_t)l.cap * nblk * 2, sw, heads,
+                                           cudaMemcpyDeviceToDevice, s)) != cudaSuccess) return r;
+            }
+            // the old buffers may still be read by queued work, and the copies above must have left them
+            return l.ki ? cudaStreamSynchronize(s) : cudaSuccess;
+        };
+        if ((e = fill()) != cudaSuccess) {
+            cudaStreamSynchronize(s);   // nothing queued may still write the buffers that are released next
+            free_layer(nl);
+            return cuda_fail(e);
         }
-        if (l.ki) {
-            TQB_CUDA(cudaStreamSynchronize(s));  // the old buffers may still be read by queued work
-            free_layer(l);
-        }
+        if (l.ki) free_layer(l);
         l = nl;
         return TQB_OK;
     }
@@ -212,11 +220,17 @@ struct tqb_pqo_cache {
     int append_and_attend(int layer, const void* k_dev, const void* v_dev, const void* q_dev, int dtype, int num_q_heads,
                           float softmax_scale, void* out_dev, cudaStream_t s) {
         const int64_t old_len = layers[layer].len;
+        const bool was_active = layers[layer].active;
         TQB_TRY(ensure_capacity(layer, old_len + 1, s));
         Layer& l = layers[layer];
-        l.len = old_len + 1;
+        l.len = old_len + 1;   // the attention call counts the new token
         l.active = true;
-        return attend(layer, q_dev, dtype, num_q_heads, softmax_scale, out_dev, dtype, nullptr, s, k_dev, v_dev);
+        const int st = attend(layer, q_dev, dtype, num_q_heads, softmax_scale, out_dev, dtype, nullptr, s, k_dev, v_dev);
+        if (st != TQB_OK) {    // nothing was launched: the row was never written, so the token is not kept
+            l.len = old_len;
+            l.active = was_active;
+        }
+        return st;
     }
 
     int attend(int layer, const void* q_dev, int dtype, int num_q_heads, float softmax_scale, void* out_dev, int out_dtype,
@@ -781,18 +795,24 @@ struct tqb_tq_cache {
             free_q(n);
             return cuda_fail(e);
         }
-        TQB_CUDA(cudaMemsetAsync(n.signs, 0, (size_t)heads * new_cap * sb(), s));
-        TQB_CUDA(cudaMemsetAsync(n.norms, 0, (size_t)heads * new_cap * 2, s));
-        if (old_len > 0 && q.signs) {
-            TQB_CUDA(cudaMemcpy2DAsync(n.signs, (size_t)new_cap * sb(), q.signs, (size_t)q.cap * sb(), (size_t)old_len * sb(),
-                                       heads, cudaMemcpyDeviceToDevice, s));
-            TQB_CUDA(cudaMemcpy2DAsync(n.norms, (size_t)new_cap * 2, q.norms, (size_t)q.cap * 2, (size_t)old_len * 2, heads,
-                                       cudaMemcpyDeviceToDevice, s));
+        auto fill = [&]() -> cudaError_t {
+            cudaError_t r;
+            if ((r = cudaMemsetAsync(n.signs, 0, (size_t)heads * new_cap * sb(), s)) != cudaSuccess) return r;
+            if ((r = cudaMemsetAsync(n.norms, 0, (size_t)heads * new_cap * 2, s)) != cudaSuccess) return r;
+            if (old_len > 0 && q.signs) {
+                if ((r = cudaMemcpy2DAsync(n.signs, (size_t)new_cap * sb(), q.signs, (size_t)q.cap * sb(), (size_t)old_len * sb(),
+                                           heads, cudaMemcpyDeviceToDevice, s)) != cudaSuccess) return r;
+                if ((r = cudaMemcpy2DAsync(n.norms, (size_t)new_cap * 2, q.norms, (size_t)q.cap * 2, (size_t)old_len * 2, heads,
+                                           cudaMemcpyDeviceToDevice, s)) != cudaSuccess) return r;
+            }
+            return q.signs ? cudaStreamSynchronize(s) : cudaSuccess;
+        };
+        if ((e = fill()) != cudaSuccess) {
+            cudaStreamSynchronize(s);
+            free_q(n);
+            return cuda_fail(e);
         }
-        if (q.signs) {
-            TQB_CUDA(cudaStreamSynchronize(s));
-            free_q(q);
-        }
+        if (q.signs) free_q(q);
         q = n;
         return TQB_OK;
     }
@@ -800,16 +820,24 @@ struct tqb_tq_cache {
     // quantize_and_store + compute_and_store_qjl (src/cache/tq.rs:99-183)
     int store(int layer, const void* k, const void* v, int dtype, int new_tokens, cudaStream_t s) {
         const int64_t old_len = base->layers[layer].len;
-        TQB_TRY(base->quantize_and_store(layer, k, v, dtype, new_tokens, s));
-        TQB_TRY(ensure_qjl_capacity(layer, old_len + new_tokens, old_len, s));
-        auto& L = base->layers[layer];
+        const bool was_active = base->layers[layer].active;
         const auto& cfg = base->cfg;
         const int64_t rows = (int64_t)base->heads * new_tokens;
+        // everything that can fail for lack of memory comes before the polar length advances
+        TQB_TRY(ensure_qjl_capacity(layer, old_len + new_tokens, old_len, s));
         TQB_TRY(deq.reserve((size_t)rows * cfg.head_dim * sizeof(float)));
-        TQB_TRY(tqb_block_dequantize(cfg.bits, cfg.head_dim, cfg.norm_mode, cfg.outlier_blocks, L.ki, L.ks, rows, new_tokens,
-                                     L.cap, old_len, deq.p, TQB_F32, s));
-        return tqb_residual_sketch(cfg.head_dim, rbits, k, dtype, (const float*)deq.p, rows, qjl[layer].signs,
-                                   qjl[layer].norms, new_tokens, qjl[layer].cap, old_len, s);
+        TQB_TRY(base->quantize_and_store(layer, k, v, dtype, new_tokens, s));
+        auto& L = base->layers[layer];
+        int st = tqb_block_dequantize(cfg.bits, cfg.head_dim, cfg.norm_mode, cfg.outlier_blocks, L.ki, L.ks, rows, new_tokens,
+                                      L.cap, old_len, deq.p, TQB_F32, s);
+        if (st == TQB_OK)
+            st = tqb_residual_sketch(cfg.head_dim, rbits, k, dtype, (const float*)deq.p, rows, qjl[layer].signs,
+                                     qjl[layer].norms, new_tokens, qjl[layer].cap, old_len, s);
+        if (st != TQB_OK) {   // tokens without a sketch are not kept
+            L.len = old_len;
+            L.active = was_active;
+        }
+        return st;
     }
 
     // compute_logit_bias (src/cache/tq.rs:185-253)
