@@ -377,6 +377,12 @@ size_t tqb_pqo_cache_memory_usage(const tqb_pqo_cache *c);
 /* Device pointers of one layer's storage (k_indices, k_scales, v_indices, v_scales). */
 int tqb_pqo_cache_layer_ptrs(const tqb_pqo_cache *c, int32_t layer, const uint8_t **k_indices,
                              const uint16_t **k_scales, const uint8_t **v_indices, const uint16_t **v_scales);
+/* Dense copy of one layer's stored rows without the capacity padding (the block-32 counterpart of
+ * export_packed_range, src/attention.rs:663-693, which the reference offers for the whole-vector cache only):
+ * k/v_indices [batch * num_kv_heads, seq_len, head_dim*bits/8], k/v_scales [.., seq_len, head_dim/32].
+ * host_buffers != 0: the destinations are host memory and the call returns when they are filled. */
+int tqb_pqo_cache_export_layer(const tqb_pqo_cache *c, int32_t layer, uint8_t *k_indices, uint16_t *k_scales,
+                               uint8_t *v_indices, uint16_t *v_scales, int32_t host_buffers, tqb_stream_t stream);
 /* Sequence-parallel decode: shard-local un-normalised output + (max, sum), no append. */
 int tqb_pqo_cache_attend_partial(tqb_pqo_cache *c, int32_t layer, const void *q, int32_t dtype,
                                  int32_t num_q_heads, float softmax_scale, float *out_unnorm, float *lse_out,

@@ -1,0 +1,99 @@
+"""Parity at the shapes and context lengths the benchmark configurations name, through PqoCache.
+
+Each case fills a cache layer with the batched quantize kernel on synthetic K/V of the configuration's
+distribution, runs one decode step (append + fused attention), and compares with the CPU oracle's decode
+attention over the IDENTICAL packed bytes copied down from the cache (tolerance 2e-3 max-abs, the parity
+contract; the observed maximum is printed).  A strided sample of the stored rows is also compared bit for
+bit with the oracle's own quantization of the same vectors.
+"""
+import numpy as np
+import pytest
+import torch
+
+import oracle_lib as o
+import turboquant_b200 as tq
+import workloads as w
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-3
+OUT_TOL = 1e-2   # with bf16 outputs: rounding of the output type on values of magnitude ~1
+
+
+def _fill_and_decode(shape, layer, ctx, batch=None):
+    cfg = w.SHAPES[shape]
+    b = cfg["batch"] if batch is None else batch
+    dev = torch.device("cuda")
+    cache = tq.PqoCache(tq.CacheConfig(bits=cfg["bits"], head_dim=cfg["head_dim"], num_kv_heads=cfg["hkv"], num_layers=1, batch=b))
+    k, v = w.synth_kv(shape, layer, ctx, dev, batch=b)
+    cache.prefill(0, k[:, :, :ctx - 1].contiguous(), v[:, :, :ctx - 1].contiguous())
+    q = w.synth_q(shape, layer, dev, batch=b)[0].float()    # f32 queries and outputs: no output rounding in the way
+    scale = 1.0 / cfg["head_dim"] ** 0.5
+    out = cache.decode(0, k[:, :, ctx - 1:].float().contiguous(), v[:, :, ctx - 1:].float().contiguous(), q,
+                       tq.AttendConfig(scale, cfg["hq"] // cfg["hkv"])).fused
+    return cache, k, v, q, out, scale
+
+
+def _check_rows(cache, cfg, k, v, stride_rows):
+    """A strided sample of the stored K and V rows equals the oracle's quantization of the same vectors."""
+    ki, ks, vi, vs = (t.numpy() for t in cache.export_layer(0))
+    heads, n = ki.shape[0], ki.shape[1]
+    rows = np.arange(0, heads * n, stride_rows)
+    for src, idx, sc in ((k, ki, ks), (v, vi, vs)):
+        x = src.float().reshape(heads * n, -1)[torch.as_tensor(rows, device=src.device)].cpu().numpy()
+        op, os_ = o.block_quantize(cfg["bits"], cfg["head_dim"], 0, -1, x, nthreads=16)
+        assert np.array_equal(idx.reshape(heads * n, -1)[rows], op)
+        assert np.array_equal(sc.reshape(heads * n, -1)[rows].view(np.uint16), os_)
+
+
+@pytest.mark.parametrize("ctx", [1024, 4096, 32768])
+@pytest.mark.parametrize("layer", [0, 1])
+def test_qwen3_shape_pqo3(ctx, layer):
+    cfg = w.SHAPES["qwen3"]
+    cache, k, v, q, out, scale = _fill_and_decode("qwen3", layer, ctx)
+    assert cache.seq_len(0) == ctx
+    want = w.oracle_decode_of_layer(cache, 0, q, scale)
+    err = float(np.abs(out.cpu().numpy().reshape(-1, 128) - want).max())
+    print(f"\n[qwen3 shape, PQO3, ctx {ctx}, layer {layer}] max-abs error vs oracle {err:.2e}")
+    assert err < TOL
+    _check_rows(cache, cfg, k, v, 97)
+
+
+def test_llama8b_shape_pqo4_batch64_ctx8192():
+    cfg = w.SHAPES["llama8b"]
+    cache, k, v, q, out, scale = _fill_and_decode("llama8b", 0, 8192)
+    want = w.oracle_decode_of_layer(cache, 0, q, scale)
+    err = float(np.abs(out.cpu().numpy().reshape(-1, 128) - want).max())
+    print(f"\n[llama-3-8b shape, PQO4, batch 64 x ctx 8192] max-abs error vs oracle {err:.2e}")
+    assert err < TOL
+    _check_rows(cache, cfg, k, v, 4099)
+    # bf16 queries and outputs, the dtype the benchmark runs in
+    qb = q.to(torch.bfloat16)
+    k1, v1 = w.synth_kv("llama8b", 7, 1, torch.device("cuda"))
+    outb = cache.decode(0, k1, v1, qb, tq.AttendConfig(scale, 4)).fused
+    wantb = w.oracle_decode_of_layer(cache, 0, qb, scale)
+    assert float(np.abs(outb.float().cpu().numpy().reshape(-1, 128) - wantb).max()) < OUT_TOL
+
+
+def test_llama70b_shape_pqo3_ctx131072_unsharded_and_sharded():
+    cfg = w.SHAPES["llama70b"]
+    ctx = 131072
+    cache, k, v, q, out, scale = _fill_and_decode("llama70b", 0, ctx)
+    want = w.oracle_decode_of_layer(cache, 0, q, scale)
+    err = float(np.abs(out.cpu().numpy().reshape(-1, 128) - want).max())
+    print(f"\n[llama-3-70b shape, PQO3, ctx 131072, unsharded] max-abs error vs oracle {err:.2e}")
+    assert err < TOL
+    _check_rows(cache, cfg, k, v, 9973)
+    # the same sequence as 8 token shards: shard-local (out, max, sum), then the log-sum-exp merge
+    shards = 8
+    outs, lses = [], []
+    for r in range(shards):
+        lo, hi = r * ctx // shards, (r + 1) * ctx // shards
+        c = tq.PqoCache(tq.CacheConfig(bits=3, head_dim=128, num_kv_heads=8, num_layers=1))
+        c.prefill(0, k[:, :, lo:hi].contiguous(), v[:, :, lo:hi].contiguous())
+        po, pl = c.attend_partial(0, q, scale)
+        outs.append(po)
+        lses.append(pl)
+    merged = tq.lse_combine(torch.stack(outs), torch.stack(lses)).cpu().numpy()
+    err = float(np.abs(merged - want).max())
+    print(f"[llama-3-70b shape, PQO3, ctx 131072, 8 sequence shards merged] max-abs error vs oracle {err:.2e}")
+    assert err < TOL

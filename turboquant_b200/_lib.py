@@ -104,6 +104,7 @@ def _declare(lib):
         "tqb_pqo_cache_reset": (c_int, [P]),
         "tqb_pqo_cache_memory_usage": (S, [P]),
         "tqb_pqo_cache_layer_ptrs": (c_int, [P, I, P, P, P, P]),
+        "tqb_pqo_cache_export_layer": (c_int, [P, I, P, P, P, P, I, P]),
         "tqb_pqo_cache_attend_partial": (c_int, [P, I, P, I, I, F, P, P, P]),
         "tqb_residual_sketch": (c_int, [I, P, P, I, P, L, P, P, L, L, L, P]),
         "tqb_qjl_logit_bias": (c_int, [I, P, P, P, P, I, I, I, I, I, I, P]),

@@ -708,6 +708,17 @@ class PqoCache:
     def memory_usage(self):
         return int(lib.tqb_pqo_cache_memory_usage(self._h))
 
+    def export_layer(self, layer, host=True):
+        """The layer's stored rows without capacity padding: (k_indices, k_scales, v_indices, v_scales) with
+        indices [batch * Hkv, seq_len, packed_dim] u8 and scales [batch * Hkv, seq_len, head_dim / 32] i16 (f16 bits)."""
+        n, heads = self.seq_len(layer), self.config.batch * self.config.num_kv_heads
+        dev = "cpu" if host else _dev()
+        pd, nb = self.config.head_dim * self.config.bits // 8, self.config.head_dim // 32
+        ki, vi = (torch.empty((heads, n, pd), dtype=torch.uint8, device=dev) for _ in range(2))
+        ks, vs = (torch.empty((heads, n, nb), dtype=torch.int16, device=dev) for _ in range(2))
+        check(lib.tqb_pqo_cache_export_layer(self._h, layer, _ptr(ki), _ptr(ks), _ptr(vi), _ptr(vs), 1 if host else 0, _stream()))
+        return ki, ks, vi, vs
+
     def layer_ptrs(self, layer):
         ptrs = [ctypes.c_void_p() for _ in range(4)]
         check(lib.tqb_pqo_cache_layer_ptrs(self._h, layer, *[ctypes.byref(p) for p in ptrs]))

@@ -13,7 +13,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libtqb200.so")
 
 NVCC_FLAGS = [
-    "-O3", "-std=c++17", "-lineinfo",
+    "-O3", "-std=c++17", "-lineinfo", "--threads", "0",
     "-gencode", "arch=compute_100a,code=sm_100a",
     # The bit-exact paths must round a*b+c twice, like the reference's scalar code;
     # kernels that want a fused multiply-add call fmaf() explicitly.

@@ -36,6 +36,7 @@
 #include <float.h>
 #include <string.h>
 
+#include <atomic>
 #include <mutex>
 #include <type_traits>
 
@@ -93,6 +94,14 @@ __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// m16n8k32, signed 8-bit operands, 32-bit integer result; the addend is zero (a fresh accumulator per call).
+__device__ __forceinline__ void imma16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                          uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
 
 __device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t b, uint32_t c) {
@@ -396,6 +405,7 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
     __shared__ __align__(8) unsigned long long s_bar[2][kStages];   // TMA staging: full / empty barriers of the stages
     __shared__ float s_q[8 * kD];   // rotated queries (prologue only)
     __shared__ __align__(16) uint4 s_qfr[8][32];   // MMA fragments of the rotated queries, [operand set * 4 + block][lane]
+    __shared__ float s_qinv[8], s_qsc[8];          // 4-bit: per head, rotated query -> 20-bit integer and back (see below)
     const uint32_t dyn_base = (uint32_t)__cvta_generic_to_shared(s_dyn);
     const uint32_t lut_base = BITS == 3 ? ((dyn_base + 8191u) & ~8191u) : 0u;
     const uint32_t rings_base = BITS == 3 ? lut_base + 8192u : ((dyn_base + 1023u) & ~1023u);
@@ -537,14 +547,62 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
         }
     }
     __syncthreads();
-    // Scores are computed as S = K~ Q~^T: the A operand is the unpacked K tile (M = 16 tokens, K = 16 dims of
-    // one block), the B operand holds the rotated queries (N = 8 columns).  NSPLIT (group <= 4): columns 2h and
-    // 2h + 1 are the f16 hi and lo parts of q~ of head h, so one MMA gives the split-precision product and
-    // both parts of a head land in the same lane; else two operand sets (hi, lo) of 8 heads.  For block b and half m the k-slots
-    // (2j, 2j+1 | 2j+8, 2j+9) hold the dims that the code unpackers deliver:
-    //   4-bit: 32b + 8j + 2m + (0, 4 | 1, 5)      3-bit: 32b + 8j + 4m + (0, 1 | 2, 3)
-    // s_qfr[set * 4 + b][lane] = (b0, b1 of half 0, b0, b1 of half 1) of the lane's column n.
-    {
+    // Scores are computed as S = K~ Q~^T: the A operand is the unpacked K tile (M = 16 tokens of one block), the B
+    // operand holds the rotated queries (N = 8 columns).
+    // 3-bit (f16 MMA, K = 16 dims): NSPLIT (group <= 4): columns 2h and 2h + 1 are the f16 hi and lo parts of q~ of
+    // head h, so one MMA gives the split-precision product and both parts of a head land in the same lane; else two
+    // operand sets (hi, lo) of 8 heads.  For block b and half m the k-slots (2j, 2j+1 | 2j+8, 2j+9) hold the dims
+    // 32b + 8j + 4m + (0, 1 | 2, 3) that the code unpacker delivers; s_qfr[set * 4 + b][lane] = (b0, b1 of half 0,
+    // b0, b1 of half 1) of the lane's column n.
+    // 4-bit (integer MMA, K = 32 dims = the whole block): k-slots 4j .. 4j+3 hold dims 32b + 8j + (0, 2, 4, 6) (the even
+    // nibbles of word j), k-slots 16 + 4j .. hold dims 32b + 8j + (1, 3, 5, 7) (the odd nibbles).
+    if (BITS == 4) {
+        // 4-bit: the scores run on the integer tensor-core path (mma.sync m16n8k32, s8 x s8 -> s32).  A code c enters
+        // as the byte 16 (c - 7.5) (two logic operations per four codes, see the token loop); the rotated query of a
+        // head enters as a 20-bit integer v = round(q~ 2^19 / max |q~|) split into three balanced base-256 digits
+        // v = 65536 D2 + 256 D1 + D0, one MMA column per digit.  All integer arithmetic is exact, |sum| < 2^31 (32 dims
+        // x 120 x 2^19), and q~ is represented to 2^-20 of the head's largest component.
+        for (int hh = warp; hh < 8; hh += kWarps) {
+            float m = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) m = fmaxf(m, fabsf(s_q[hh * kD + lane + 32 * i]));
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+            if (lane == 0) {
+                const bool ok = m > 0.0f && m < 3.0e38f;
+                s_qinv[hh] = ok ? 524287.0f / m : 0.0f;
+                s_qsc[hh] = ok ? m / (524287.0f * 16.0f) : 0.0f;
+            }
+        }
+        __syncthreads();
+        const int b = warp;   // one block per warp
+        const int head = NSPLIT ? (n >> 1) : n;
+        const float* sq = s_q + head * kD;
+        const float inv = s_qinv[head];
+        uint32_t dg[3][2] = {{0u, 0u}, {0u, 0u}, {0u, 0u}};   // [digit 0 = D0 (low)][k half: dims 8j + even | 8j + odd]
+#pragma unroll
+        for (int half = 0; half < 2; ++half)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int v = __float2int_rn(sq[32 * b + 8 * j + 2 * i + half] * inv);
+                const int d0 = (int)(signed char)(v & 0xFF);
+                const int v1 = (v - d0) >> 8;
+                const int d1 = (int)(signed char)(v1 & 0xFF);
+                const int d2 = (v1 - d1) >> 8;
+                dg[0][half] |= (uint32_t)(d0 & 0xFF) << (8 * i);
+                dg[1][half] |= (uint32_t)(d1 & 0xFF) << (8 * i);
+                dg[2][half] |= (uint32_t)(d2 & 0xFF) << (8 * i);
+            }
+        if (NSPLIT) {
+            // columns 2h, 2h + 1 of the first MMA: digits D2, D1 of head h; of the second MMA: D0 and an empty column
+            const bool odd = n & 1;
+            s_qfr[b][lane] = make_uint4(odd ? dg[1][0] : dg[2][0], odd ? dg[1][1] : dg[2][1], odd ? 0u : dg[0][0], odd ? 0u : dg[0][1]);
+        } else {
+            // column h of three MMAs: digits D2, D1, D0 of head h
+            s_qfr[b][lane] = make_uint4(dg[2][0], dg[2][1], dg[1][0], dg[1][1]);
+            s_qfr[4 + b][lane] = make_uint4(dg[0][0], dg[0][1], 0u, 0u);
+        }
+    } else {
         const float* sq = s_q + (NSPLIT ? (n >> 1) : n) * kD;
         const int b = warp;   // one block per warp
 #pragma unroll
@@ -553,9 +611,9 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
             uint32_t r[4];
 #pragma unroll
             for (int m = 0; m < 2; ++m) {
-                const int d0 = 32 * b + 8 * j + (BITS == 4 ? 2 * m : 4 * m);
-                const float qa = sq[d0], qb = sq[d0 + (BITS == 4 ? 4 : 1)];
-                const float qc = sq[d0 + (BITS == 4 ? 1 : 2)], qd = sq[d0 + (BITS == 4 ? 5 : 3)];
+                const int d0 = 32 * b + 8 * j + 4 * m;
+                const float qa = sq[d0], qb = sq[d0 + 1];
+                const float qc = sq[d0 + 2], qd = sq[d0 + 3];
                 r[2 * m] = lo_part ? pack_lo(qa, qb) : pack_hi(qa, qb);
                 r[2 * m + 1] = lo_part ? pack_lo(qc, qd) : pack_hi(qc, qd);
             }
@@ -567,6 +625,9 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
     // After the scores, lane (n, j) holds tokens n and n + 8 of the step and kE heads:
     //   NSPLIT: head j (its hi and lo columns 2j, 2j+1 are summed in the lane)  |  otherwise heads 2j, 2j+1.
     constexpr int kE = NSPLIT ? 1 : 2;
+    float qsc[kE];                // 4-bit: integer score -> log2-domain score of the lane's head(s)
+#pragma unroll
+    for (int e = 0; e < kE; ++e) qsc[e] = BITS == 4 ? s_qsc[NSPLIT ? j : 2 * j + e] : 1.0f;
     float m_run[kE], l_run[kE];   // per head; l_run: this lane's tokens only
 #pragma unroll
     for (int e = 0; e < kE; ++e) {
@@ -623,51 +684,73 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
             const uint2 sca = lds64_o<0>(bS), scb = lds64_o<64>(bS);   // scale rows of the two tokens
             static_for<0, 4>([&](auto b_) {
                 constexpr int b = decltype(b_)::value;
-                uint32_t x[2][4];   // [token n | n + 8]: codes 8j..8j+7 of block b as four half2
-                static_for<0, 2>([&](auto t_) {
-                    constexpr int t = decltype(t_)::value;
-                    if (BITS == 4) {
-                        nibbles_to_half2(kw[b >> 1][t + 2 * (b & 1)], x[t]);
-                    } else {
+                const __half2 pa = u32_as_h2(b < 2 ? sca.x : sca.y), pb = u32_as_h2(b < 2 ? scb.x : scb.y);
+                const float ka = fabsf((b & 1) ? __high2float(pa) : __low2float(pa));
+                const float kb = fabsf((b & 1) ? __high2float(pb) : __low2float(pb));
+                if constexpr (BITS == 4) {
+                    // Codes -> signed bytes 16 (c - 7.5) = 8 (2c - 15): flip the top bit of every nibble (c ^ 8 is the
+                    // 4-bit two's complement of c - 8), move the nibble to the top of a byte and set bit 3 below it.
+                    // Even nibbles (dims 8j + 0, 2, 4, 6) fill k-slots 4j .. 4j+3, odd nibbles k-slots 16 + 4j ..
+                    const uint32_t u0 = kw[b >> 1][2 * (b & 1)] ^ 0x88888888u;        // token n
+                    const uint32_t u1 = kw[b >> 1][2 * (b & 1) + 1] ^ 0x88888888u;    // token n + 8
+                    const uint32_t a0 = lop3_and_or(u0 << 4, 0xF0F0F0F0u, 0x08080808u), a2 = lop3_and_or(u0, 0xF0F0F0F0u, 0x08080808u);
+                    const uint32_t a1 = lop3_and_or(u1 << 4, 0xF0F0F0F0u, 0x08080808u), a3 = lop3_and_or(u1, 0xF0F0F0F0u, 0x08080808u);
+                    const uint4 q4 = lds128_volatile_o<b * 512>(qfr_base);
+                    int hi[4], lo[4];
+                    imma16832(hi, a0, a1, a2, a3, q4.x, q4.y);
+                    imma16832(lo, a0, a1, a2, a3, q4.z, q4.w);
+                    if (NSPLIT) {   // hi: columns (D2, D1) of head j, lo: columns (D0, -)
+                        const int i0 = (int)((uint32_t)hi[0] * 65536u + (uint32_t)hi[1] * 256u + (uint32_t)lo[0]);
+                        const int i1 = (int)((uint32_t)hi[2] * 65536u + (uint32_t)hi[3] * 256u + (uint32_t)lo[2]);
+                        s[0][0] = fmaf(ka, (float)i0, s[0][0]);
+                        s[1][0] = fmaf(kb, (float)i1, s[1][0]);
+                    } else {        // hi: digit D2 of heads 2j, 2j+1, lo: digit D1, third MMA: digit D0
+                        const uint2 q2 = lds64_o<(4 + b) * 512>(qfr_base);
+                        int l0[4];
+                        imma16832(l0, a0, a1, a2, a3, q2.x, q2.y);
+                        int iv[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) iv[i] = (int)((uint32_t)hi[i] * 65536u + (uint32_t)lo[i] * 256u + (uint32_t)l0[i]);
+                        s[0][0] = fmaf(ka, (float)iv[0], s[0][0]);
+                        s[0][1] = fmaf(ka, (float)iv[1], s[0][1]);
+                        s[1][0] = fmaf(kb, (float)iv[2], s[1][0]);
+                        s[1][1] = fmaf(kb, (float)iv[3], s[1][1]);
+                    }
+                } else {
+                    uint32_t x[2][4];   // [token n | n + 8]: codes 8j..8j+7 of block b as four half2
+                    static_for<0, 2>([&](auto t_) {
+                        constexpr int t = decltype(t_)::value;
                         const uint32_t lo = lds32_o<12 * b + t * kOct>(bK0), hi = lds32_o<12 * b + t * kOct>(bK1);
                         const uint32_t w = __funnelshift_r(lo, hi, ksh);          // codes 8j..8j+7 in bits 0..23
                         x[t][0] = lds32(lop3_and_or(w << 7, 0x1F80u, lut));
                         x[t][1] = lds32(lop3_and_or(w << 1, 0x1F80u, lut));
                         x[t][2] = lds32(lop3_and_or(w >> 5, 0x1F80u, lut));
                         x[t][3] = lds32(lop3_and_or(w >> 11, 0x1F80u, lut));
+                    });
+                    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                    static_for<0, (NSPLIT ? 1 : 2)>([&](auto set_) {
+                        constexpr int set = decltype(set_)::value;
+                        const uint4 q4 = lds128_volatile_o<(set * 4 + b) * 512>(qfr_base);
+                        mma16816(acc, x[0][0], x[1][0], x[0][1], x[1][1], q4.x, q4.y);
+                        mma16816(acc, x[0][2], x[1][2], x[0][3], x[1][3], q4.z, q4.w);
+                    });
+                    if (NSPLIT) {   // columns 2j, 2j+1 are the hi and lo part of one head: one running sum per token
+                        s[0][0] = fmaf(ka, acc[1], fmaf(ka, acc[0], s[0][0]));
+                        s[1][0] = fmaf(kb, acc[3], fmaf(kb, acc[2], s[1][0]));
+                    } else {
+                        s[0][0] = fmaf(ka, acc[0], s[0][0]);
+                        s[0][1] = fmaf(ka, acc[1], s[0][1]);
+                        s[1][0] = fmaf(kb, acc[2], s[1][0]);
+                        s[1][1] = fmaf(kb, acc[3], s[1][1]);
                     }
-                });
-                float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                static_for<0, (NSPLIT ? 1 : 2)>([&](auto set_) {
-                    constexpr int set = decltype(set_)::value;
-                    const uint4 q4 = lds128_volatile_o<(set * 4 + b) * 512>(qfr_base);
-                    mma16816(acc, x[0][0], x[1][0], x[0][1], x[1][1], q4.x, q4.y);
-                    mma16816(acc, x[0][2], x[1][2], x[0][3], x[1][3], q4.z, q4.w);
-                });
-                const __half2 pa = u32_as_h2(b < 2 ? sca.x : sca.y), pb = u32_as_h2(b < 2 ? scb.x : scb.y);
-                const float ka = fabsf((b & 1) ? __high2float(pa) : __low2float(pa));
-                const float kb = fabsf((b & 1) ? __high2float(pb) : __low2float(pb));
-                if (NSPLIT) {   // columns 2j, 2j+1 are the hi and lo part of one head: one running sum per token
-                    s[0][0] = fmaf(ka, acc[1], fmaf(ka, acc[0], s[0][0]));
-                    s[1][0] = fmaf(kb, acc[3], fmaf(kb, acc[2], s[1][0]));
-                } else {
-                    s[0][0] = fmaf(ka, acc[0], s[0][0]);
-                    s[0][1] = fmaf(ka, acc[1], s[0][1]);
-                    s[1][0] = fmaf(kb, acc[2], s[1][0]);
-                    s[1][1] = fmaf(kb, acc[3], s[1][1]);
                 }
             });
         }
         float sc[2][kE];   // scores [token n | n + 8][head]
 #pragma unroll
-        for (int t = 0; t < 2; ++t) {
-            if (NSPLIT) {
-                sc[t][0] = s[t][0];
-            } else {
+        for (int t = 0; t < 2; ++t)
 #pragma unroll
-                for (int e = 0; e < kE; ++e) sc[t][e] = s[t][e];
-            }
-        }
+            for (int e = 0; e < kE; ++e) sc[t][e] = BITS == 4 ? s[t][e] * qsc[e] : s[t][e];
         if (it >= rag_from) {   // ragged tail: tokens past the end (of the sequence, or of the partition) get zero weight
             const int gs = first + it * stride;
             if (TMA) {
@@ -865,7 +948,11 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
             m.dev_signs = nullptr; m.out = a.out; m.lse_out = a.lse_out;
             m.head_dim = kD; m.nblk = kD / 32; m.num_partitions = a.num_partitions; m.rotate = 1;
             m.out_dtype = a.out_dtype; m.sign_mag = a.sign_mag;
-            for (int hh = warp; hh < g; hh += kWarps) merge_head(m, kvh * g + hh, lane, 0, 1);   // one warp per query head
+            // all heads of the group at once when the weight table fits the (now idle) ring memory
+            if ((size_t)(16 + g * a.num_partitions) * sizeof(float) <= (size_t)kWarps * G::kRingB)
+                merge_group128(m, kvh * g, g, tid, reinterpret_cast<float*>(s_raw));
+            else
+                for (int hh = warp; hh < g; hh += kWarps) merge_head(m, kvh * g + hh, lane, 0, 1);   // one warp per query head
             if (tid == 0) a.counters[kvh] = 0u;   // ready for the next launch
         }
     }
@@ -950,8 +1037,16 @@ int launch_one(const MmaArgs& a, const TmaMaps& maps, const Codebook& app_cb, di
     using G = Geo<BITS>;
     // dynamic shared memory: the stage rings (1 KB alignment slack), for 3-bit after the 8 KB table and its slack
     const size_t dyn = BITS == 3 ? 16384 + kWarps * G::kRingB : 1024 + kWarps * G::kRingB;
-    cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<QT, BITS, NSPLIT, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn);
-    if (e != cudaSuccess) { set_cuda_error(e); return TQB_ERR_CUDA; }
+    // the opt-in to more than 48 KB of dynamic shared memory is a per-device property of the kernel: set it once
+    // per device and instantiation, not on every launch
+    static std::atomic<unsigned long long> configured{0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = -1;
+    if (dev < 0 || !((configured.load(std::memory_order_acquire) >> dev) & 1ull)) {
+        cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<QT, BITS, NSPLIT, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn);
+        if (e != cudaSuccess) { set_cuda_error(e); return TQB_ERR_CUDA; }
+        if (dev >= 0) configured.fetch_or(1ull << dev, std::memory_order_release);
+    }
     decode_mma_kernel<QT, BITS, NSPLIT, TMA><<<grid, kThreads, dyn, s>>>(a, maps, app_cb);
     return check_launch(s);
 }

@@ -454,6 +454,25 @@ size_t tqb_pqo_cache_memory_usage(const tqb_pqo_cache* c) {
     return total;
 }
 
+// Dense copy of one layer's stored rows (the capacity padding is dropped): indices [heads, len, packed_dim],
+// scales [heads, len, nblk]; `host_buffers` != 0: the destinations are host memory.
+int tqb_pqo_cache_export_layer(const tqb_pqo_cache* c, int32_t layer, uint8_t* k_indices, uint16_t* k_scales,
+                               uint8_t* v_indices, uint16_t* v_scales, int32_t host_buffers, tqb_stream_t stream) {
+    TQB_TRY(check_layer(c, layer));
+    if (!k_indices || !k_scales || !v_indices || !v_scales) return TQB_ERR_NULL_POINTER;
+    const auto& l = c->layers[layer];
+    if (l.len == 0) return TQB_OK;
+    cudaStream_t s = as_stream(stream);
+    const cudaMemcpyKind kind = host_buffers ? cudaMemcpyDeviceToHost : cudaMemcpyDeviceToDevice;
+    const size_t iw = (size_t)l.len * c->packed_dim, sw = (size_t)l.len * c->nblk * 2;
+    TQB_CUDA(cudaMemcpy2DAsync(k_indices, iw, l.ki, (size_t)l.cap * c->packed_dim, iw, c->heads, kind, s));
+    TQB_CUDA(cudaMemcpy2DAsync(v_indices, iw, l.vi, (size_t)l.cap * c->packed_dim, iw, c->heads, kind, s));
+    TQB_CUDA(cudaMemcpy2DAsync(k_scales, sw, l.ks, (size_t)l.cap * c->nblk * 2, sw, c->heads, kind, s));
+    TQB_CUDA(cudaMemcpy2DAsync(v_scales, sw, l.vs, (size_t)l.cap * c->nblk * 2, sw, c->heads, kind, s));
+    if (host_buffers) TQB_CUDA(cudaStreamSynchronize(s));
+    return TQB_OK;
+}
+
 int tqb_pqo_cache_layer_ptrs(const tqb_pqo_cache* c, int32_t layer, const uint8_t** k_indices, const uint16_t** k_scales,
                              const uint8_t** v_indices, const uint16_t** v_scales) {
     TQB_TRY(check_layer(c, layer));

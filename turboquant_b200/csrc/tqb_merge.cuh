@@ -95,4 +95,82 @@ __device__ __forceinline__ void merge_head(const MergeArgs& a, int head, int lan
     }
 }
 
+// The same merge for ALL g query heads of one KV head by one CTA of 128 threads, head_dim 128: thread d owns output
+// element d of every head (warp = 32-block, lane = element).  The partition weights exp(max_p - M) of all heads are
+// tabulated in shared memory first, then each thread walks the partitions eight at a time with the loads of all heads
+// in flight together, so the whole merge costs about P / 8 trips to L2 (the per-head routine above makes one trip per
+// partition, block and head).  Same sums in the same order, hence the same bits as merge_head.
+// `s_work`: shared memory, at least (2 * 8 + g * P) floats; all 128 threads must call.
+__device__ __forceinline__ void merge_group128(const MergeArgs& a, int head0, int g, int tid, float* s_work) {
+    using namespace merge_detail;
+    const int P = a.num_partitions, lane = tid & 31, warp = tid >> 5;
+    constexpr int D = 128;
+    float* s_M = s_work;          // [8]
+    float* s_L = s_work + 8;      // [8]
+    float* s_w = s_work + 16;     // [g][P]
+    for (int hh = warp; hh < g; hh += 4) {
+        const float* pm = a.partial_max + (size_t)(head0 + hh) * P;
+        const float* ps = a.partial_sum + (size_t)(head0 + hh) * P;
+        float pmv = -FLT_MAX, psv = 0.0f;
+        if (lane < P) {
+            pmv = __ldcg(pm + lane);
+            psv = __ldcg(ps + lane);
+        }
+        float M = pmv;
+        for (int p = lane + 32; p < P; p += 32) M = fmaxf(M, __ldcg(pm + p));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+        const float wl = lane < P ? expf(pmv - M) : 0.0f;
+        if (lane < P) s_w[hh * P + lane] = wl;
+        float L = lane < P ? psv * wl : 0.0f;
+        for (int p = lane + 32; p < P; p += 32) {
+            const float wp = expf(__ldcg(pm + p) - M);
+            s_w[hh * P + p] = wp;
+            L += __ldcg(ps + p) * wp;
+        }
+        L = sum32(L);
+        if (lane == 0) {
+            s_M[hh] = M;
+            s_L[hh] = L;
+        }
+    }
+    __syncthreads();
+    float acc[8];
+#pragma unroll
+    for (int hh = 0; hh < 8; ++hh) acc[hh] = 0.0f;
+    const float* po = a.partial_out + (size_t)head0 * P * D + tid;
+    for (int p0 = 0; p0 < P; p0 += 8) {
+        float v[8][8];
+#pragma unroll
+        for (int hh = 0; hh < 8; ++hh)
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                v[hh][i] = (hh < g && p0 + i < P) ? __ldcg(po + ((size_t)hh * P + p0 + i) * D) : 0.0f;
+#pragma unroll
+        for (int hh = 0; hh < 8; ++hh)
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                if (hh < g && p0 + i < P) acc[hh] = fmaf(v[hh][i], s_w[hh * P + p0 + i], acc[hh]);
+    }
+    const float inv_sqrt = 1.0f / sqrtf((float)kBlock);
+    const uint32_t neg = 0xB1A6D4B2u;   // src/cache/precomputed/rotation.rs:16-20
+    const float sg = a.dev_signs ? a.dev_signs[lane] : (((neg >> lane) & 1u) ? -a.sign_mag : a.sign_mag);
+#pragma unroll
+    for (int hh = 0; hh < 8; ++hh) {
+        if (hh < g) {
+            float r = acc[hh];
+            if (a.rotate) r = wht32(r * sg, lane) * inv_sqrt;
+            if (a.lse_out == nullptr) {
+                const float L = s_L[hh];
+                r *= L > 0.0f ? 1.0f / L : 0.0f;
+            }
+            store_out(a.out, a.out_dtype, (size_t)(head0 + hh) * D + tid, r);
+        }
+    }
+    if (a.lse_out != nullptr && tid < g) {
+        a.lse_out[(head0 + tid) * 2] = s_M[tid];
+        a.lse_out[(head0 + tid) * 2 + 1] = s_L[tid];
+    }
+}
+
 }  // namespace tqb

@@ -58,13 +58,26 @@ class SequenceParallelDecoder:
         self.gathered = torch.empty((self.world * self.hq * (d + 2),), dtype=torch.float32, device=dev)
         self.out = torch.empty((self.hq, d), dtype=out_dtype, device=dev)
 
-    def attend(self, layer, q, softmax_scale):
+    exchange_kind = "NCCL all-gather of one flat (out, max, sum) record per rank, then a merge kernel"
+
+    def attend_local(self, layer, q, softmax_scale):
+        """Shard-local split-K pass: fills this rank's record (un-normalised out, then (max, sum) pairs)."""
         from .api import check, _dtype_code, _stream
         lib, d = self._lib, self.cache.config.head_dim
         q = q.contiguous()
         check(lib.tqb_pqo_cache_attend_partial(self.cache._h, layer, q.data_ptr(), _dtype_code(q.dtype), self.nq, softmax_scale,
                                                self.rec.data_ptr(), self.rec.data_ptr() + 4 * self.hq * d, _stream()))
+
+    def exchange(self):
         dist.all_gather_into_tensor(self.gathered, self.rec, group=self.group)
-        check(lib.tqb_lse_combine_packed(self.gathered.data_ptr(), self.world, self.hq, d, self.out.data_ptr(),
-                                         _dtype_code(self.out_dtype), _stream()))
+
+    def combine(self):
+        from .api import check, _dtype_code, _stream
+        check(self._lib.tqb_lse_combine_packed(self.gathered.data_ptr(), self.world, self.hq, self.cache.config.head_dim,
+                                               self.out.data_ptr(), _dtype_code(self.out_dtype), _stream()))
         return self.out
+
+    def attend(self, layer, q, softmax_scale):
+        self.attend_local(layer, q, softmax_scale)
+        self.exchange()
+        return self.combine()
