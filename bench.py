@@ -18,7 +18,8 @@ roofline= the decode kernel alone: algorithmic bytes per launch / mean launch du
           measured with CUDA events around single launches.
 parity_max_abs = max-abs difference between one layer's decode output of the cache under test and the
           CPU oracle's attention over the identical packed bytes copied down from that cache.
-Extra records (headline unchanged): `pqo3` (the same batch-64 x 8,192 shape stored as PQO3), `config3`
+Extra records (headline unchanged): `pqo3` (the same batch-64 x 8,192 shape stored as PQO3), `tq3_fused` (the same
+shape in a TqCache with the QJL correction inside the attention kernel), `config3`
 (Qwen3-0.6B shape, batch 1, context 1K .. 32K, per layer and per 28-layer step against the HBM roofline),
 `seq_parallel` (Llama-3-70B shape, one 131,072-token sequence split along the tokens over the ranks,
 partials exchanged and merged per layer).
@@ -316,6 +317,7 @@ def run_ours(args):
         if world == 1:
             extras = {}
             for name, fn in (("pqo3", lambda: extra_pqo3(tq, w, lib, dev, args, peak)),
+                             ("tq3_fused", lambda: extra_tq3(tq, w, lib, dev, args, peak)),
                              ("config3", lambda: extra_config3(tq, w, lib, dev, args, peak)),
                              ("seq_parallel", lambda: extra_seq_parallel(tq, w, lib, dev, args, peak, None, 0, 1))):
                 try:
@@ -386,6 +388,35 @@ def extra_pqo3(tq, w, lib, dev, args, peak):
                          "unit": "GB/s", "frac": round(ach / peak, 4), "launch_us": round(launch_ms * 1e3, 1),
                          "algorithmic_bytes_per_launch": units * bpt, "algorithmic_bytes_per_token_head": bpt},
             "parity_max_abs": par}
+
+
+def extra_tq3(tq, w, lib, dev, args, peak):
+    """TqCache (TQ3: 2-bit codebook stored at 3 bits + a 128-bit QJL sign sketch and a residual norm per key) at the
+    headline shape: 4 layers x 64 sequences x 8 kv heads x ctx 8192; a step = per layer, append (quantize, dequantize,
+    residual sketch), query projection and fused attention with the in-kernel QJL correction.  Algorithmic bytes per
+    (token, KV head): 56 (K) + 56 (V) + 16 (sketch) + 2 (norm) = 130."""
+    L, B, HQ, HKV, D, CTX = 4, CFG["batch"], CFG["hq"], CFG["hkv"], CFG["head_dim"], CFG["ctx"]
+    scale = 1.0 / np.sqrt(D)
+    cache = tq.TqCache(tq.CacheConfig(bits=3, head_dim=D, num_kv_heads=HKV, num_layers=L, batch=B, outlier_blocks=0))
+    g = torch.Generator(device=dev).manual_seed(7)
+    q = (torch.randn((B, HQ, 1, D), generator=g, device=dev) * scale).to(torch.bfloat16)
+    for layer in range(L):
+        k, v = w.synth_kv("llama8b", layer, CTX, dev)
+        cache.prefill(layer, k, v, q)
+        del k, v
+    nk = torch.randn((B, HKV, 1, D), generator=g, device=dev).to(torch.bfloat16)
+    att = tq.AttendConfig(scale, HQ // HKV)
+
+    def step():
+        for layer in range(L):
+            cache.decode_fused(layer, nk, nk, q, att)
+    ms = timed_chain(step, 2, max(3, args.steps))
+    bpt = 130
+    step_bytes = L * B * HKV * cache.seq_len(0) * bpt
+    return {"workload": "TqCache TQ3 fused decode (in-kernel QJL correction): 4 layers x 64 sequences x 8 kv heads x ctx 8192",
+            "value": round(step_bytes / (ms * 1e-3) / 1e9, 1), "unit": "GB/s", "frac_of_hbm_peak": round(step_bytes / (ms * 1e-3) / 1e9 / peak, 4),
+            "us_per_layer": round(ms * 1e3 / L, 1), "algorithmic_bytes_per_token_head": bpt,
+            "note": "per layer: block quantize K and V, dequantize K, residual sketch, query projection, then one attention launch"}
 
 
 def extra_config3(tq, w, lib, dev, args, peak):

@@ -208,24 +208,34 @@ def test_other_cache_modes(nm, ob):
     assert np.abs(got - want).max() < TOL
 
 
-def test_qjl_correction_branch():
-    # tq_attention_kernel.cu:197-231: per-key residual sign sketch over the whole head_dim
-    rng = np.random.default_rng(9)
-    hq, hkv, L, D = 4, 2, 200, 128
+@pytest.mark.parametrize("g", [1, 2, 4, 8])
+@pytest.mark.parametrize("L", [200, 4133])
+def test_qjl_correction_branch(g, L):
+    # tq_attention_kernel.cu:197-231: per-key residual sign sketch over the whole head_dim.  The 3-bit tensor-core
+    # kernel applies it on the integer tensor-core path; the general kernel (forced) is the cross-check.
+    rng = np.random.default_rng(9 + g + L)
+    hkv, D = 2, 128
+    hq = hkv * g
     k = rng.standard_normal((hkv, L, D)).astype(np.float32)
-    ki, ks, vi, vs = make_cache(rng, hkv, L, L, 3, outliers=False, ob=0)
-    kp, ksc = o.block_quantize(3, D, 0, 0, k.reshape(-1, D))
-    ki, ks = kp.reshape(hkv, L, -1), ksc.reshape(hkv, L, -1)
-    res = k.reshape(-1, D) - o.block_dequantize(3, D, 0, 0, kp, ksc)
-    signs = np.stack([o.qjl_signs(r, D, 12345) for r in res]).reshape(hkv, L, D // 8)
-    norms = np.array([o.f32_to_f16_bits(float(np.linalg.norm(r))) for r in res], np.uint16).reshape(hkv, L)
+    ki, ks, vi, vs = make_cache(rng, hkv, L, L + 3, 3, outliers=False, ob=0)
+    kp, ksc = o.block_quantize(3, D, 0, 0, k.reshape(-1, D), nthreads=8)
+    ki[:, :L], ks[:, :L] = kp.reshape(hkv, L, -1), ksc.reshape(hkv, L, -1)
+    res = k.reshape(-1, D) - o.block_dequantize(3, D, 0, 0, kp, ksc, nthreads=8)
+    signs = np.zeros((hkv, L + 3, D // 8), np.uint8)
+    norms = np.zeros((hkv, L + 3), np.uint16)
+    signs[:, :L] = np.stack([o.qjl_signs(r, D, 12345) for r in res]).reshape(hkv, L, D // 8)
+    norms[:, :L] = np.array([o.f32_to_f16_bits(float(np.linalg.norm(r))) for r in res], np.uint16).reshape(hkv, L)
+    signs[:, L:], norms[:, L:] = 0xFF, 0x7E00     # slots behind the last token: nothing of them may reach the result
     q = (rng.standard_normal((hq, D)) / np.sqrt(D)).astype(np.float32)
     rq = np.stack([o.query_projections(qh, D, 12345) for qh in q])
-    want = o.block_attention(3, D, 0, 0, q, ki, ks, vi, vs, L, 0.0884, qjl=(signs, norms, rq))
-    got = gpu_attend(q, ki, ks, vi, vs, L, 3, 0.0884, outlier_blocks=0,
-                     qjl=(dev(signs), dev(norms.view(np.int16)), dev(rq))).cpu().numpy()
-    assert np.abs(got - want).max() < TOL
-    plain = o.block_attention(3, D, 0, 0, q, ki, ks, vi, vs, L, 0.0884)
+    want = o.block_attention(3, D, 0, 0, q, ki, ks, vi, vs, L, 0.0884, qjl=(signs, norms, rq), nthreads=8)
+    args = dict(outlier_blocks=0, qjl=(dev(signs), dev(norms.view(np.int16)), dev(rq)))
+    for parts in (0, 1, 3):
+        got = gpu_attend(q, ki, ks, vi, vs, L, 3, 0.0884, num_partitions=parts, **args).cpu().numpy()
+        assert np.abs(got - want).max() < 3e-4, np.abs(got - want).max()
+    slow = gpu_attend(q, ki, ks, vi, vs, L, 3, 0.0884, force_general=True, **args).cpu().numpy()
+    assert np.abs(slow - want).max() < 2e-5
+    plain = o.block_attention(3, D, 0, 0, q, ki, ks, vi, vs, L, 0.0884, nthreads=8)
     assert np.abs(plain - want).max() > 1e-4      # the correction is not a no-op
 
 

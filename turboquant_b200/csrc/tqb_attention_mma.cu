@@ -85,6 +85,12 @@ struct MmaArgs {
     // causal chunk: "KV head" x of the grid is query position x / alias_heads on cache head x % alias_heads and
     // sees kv_len0 + x / alias_heads tokens (0: off, every head has its own rows and kv_len tokens)
     int alias_heads, kv_len0;
+    // QJL correction of the scores (tq_attention_kernel.cu:197-231): sign sketch words [hkv, kv_stride, 4], residual
+    // norms [hkv, kv_stride] (f16 bits), projected queries [hq, 128]; qjl_const = sqrt(pi/2) / sqrt(128) * softmax_scale * log2(e)
+    const uint32_t* qjl_signs;
+    const uint16_t* qjl_norms;
+    const float* rq;
+    float qjl_const;
 };
 
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -102,6 +108,13 @@ __device__ __forceinline__ void imma16832(int (&d)[4], uint32_t a0, uint32_t a1,
     asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
         : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
+__device__ __forceinline__ void imma16832_acc(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                              uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
 __device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t b, uint32_t c) {
@@ -394,7 +407,14 @@ __device__ __forceinline__ void stage_fill(FillPlan& f, bool issue, bool ragged,
 // (193-196 us).  The per-warp cp.async rings let the four warps drift apart freely and keep the copy issue
 // off any single warp's critical path; the shared tile ring couples them through its barriers.  So cp.async
 // is the default and TMA is opt-in (TQB_DECODE_TMA).
-template <typename QT, int BITS, bool NSPLIT, bool TMA>
+//
+// QJL = true (3-bit, cp.async staging): the score of every token gets the correction of the reference's kernel
+// (tq_attention_kernel.cu:197-231), norm_t * sqrt(pi/2) / sqrt(128) * sum_d rq[h, d] * (+-1 by the token's sign
+// sketch), computed on the integer tensor-core path: the 128 sign bits of a token enter as 0 / 1 bytes (one shift and
+// one AND per four of them), the projected query rq as a 20-bit integer in three base-256 digits, and
+// sum rq (2 bit - 1) = 2 sum rq bit - sum rq.  The sketch words and norms are fetched straight from global memory one
+// step ahead of their use (16 + 2 bytes per token; they are not staged).
+template <typename QT, int BITS, bool NSPLIT, bool TMA, bool QJL = false>
 __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, const __grid_constant__ TmaMaps maps,
                                                                  const __grid_constant__ Codebook app_cb) {
     if (a.gate != nullptr && *a.gate != a.gate_want) return;   // the caller's tables are not the ones this kernel decodes
@@ -405,7 +425,9 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
     __shared__ __align__(8) unsigned long long s_bar[2][kStages];   // TMA staging: full / empty barriers of the stages
     __shared__ float s_q[8 * kD];   // rotated queries (prologue only)
     __shared__ __align__(16) uint4 s_qfr[8][32];   // MMA fragments of the rotated queries, [operand set * 4 + block][lane]
-    __shared__ float s_qinv[8], s_qsc[8];          // 4-bit: per head, rotated query -> 20-bit integer and back (see below)
+    __shared__ float s_qinv[8], s_qsc[8];          // integer operands: per head, value -> 20-bit integer and back (see below)
+    __shared__ __align__(16) uint4 s_rqfr[QJL ? (NSPLIT ? 4 : 8) : 1][32];   // QJL: digit fragments of the projected queries
+    __shared__ int s_rqsum[8];                     // QJL: per head, the sum of the integer projected query
     const uint32_t dyn_base = (uint32_t)__cvta_generic_to_shared(s_dyn);
     const uint32_t lut_base = BITS == 3 ? ((dyn_base + 8191u) & ~8191u) : 0u;
     const uint32_t rings_base = BITS == 3 ? lut_base + 8192u : ((dyn_base + 1023u) & ~1023u);
@@ -621,13 +643,92 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
         }
     }
     __syncthreads();
+    if constexpr (QJL) {
+        // The projected queries rq of the g heads replace the rotated queries in s_q (those live in their fragments
+        // by now), are scaled to 20-bit integers per head like the 4-bit path's queries, and laid out as B fragments:
+        // MMA number m (0..3) contracts, in lane quad position j, the dims 32j + 2m + 8i (k-slots 4j + i) and
+        // 32j + 2m + 1 + 8i (k-slots 16 + 4j + i), i = 0..3 - the order in which the sign bits are peeled off a word.
+        for (int i = tid; i < 8 * kD; i += kThreads) {
+            const int hh = i >> 7;
+            s_q[i] = hh < g ? a.rq[(size_t)(kvh * g + hh) * kD + (i & 127)] : 0.0f;
+        }
+        __syncthreads();
+        for (int hh = warp; hh < 8; hh += kWarps) {
+            float m = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) m = fmaxf(m, fabsf(s_q[hh * kD + lane + 32 * i]));
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+            const bool ok = m > 0.0f && m < 3.0e38f;
+            const float inv = ok ? 524287.0f / m : 0.0f;
+            int sum = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) sum += __float2int_rn(s_q[hh * kD + lane + 32 * i] * inv);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            if (lane == 0) {
+                s_qinv[hh] = inv;
+                s_qsc[hh] = ok ? m / 524287.0f : 0.0f;
+                s_rqsum[hh] = sum;
+            }
+        }
+        __syncthreads();
+        {
+            const int m4 = warp;   // one of the four MMAs per warp
+            const int head = NSPLIT ? (n >> 1) : n;
+            const float inv = s_qinv[head];
+            uint32_t dg[3][2] = {{0u, 0u}, {0u, 0u}, {0u, 0u}};
+#pragma unroll
+            for (int half = 0; half < 2; ++half)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int v = __float2int_rn(s_q[head * kD + 32 * j + 2 * m4 + half + 8 * i] * inv);
+                    const int d0 = (int)(signed char)(v & 0xFF);
+                    const int v1 = (v - d0) >> 8;
+                    const int d1 = (int)(signed char)(v1 & 0xFF);
+                    const int d2 = (v1 - d1) >> 8;
+                    dg[0][half] |= (uint32_t)(d0 & 0xFF) << (8 * i);
+                    dg[1][half] |= (uint32_t)(d1 & 0xFF) << (8 * i);
+                    dg[2][half] |= (uint32_t)(d2 & 0xFF) << (8 * i);
+                }
+            if (NSPLIT) {
+                const bool odd = n & 1;
+                s_rqfr[m4][lane] = make_uint4(odd ? dg[1][0] : dg[2][0], odd ? dg[1][1] : dg[2][1], odd ? 0u : dg[0][0], odd ? 0u : dg[0][1]);
+            } else {
+                s_rqfr[m4][lane] = make_uint4(dg[2][0], dg[2][1], dg[1][0], dg[1][1]);
+                s_rqfr[4 + m4][lane] = make_uint4(dg[0][0], dg[0][1], 0u, 0u);
+            }
+        }
+        __syncthreads();
+    }
     const uint32_t qfr_base = (uint32_t)__cvta_generic_to_shared(&s_qfr[0][lane]);
+    const uint32_t rqfr_base = (uint32_t)__cvta_generic_to_shared(&s_rqfr[0][lane]);
     // After the scores, lane (n, j) holds tokens n and n + 8 of the step and kE heads:
     //   NSPLIT: head j (its hi and lo columns 2j, 2j+1 are summed in the lane)  |  otherwise heads 2j, 2j+1.
     constexpr int kE = NSPLIT ? 1 : 2;
     float qsc[kE];                // 4-bit: integer score -> log2-domain score of the lane's head(s)
 #pragma unroll
     for (int e = 0; e < kE; ++e) qsc[e] = BITS == 4 ? s_qsc[NSPLIT ? j : 2 * j + e] : 1.0f;
+    float rqc[kE];                // QJL: integer correction -> log2-domain score, without the token's residual norm
+    int rqsum[kE];
+#pragma unroll
+    for (int e = 0; e < kE; ++e) {
+        rqc[e] = QJL ? s_qsc[NSPLIT ? j : 2 * j + e] * a.qjl_const : 0.0f;
+        rqsum[e] = QJL ? s_rqsum[NSPLIT ? j : 2 * j + e] : 0;
+    }
+    // QJL: sketch word j and residual norm of tokens n and n + 8 of the step, fetched one step ahead (tokens past
+    // the end re-read the last token; they are masked later)
+    uint32_t sgw[2] = {0u, 0u};
+    uint32_t nrw[2] = {0u, 0u};
+    auto qjl_fetch = [&](int it, uint32_t (&sg)[2], uint32_t (&nr)[2]) {
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+            const size_t row = row0 + (size_t)min(first + it * stride + n + 8 * t, last);
+            sg[t] = __ldg(a.qjl_signs + row * 4 + j);
+            nr[t] = __ldg(a.qjl_norms + row);
+        }
+    };
+    if (QJL && nsteps > 0) qjl_fetch(0, sgw, nrw);
     float m_run[kE], l_run[kE];   // per head; l_run: this lane's tokens only
 #pragma unroll
     for (int e = 0; e < kE; ++e) {
@@ -751,6 +852,41 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
         for (int t = 0; t < 2; ++t)
 #pragma unroll
             for (int e = 0; e < kE; ++e) sc[t][e] = BITS == 4 ? s[t][e] * qsc[e] : s[t][e];
+        if constexpr (QJL) {
+            uint32_t sgn[2] = {0u, 0u}, nrn[2] = {0u, 0u};
+            if (it + 1 < nsteps) qjl_fetch(it + 1, sgn, nrn);   // next step's sketch words, in flight during this step
+            int ca[4] = {0, 0, 0, 0}, cb[4] = {0, 0, 0, 0}, cc[4] = {0, 0, 0, 0};
+            static_for<0, 4>([&](auto m_) {
+                constexpr int m4 = decltype(m_)::value;
+                // bytes i of the four operands: sign bits 2 m4 + 8 i (and 2 m4 + 1 + 8 i) of the two tokens' words
+                const uint32_t a0 = (sgw[0] >> (2 * m4)) & 0x01010101u, a1 = (sgw[1] >> (2 * m4)) & 0x01010101u;
+                const uint32_t a2 = (sgw[0] >> (2 * m4 + 1)) & 0x01010101u, a3 = (sgw[1] >> (2 * m4 + 1)) & 0x01010101u;
+                const uint4 r4 = lds128_volatile_o<m4 * 512>(rqfr_base);
+                imma16832_acc(ca, a0, a1, a2, a3, r4.x, r4.y);
+                imma16832_acc(cb, a0, a1, a2, a3, r4.z, r4.w);
+                if (!NSPLIT) {
+                    const uint2 r2 = lds64_o<(4 + m4) * 512>(rqfr_base);
+                    imma16832_acc(cc, a0, a1, a2, a3, r2.x, r2.y);
+                }
+            });
+            const float n0 = __half2float(__ushort_as_half((unsigned short)nrw[0]));
+            const float n1 = __half2float(__ushort_as_half((unsigned short)nrw[1]));
+            if (NSPLIT) {   // ca: columns (D2, D1) of head j, cb: (D0, -)
+                const int i0 = (int)((uint32_t)ca[0] * 65536u + (uint32_t)ca[1] * 256u + (uint32_t)cb[0]);
+                const int i1 = (int)((uint32_t)ca[2] * 65536u + (uint32_t)ca[3] * 256u + (uint32_t)cb[2]);
+                sc[0][0] = fmaf((float)(2 * i0 - rqsum[0]), n0 * rqc[0], sc[0][0]);
+                sc[1][0] = fmaf((float)(2 * i1 - rqsum[0]), n1 * rqc[0], sc[1][0]);
+            } else {        // ca / cb / cc: digits D2 / D1 / D0 of heads 2j, 2j+1
+                int iv[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) iv[i] = (int)((uint32_t)ca[i] * 65536u + (uint32_t)cb[i] * 256u + (uint32_t)cc[i]);
+                sc[0][0] = fmaf((float)(2 * iv[0] - rqsum[0]), n0 * rqc[0], sc[0][0]);
+                sc[0][1] = fmaf((float)(2 * iv[1] - rqsum[1]), n0 * rqc[1], sc[0][1]);
+                sc[1][0] = fmaf((float)(2 * iv[2] - rqsum[0]), n1 * rqc[0], sc[1][0]);
+                sc[1][1] = fmaf((float)(2 * iv[3] - rqsum[1]), n1 * rqc[1], sc[1][1]);
+            }
+            sgw[0] = sgn[0]; sgw[1] = sgn[1]; nrw[0] = nrn[0]; nrw[1] = nrn[1];
+        }
         if (it >= rag_from) {   // ragged tail: tokens past the end (of the sequence, or of the partition) get zero weight
             const int gs = first + it * stride;
             if (TMA) {
@@ -1032,7 +1168,7 @@ bool make_tma_maps(const MmaArgs& a, TmaMaps& m) {
     return ok;
 }
 
-template <typename QT, int BITS, bool NSPLIT, bool TMA>
+template <typename QT, int BITS, bool NSPLIT, bool TMA, bool QJL>
 int launch_one(const MmaArgs& a, const TmaMaps& maps, const Codebook& app_cb, dim3 grid, cudaStream_t s) {
     using G = Geo<BITS>;
     // dynamic shared memory: the stage rings (1 KB alignment slack), for 3-bit after the 8 KB table and its slack
@@ -1043,11 +1179,11 @@ int launch_one(const MmaArgs& a, const TmaMaps& maps, const Codebook& app_cb, di
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = -1;
     if (dev < 0 || !((configured.load(std::memory_order_acquire) >> dev) & 1ull)) {
-        cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<QT, BITS, NSPLIT, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn);
+        cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<QT, BITS, NSPLIT, TMA, QJL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn);
         if (e != cudaSuccess) { set_cuda_error(e); return TQB_ERR_CUDA; }
         if (dev >= 0) configured.fetch_or(1ull << dev, std::memory_order_release);
     }
-    decode_mma_kernel<QT, BITS, NSPLIT, TMA><<<grid, kThreads, dyn, s>>>(a, maps, app_cb);
+    decode_mma_kernel<QT, BITS, NSPLIT, TMA, QJL><<<grid, kThreads, dyn, s>>>(a, maps, app_cb);
     return check_launch(s);
 }
 
@@ -1055,13 +1191,18 @@ template <int BITS>
 int launch(const MmaArgs& a, int g, int q_dtype, bool allow_tma, const Codebook& app_cb, dim3 grid, cudaStream_t s) {
     TmaMaps maps;
     memset(&maps, 0, sizeof(maps));
-    const bool tma = allow_tma && make_tma_maps<BITS>(a, maps);
-#define TQB_LAUNCH_MMA(QT)                                                                       \
-    do {                                                                                         \
-        if (g <= 4) return tma ? launch_one<QT, BITS, true, true>(a, maps, app_cb, grid, s)              \
-                               : launch_one<QT, BITS, true, false>(a, maps, app_cb, grid, s);            \
-        return tma ? launch_one<QT, BITS, false, true>(a, maps, app_cb, grid, s)                         \
-                   : launch_one<QT, BITS, false, false>(a, maps, app_cb, grid, s);                       \
+    const bool qjl = a.qjl_signs != nullptr;
+    const bool tma = allow_tma && !qjl && make_tma_maps<BITS>(a, maps);
+#define TQB_LAUNCH_MMA(QT)                                                                               \
+    do {                                                                                                 \
+        if constexpr (BITS == 3) {                                                                       \
+            if (qjl) return g <= 4 ? launch_one<QT, BITS, true, false, true>(a, maps, app_cb, grid, s)   \
+                                   : launch_one<QT, BITS, false, false, true>(a, maps, app_cb, grid, s); \
+        }                                                                                                \
+        if (g <= 4) return tma ? launch_one<QT, BITS, true, true, false>(a, maps, app_cb, grid, s)       \
+                               : launch_one<QT, BITS, true, false, false>(a, maps, app_cb, grid, s);     \
+        return tma ? launch_one<QT, BITS, false, true, false>(a, maps, app_cb, grid, s)                  \
+                   : launch_one<QT, BITS, false, false, false>(a, maps, app_cb, grid, s);                \
     } while (0)
     if (q_dtype == TQB_F32) TQB_LAUNCH_MMA(float);
     else if (q_dtype == TQB_F16) TQB_LAUNCH_MMA(__half);
@@ -1082,10 +1223,11 @@ int launch_decode_mma(const tqb_decode_params* p, int num_partitions, float* par
     const int nblk = p->head_dim / kBlock;
     const bool all_outlier = p->outlier_blocks < 0 || p->outlier_blocks >= nblk;
     const bool all_normal = p->outlier_blocks == 0;
-    if (p->head_dim != kD || g > 8 || p->qjl_enabled || p->kv_len <= 0) return TQB_ERR_UNSUPPORTED;
+    if (p->head_dim != kD || g > 8 || p->kv_len <= 0) return TQB_ERR_UNSUPPORTED;
     const bool pqo4 = p->bits == 4 && p->norm_mode == TQB_MAXNORM && all_outlier;
     const bool lut3 = p->bits == 3 && (all_outlier || all_normal);
     if (!pqo4 && !lut3) return TQB_ERR_UNSUPPORTED;
+    if (p->qjl_enabled && !lut3) return TQB_ERR_UNSUPPORTED;   // the in-kernel QJL correction exists for the 3-bit kernels
     if (((uintptr_t)p->k_scales % 8) || ((uintptr_t)p->v_scales % 8)) return TQB_ERR_UNSUPPORTED;
     if (((uintptr_t)p->k_indices % 16) || ((uintptr_t)p->v_indices % 16)) return TQB_ERR_UNSUPPORTED;
     MmaArgs a{};
@@ -1114,6 +1256,13 @@ int launch_decode_mma(const tqb_decode_params* p, int num_partitions, float* par
     a.gate = gate;
     a.gate_want = gate_want;
     a.dev_signs = dev_signs;
+    if (p->qjl_enabled) {
+        if (((uintptr_t)p->qjl_signs % 4) || ((uintptr_t)p->rq % 4)) return TQB_ERR_UNSUPPORTED;
+        a.qjl_signs = reinterpret_cast<const uint32_t*>(p->qjl_signs);
+        a.qjl_norms = p->qjl_norms;
+        a.rq = p->rq;
+        a.qjl_const = (1.2533141f * (1.0f / sqrtf((float)kD))) * p->softmax_scale * 1.4426950408889634f;   // tq_attention_kernel.cu:225
+    }
     a.alias_heads = alias_heads;
     a.kv_len0 = alias_heads > 0 ? p->kv_len - p->num_kv_heads / alias_heads + 1 : p->kv_len;
     if (alias_heads > 0 && p->append_k != nullptr) return TQB_ERR_UNSUPPORTED;
