@@ -36,7 +36,8 @@ typedef enum tqb_status {
     TQB_ERR_UNSUPPORTED = 9,         /* valid for the reference, outside what this build covers */
     TQB_ERR_CUDA = 10,               /* a CUDA call failed; see tqb_last_cuda_error() */
     TQB_ERR_OUT_OF_MEMORY = 11,
-    TQB_ERR_TOO_LARGE = 12           /* exceeds a fixed capacity of the called entry point */
+    TQB_ERR_TOO_LARGE = 12,          /* exceeds a fixed capacity of the called entry point */
+    TQB_ERR_PEER_TIMEOUT = 13        /* a bounded device-side wait for another rank's data ran out */
 } tqb_status;
 
 const char *tqb_status_string(int status);
@@ -387,6 +388,33 @@ int tqb_pqo_cache_export_layer(const tqb_pqo_cache *c, int32_t layer, uint8_t *k
 int tqb_pqo_cache_attend_partial(tqb_pqo_cache *c, int32_t layer, const void *q, int32_t dtype,
                                  int32_t num_q_heads, float softmax_scale, float *out_unnorm, float *lse_out,
                                  tqb_stream_t stream);
+
+/* Sequence-parallel decode with the exchange fused into the attention kernel (no counterpart in the reference,
+ * which is single-GPU; the merge algebra is that of tq_fused_attention_reduce, tq_attention_kernel.cu:299-332).
+ * One sequence is split along the tokens over `world` <= 8 ranks of one NVLink domain, one process per GPU.  Every
+ * rank owns a receive buffer; its 64-byte CUDA IPC handle is exchanged by the host (any channel) and opened by the
+ * peers.  Per layer, tqb_pqo_cache_attend_push runs the shard-local attention: the CTA that finishes a KV head stores
+ * the head group's (un-normalised output, max, sum) record into every rank's buffer with plain global stores and
+ * releases a flag; tqb_peer_exchange_combine then acquires the flags of all ranks - each wait bounded by wait_cycles
+ * GPU clock cycles - and merges the records in local memory into out [num_q_heads, 128].  All ranks must make the
+ * same sequence of calls.  A wait that runs out is counted, zeros are written, the kernel returns and the context
+ * stays usable: tqb_peer_exchange_check reports TQB_ERR_PEER_TIMEOUT (it synchronises the device).  head_dim 128,
+ * the formats of the tensor-core kernels, every rank's shard non-empty. */
+typedef struct tqb_peer_exchange tqb_peer_exchange;
+int tqb_peer_exchange_create(int32_t world, int32_t rank, int32_t num_q_heads, int32_t head_dim, tqb_peer_exchange **out);
+void tqb_peer_exchange_destroy(tqb_peer_exchange *x);
+int tqb_peer_exchange_handle(const tqb_peer_exchange *x, void *handle64);
+/* handles: world x 64 bytes in rank order (this rank's own entry is ignored). */
+int tqb_peer_exchange_connect(tqb_peer_exchange *x, const void *handles);
+/* The same for ranks that live in ONE process (an IPC handle cannot be opened by the process that made it):
+ * `all` = the world's exchange objects in rank order. */
+int tqb_peer_exchange_connect_local(tqb_peer_exchange *x, tqb_peer_exchange *const *all);
+int tqb_pqo_cache_attend_push(tqb_pqo_cache *c, int32_t layer, const void *q, int32_t dtype, int32_t num_q_heads,
+                              float softmax_scale, tqb_peer_exchange *x, tqb_stream_t stream);
+int tqb_peer_exchange_combine(tqb_peer_exchange *x, int32_t num_kv_heads, void *out, int32_t out_dtype,
+                              int64_t wait_cycles, tqb_stream_t stream);
+long long tqb_peer_exchange_timeouts(const tqb_peer_exchange *x);
+int tqb_peer_exchange_check(const tqb_peer_exchange *x);
 
 /* compute_qjl_signs_and_norms (src/cache/tq.rs:380-411) as a kernel: residual = original - dequantized
  * for n vectors of `dim` (32, 64, 128 or 256), its L2 norm as f16 bits and the dim-wide sign sketch,

@@ -106,6 +106,15 @@ def _declare(lib):
         "tqb_pqo_cache_layer_ptrs": (c_int, [P, I, P, P, P, P]),
         "tqb_pqo_cache_export_layer": (c_int, [P, I, P, P, P, P, I, P]),
         "tqb_pqo_cache_attend_partial": (c_int, [P, I, P, I, I, F, P, P, P]),
+        "tqb_peer_exchange_create": (c_int, [I, I, I, I, P]),
+        "tqb_peer_exchange_destroy": (None, [P]),
+        "tqb_peer_exchange_handle": (c_int, [P, P]),
+        "tqb_peer_exchange_connect": (c_int, [P, P]),
+        "tqb_peer_exchange_connect_local": (c_int, [P, P]),
+        "tqb_pqo_cache_attend_push": (c_int, [P, I, P, I, I, F, P, P]),
+        "tqb_peer_exchange_combine": (c_int, [P, I, P, I, L, P]),
+        "tqb_peer_exchange_timeouts": (ctypes.c_longlong, [P]),
+        "tqb_peer_exchange_check": (c_int, [P]),
         "tqb_residual_sketch": (c_int, [I, P, P, I, P, L, P, P, L, L, L, P]),
         "tqb_qjl_logit_bias": (c_int, [I, P, P, P, P, I, I, I, I, I, I, P]),
         "tqb_tq_cache_create": (c_int, [P, P]),

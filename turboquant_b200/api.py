@@ -54,6 +54,11 @@ class TqbRuntimeError(TurboQuantError):
     """Status codes beyond the reference's five error variants (null, CUDA, ...)."""
 
 
+class PeerTimeout(TqbRuntimeError):
+    """A bounded device-side wait for another rank's data ran out (TQB_ERR_PEER_TIMEOUT)."""
+    status = 13
+
+
 _ERRORS = {c.status: c for c in (InvalidDimension, UnsupportedBits, DimensionMismatch, LayerOutOfRange, RangeOutOfBounds)}
 
 
@@ -64,6 +69,8 @@ def check(status):
     cls = _ERRORS.get(status)
     if cls is not None:
         raise cls(msg)
+    if status == PeerTimeout.status:
+        raise PeerTimeout(msg)
     err = TqbRuntimeError(f"{msg} (status {status}, cuda error {lib.tqb_last_cuda_error()})")
     err.status = status
     raise err

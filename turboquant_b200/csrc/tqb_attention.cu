@@ -25,7 +25,8 @@ namespace tqb {
 int block_cfg_check(int bits, int head_dim, int norm_mode);
 int launch_decode_mma(const tqb_decode_params* p, int num_partitions, float* partial_out, float* partial_max,
                       float* partial_sum, float sign_mag, unsigned* counters, bool counters_clean, cudaStream_t s,
-                      const int* gate = nullptr, int gate_want = 0, const float* dev_signs = nullptr, int alias_heads = 0);
+                      const int* gate = nullptr, int gate_want = 0, const float* dev_signs = nullptr, int alias_heads = 0,
+                      const PeerPush* peer = nullptr);
 
 namespace {
 
@@ -428,7 +429,7 @@ size_t tqb_decode_scratch_bytes(int32_t num_q_heads, int32_t head_dim, int32_t n
 }
 
 // alias_heads > 0: p is a causal chunk folded into heads (see tqb_chunk_attention)
-static int decode_impl(const tqb_decode_params* p, int alias_heads, tqb_stream_t stream) {
+static int decode_impl(const tqb_decode_params* p, int alias_heads, tqb_stream_t stream, const PeerPush* peer = nullptr) {
     if (!p) return TQB_ERR_NULL_POINTER;
     int st = block_cfg_check(p->bits, p->head_dim, p->norm_mode);
     if (st != TQB_OK) return st;
@@ -487,7 +488,8 @@ static int decode_impl(const tqb_decode_params* p, int alias_heads, tqb_stream_t
         // (the merge runs inside the kernel, in the CTA that finishes a KV head last)
         st = launch_decode_mma(&local, P, a.partial_out, a.partial_max, a.partial_sum, a.sign_mag,
                                partials_only ? nullptr : tickets, (p->flags & TQB_DECODE_TICKETS_ZERO) != 0, as_stream(stream),
-                               nullptr, 0, nullptr, alias_heads);
+                               nullptr, 0, nullptr, alias_heads, peer);
+        if (peer != nullptr) return st;   // the push exists in the tensor-core kernels only
         if (st == TQB_ERR_UNSUPPORTED && local.append_k != nullptr) {
             st = append_separately();
             if (st != TQB_OK) return st;
@@ -504,6 +506,14 @@ static int decode_impl(const tqb_decode_params* p, int alias_heads, tqb_stream_t
 }
 
 int tqb_decode_attention(const tqb_decode_params* p, tqb_stream_t stream) { return decode_impl(p, 0, stream); }
+}  // extern "C"
+namespace tqb {
+int decode_with_peer_push(const tqb_decode_params* p, const PeerPush& push, tqb_stream_t stream) {
+    if (p && (p->append_k || p->flags & (TQB_DECODE_PARTIALS_ONLY | TQB_DECODE_FORCE_GENERAL))) return TQB_ERR_INVALID_ARGUMENT;
+    return decode_impl(p, 0, stream, &push);
+}
+}  // namespace tqb
+extern "C" {
 
 // Causal attention of a chunk of q_len consecutive query tokens over the packed cache.  Query position i is
 // run as one more "sequence" of a batched decode whose cache rows are those of the one real sequence: grid

@@ -91,7 +91,13 @@ struct MmaArgs {
     const uint16_t* qjl_norms;
     const float* rq;
     float qjl_const;
+    // sequence-parallel decode: the merging CTA of a KV head pushes the head group's record to every rank (world == 0: off)
+    PeerPush peer;
 };
+
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
+}
 
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
@@ -1084,12 +1090,23 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
             m.dev_signs = nullptr; m.out = a.out; m.lse_out = a.lse_out;
             m.head_dim = kD; m.nblk = kD / 32; m.num_partitions = a.num_partitions; m.rotate = 1;
             m.out_dtype = a.out_dtype; m.sign_mag = a.sign_mag;
-            // all heads of the group at once when the weight table fits the (now idle) ring memory
+            m.num_copies = a.peer.world; m.num_q_heads = a.hq;
+#pragma unroll
+            for (int c = 0; c < kMaxPeers; ++c) m.copy_rec[c] = a.peer.rec[c];
+            // all heads of the group at once when the weight table fits the (now idle) ring memory (the host
+            // checks that it does before it asks for a peer push)
             if ((size_t)(16 + g * a.num_partitions) * sizeof(float) <= (size_t)kWarps * G::kRingB)
                 merge_group128(m, kvh * g, g, tid, reinterpret_cast<float*>(s_raw));
             else
                 for (int hh = warp; hh < g; hh += kWarps) merge_head(m, kvh * g + hh, lane, 0, 1);   // one warp per query head
             if (tid == 0) a.counters[kvh] = 0u;   // ready for the next launch
+            if (a.peer.world > 0) {
+                // the records are in the peers' memory: make them visible system-wide, then release this KV head's flag
+                // on every rank (plain stores over NVLink; nobody is waited for here)
+                __threadfence_system();
+                __syncthreads();
+                if (tid < a.peer.world) st_release_sys(a.peer.flag[tid] + kvh, a.peer.seq);
+            }
         }
     }
 }
@@ -1218,7 +1235,7 @@ int launch(const MmaArgs& a, int g, int q_dtype, bool allow_tma, const Codebook&
 // caller vouches for them (counters_clean).
 int launch_decode_mma(const tqb_decode_params* p, int num_partitions, float* partial_out, float* partial_max,
                       float* partial_sum, float sign_mag, unsigned* counters, bool counters_clean, cudaStream_t s,
-                      const int* gate, int gate_want, const float* dev_signs, int alias_heads) {
+                      const int* gate, int gate_want, const float* dev_signs, int alias_heads, const PeerPush* peer) {
     const int g = p->num_q_heads / p->num_kv_heads;
     const int nblk = p->head_dim / kBlock;
     const bool all_outlier = p->outlier_blocks < 0 || p->outlier_blocks >= nblk;
@@ -1266,6 +1283,14 @@ int launch_decode_mma(const tqb_decode_params* p, int num_partitions, float* par
     a.alias_heads = alias_heads;
     a.kv_len0 = alias_heads > 0 ? p->kv_len - p->num_kv_heads / alias_heads + 1 : p->kv_len;
     if (alias_heads > 0 && p->append_k != nullptr) return TQB_ERR_UNSUPPORTED;
+    if (peer != nullptr && peer->world > 0) {
+        // the push happens in the CTA-wide merge, which needs its weight table to fit the idle ring memory
+        const size_t ring = (size_t)kWarps * (p->bits == 4 ? Geo<4>::kRingB : Geo<3>::kRingB);
+        if (counters == nullptr || peer->world > kMaxPeers || p->num_kv_heads > kPeerFlagHeads ||
+            (size_t)(16 + g * num_partitions) * sizeof(float) > ring)
+            return TQB_ERR_UNSUPPORTED;
+        a.peer = *peer;
+    }
     a.counters = counters;
     a.out = p->out;
     a.lse_out = p->lse_out;

@@ -72,4 +72,19 @@ __device__ __forceinline__ uint32_t extract_bits(uint32_t w0, uint32_t w1, int b
 
 inline cudaStream_t as_stream(tqb_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
 
+// Sequence-parallel decode, fused exchange: where the CTA that finishes a KV head stores the head group's shard-local
+// record (un-normalised outputs, then (max, sum) pairs) - once per rank of the group, into that rank's receive buffer
+// (peer memory mapped into this process; plain stores, no bulk or multicast copy) - and the flag words it then
+// releases.  world == 0: off.
+constexpr int kMaxPeers = 8;
+constexpr int kPeerFlagHeads = 64;     // flag words per source rank (one per KV head)
+struct PeerPush {
+    int world;
+    unsigned seq;                      // value written to the flags: the exchange's step counter
+    float* rec[kMaxPeers];             // this rank's record inside rank p's receive buffer
+    unsigned* flag[kMaxPeers];         // this rank's flag row [kPeerFlagHeads] inside rank p's receive buffer
+};
+// Decode attention (as tqb_decode_attention with lse_out semantics) whose merge CTAs push the result to the peers.
+int decode_with_peer_push(const tqb_decode_params* p, const PeerPush& push, tqb_stream_t stream);
+
 }  // namespace tqb

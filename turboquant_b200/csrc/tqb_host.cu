@@ -284,8 +284,37 @@ struct tqb_pqo_cache {
         p.flags = TQB_DECODE_TICKETS_ZERO;
         return tqb_chunk_attention(&p, q_len, s);
     }
+    // Shard-local attention whose merging CTAs push the record to the ranks of a peer exchange (no append).
+    int attend_push(int layer, const void* q_dev, int dtype, int num_q_heads, float softmax_scale, const PeerPush& push,
+                    float* local_rec, cudaStream_t s) {
+        Layer& l = layers[layer];
+        tqb_decode_params p{};
+        p.q = q_dev;
+        p.k_indices = l.ki; p.k_scales = l.ks; p.v_indices = l.vi; p.v_scales = l.vs;
+        p.num_q_heads = cfg.batch * num_q_heads;
+        p.out = local_rec;                                        // not written through these two: the kernel stores the
+        p.lse_out = local_rec + (size_t)p.num_q_heads * cfg.head_dim;   // record through the push targets
+        p.q_dtype = dtype;
+        p.out_dtype = TQB_F32;
+        p.bits = cfg.bits; p.head_dim = cfg.head_dim; p.norm_mode = cfg.norm_mode; p.outlier_blocks = cfg.outlier_blocks;
+        p.num_kv_heads = heads;
+        p.kv_len = (int32_t)l.len;
+        p.kv_stride = (int32_t)l.cap;
+        p.num_partitions = tqb_decode_num_partitions(heads, (int32_t)l.len);
+        p.softmax_scale = softmax_scale;
+        const size_t need = tqb_decode_scratch_bytes(p.num_q_heads, cfg.head_dim, p.num_partitions);
+        TQB_TRY(prepare_scratch(scratch, ticket_heads, need, p.num_q_heads, cfg.head_dim, p.num_partitions, s));
+        p.scratch = scratch.p;
+        p.scratch_bytes = scratch.bytes;
+        p.flags = TQB_DECODE_TICKETS_ZERO;
+        return decode_with_peer_push(&p, push, s);
+    }
     int ticket_heads = -1;   // head count the zeroed ticket area of `scratch` was sized for
 };
+
+namespace tqb {
+int peer_exchange_begin_step(tqb_peer_exchange* x, int num_q_heads, PeerPush& push, float** local_rec);
+}
 
 extern "C" {
 
@@ -417,6 +446,19 @@ int tqb_pqo_cache_attend_partial(tqb_pqo_cache* c, int32_t layer, const void* q,
     if (!q || !out_unnorm || !lse_out) return TQB_ERR_NULL_POINTER;
     if (num_q_heads <= 0 || num_q_heads % c->cfg.num_kv_heads != 0) return TQB_ERR_INVALID_ARGUMENT;
     return c->attend(layer, q, dtype, num_q_heads, softmax_scale, out_unnorm, TQB_F32, lse_out, as_stream(stream));
+}
+
+int tqb_pqo_cache_attend_push(tqb_pqo_cache* c, int32_t layer, const void* q, int32_t dtype, int32_t num_q_heads,
+                              float softmax_scale, tqb_peer_exchange* x, tqb_stream_t stream) {
+    TQB_TRY(check_layer(c, layer));
+    if (!q || !x) return TQB_ERR_NULL_POINTER;
+    if (dtype != TQB_F32 && dtype != TQB_F16 && dtype != TQB_BF16) return TQB_ERR_INVALID_ARGUMENT;
+    if (num_q_heads <= 0 || num_q_heads % c->cfg.num_kv_heads != 0) return TQB_ERR_INVALID_ARGUMENT;
+    if (c->layers[layer].len <= 0) return TQB_ERR_RANGE_OUT_OF_BOUNDS;   // every rank must hold a part of the sequence
+    PeerPush push;
+    float* local_rec = nullptr;
+    TQB_TRY(peer_exchange_begin_step(x, c->cfg.batch * num_q_heads, push, &local_rec));
+    return c->attend_push(layer, q, dtype, num_q_heads, softmax_scale, push, local_rec, as_stream(stream));
 }
 
 int tqb_pqo_cache_dequantize_full(tqb_pqo_cache* c, int32_t layer, void* k_out, void* v_out, int32_t dtype,

@@ -20,6 +20,10 @@ struct MergeArgs {
     int head_dim, nblk, num_partitions, rotate;
     int out_dtype;
     float sign_mag;
+    // merge_group128 only: when num_copies > 0 the un-normalised f32 result and the (max, sum) pairs go to these
+    // record buffers ([num_q_heads, 128] floats, then [num_q_heads, 2]) instead of out / lse_out
+    int num_copies, num_q_heads;
+    float* copy_rec[kMaxPeers];
 };
 
 namespace merge_detail {
@@ -160,6 +164,10 @@ __device__ __forceinline__ void merge_group128(const MergeArgs& a, int head0, in
         if (hh < g) {
             float r = acc[hh];
             if (a.rotate) r = wht32(r * sg, lane) * inv_sqrt;
+            if (a.num_copies > 0) {
+                for (int c = 0; c < a.num_copies; ++c) a.copy_rec[c][(size_t)(head0 + hh) * D + tid] = r;
+                continue;
+            }
             if (a.lse_out == nullptr) {
                 const float L = s_L[hh];
                 r *= L > 0.0f ? 1.0f / L : 0.0f;
@@ -167,7 +175,14 @@ __device__ __forceinline__ void merge_group128(const MergeArgs& a, int head0, in
             store_out(a.out, a.out_dtype, (size_t)(head0 + hh) * D + tid, r);
         }
     }
-    if (a.lse_out != nullptr && tid < g) {
+    if (a.num_copies > 0) {
+        if (tid < g)
+            for (int c = 0; c < a.num_copies; ++c) {
+                float* lse = a.copy_rec[c] + (size_t)a.num_q_heads * D;
+                lse[(head0 + tid) * 2] = s_M[tid];
+                lse[(head0 + tid) * 2 + 1] = s_L[tid];
+            }
+    } else if (a.lse_out != nullptr && tid < g) {
         a.lse_out[(head0 + tid) * 2] = s_M[tid];
         a.lse_out[(head0 + tid) * 2 + 1] = s_L[tid];
     }

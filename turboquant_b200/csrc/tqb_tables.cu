@@ -111,6 +111,7 @@ const char* tqb_status_string(int s) {
         case TQB_ERR_INVALID_ARGUMENT: return "invalid argument";
         case TQB_ERR_MISALIGNED: return "misaligned pointer";
         case TQB_ERR_UNSUPPORTED: return "unsupported configuration";
+        case TQB_ERR_PEER_TIMEOUT: return "a bounded wait for another rank timed out";
         case TQB_ERR_CUDA: return "CUDA error";
         case TQB_ERR_OUT_OF_MEMORY: return "out of device memory";
         case TQB_ERR_TOO_LARGE: return "size exceeds the entry point's fixed capacity";

@@ -1,12 +1,15 @@
 """Multi-GPU plumbing for the decode path (one process per GPU, torch.distributed).
 
-Two ways the path shards (both without any collective inside a kernel):
+Two ways the path shards:
   * (batch, KV head) units are independent: `shard_range` gives each rank a contiguous slice and
     nothing is exchanged;
   * one long sequence is split along the tokens: every rank attends over its shard and produces the
     un-normalised output and the (max, sum) pair per query head; `gather_partials` all-gathers
     them (NCCL over NVLink on GPUs, gloo in CPU tests) and `tqb_lse_combine` merges them with
     the log-sum-exp algebra of tq_fused_attention_reduce (tq_attention_kernel.cu:299-332).
+    `FusedSequenceParallelDecoder` replaces the all-gather by stores from inside the attention kernel: the CTA that
+    finishes a KV head writes the head group's record into every rank's receive buffer over NVLink (peer memory
+    shared through CUDA IPC) and a combine kernel waits, with a bound, for the flags of all ranks.
 """
 import torch
 import torch.distributed as dist
@@ -81,3 +84,65 @@ class SequenceParallelDecoder:
         self.attend_local(layer, q, softmax_scale)
         self.exchange()
         return self.combine()
+
+
+class FusedSequenceParallelDecoder:
+    """Sequence-parallel decode with the exchange fused into the attention kernel (tqb_peer_exchange_* in the C ABI).
+
+    The receive buffer of every rank is created by the library, its CUDA IPC handle travels through
+    `dist.all_gather_object` once, at construction; after that a layer is two launches (attention with the push,
+    combine) and no collective call.  `wait_cycles` bounds every device-side wait (GPU clock cycles, ~0.5 s by default);
+    `check()` raises PeerTimeout if one ever ran out."""
+
+    exchange_kind = "records pushed into every rank's buffer by the attention kernel's merging CTAs (plain NVLink stores), flags, combine kernel"
+
+    def __init__(self, cache, num_q_heads, group=None, out_dtype=torch.float32, device=None, wait_cycles=1 << 30):
+        import ctypes
+        from ._lib import lib
+        from .api import check
+        self.cache, self.group, self.out_dtype, self._lib = cache, group, out_dtype, lib
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.nq = num_q_heads
+        self.hq = cache.config.batch * num_q_heads
+        self.hkv = cache.config.batch * cache.config.num_kv_heads
+        self.wait_cycles = int(wait_cycles)
+        d = cache.config.head_dim
+        dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self._x = ctypes.c_void_p()
+        check(lib.tqb_peer_exchange_create(self.world, self.rank, self.hq, d, ctypes.byref(self._x)))
+        mine = ctypes.create_string_buffer(64)
+        check(lib.tqb_peer_exchange_handle(self._x, mine))
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(mine.raw), group=group)
+        check(lib.tqb_peer_exchange_connect(self._x, b"".join(handles)))
+        dist.barrier(group=group)
+        self.out = torch.empty((self.hq, d), dtype=out_dtype, device=dev)
+
+    def __del__(self):
+        x = getattr(self, "_x", None)
+        if x:
+            self._lib.tqb_peer_exchange_destroy(x)
+            self._x = None
+
+    def attend_local(self, layer, q, softmax_scale):
+        from .api import check, _dtype_code, _stream
+        q = q.contiguous()
+        check(self._lib.tqb_pqo_cache_attend_push(self.cache._h, layer, q.data_ptr(), _dtype_code(q.dtype), self.nq,
+                                                  softmax_scale, self._x, _stream()))
+
+    def exchange(self):
+        pass   # the attention kernel has already stored the records where they are needed
+
+    def combine(self):
+        from .api import check, _dtype_code, _stream
+        check(self._lib.tqb_peer_exchange_combine(self._x, self.hkv, self.out.data_ptr(), _dtype_code(self.out_dtype),
+                                                  self.wait_cycles, _stream()))
+        return self.out
+
+    def attend(self, layer, q, softmax_scale):
+        self.attend_local(layer, q, softmax_scale)
+        return self.combine()
+
+    def check(self):
+        from .api import check
+        check(self._lib.tqb_peer_exchange_check(self._x))
