@@ -266,8 +266,9 @@ typedef struct tqb_decode_params {
 } tqb_decode_params;
 
 /* flags: stop after the split-K pass and leave the per-partition (max, sum, out) partials in
- * `scratch`; `out` is not written.  Scratch layout: merge tickets (one u32 per query head, rounded up to
- * 256 bytes), then [num_q_heads, P, head_dim] f32, then [num_q_heads, P] max, then sum. */
+ * `scratch`; `out` is not written.  Scratch layout: merge tickets (1 + G u32 per query head, rounded up to
+ * 256 bytes; G = 0 for P <= 16, else ceil(P / 8): the partition groups of the two-level merge), then
+ * [num_q_heads, P, head_dim] f32, then [num_q_heads, P] max, then sum, then the group partials. */
 #define TQB_DECODE_PARTIALS_ONLY 1
 /* flags: always take the general (SIMT, any shape) kernel; used to cross-check the tensor-core kernels. */
 #define TQB_DECODE_FORCE_GENERAL 2

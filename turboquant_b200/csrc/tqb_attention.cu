@@ -26,7 +26,7 @@ int block_cfg_check(int bits, int head_dim, int norm_mode);
 int launch_decode_mma(const tqb_decode_params* p, int num_partitions, float* partial_out, float* partial_max,
                       float* partial_sum, float sign_mag, unsigned* counters, bool counters_clean, cudaStream_t s,
                       const int* gate = nullptr, int gate_want = 0, const float* dev_signs = nullptr, int alias_heads = 0,
-                      const PeerPush* peer = nullptr);
+                      const PeerPush* peer = nullptr, float* group_area = nullptr);
 
 namespace {
 
@@ -419,13 +419,17 @@ int32_t tqb_decode_num_partitions(int32_t num_kv_heads, int32_t kv_len) {
     return (int32_t)p;
 }
 
-// Scratch layout: [merge tickets: one u32 per query head, rounded up to 256 bytes][partial out]
-// [partial max][partial sum].
-static size_t ticket_bytes(int32_t num_q_heads) { return (sizeof(unsigned) * (size_t)num_q_heads + 255) / 256 * 256; }
+// Scratch layout: [merge tickets: (1 + G) u32 per query head, rounded up to 256 bytes][partial out [hq, P, D]]
+// [partial max [hq, P]][partial sum [hq, P]][group partials: out [hq, G, D], max [hq, G], sum [hq, G]], where
+// G = merge_groups(P) is the number of partition groups of the two-level merge (0 up to kMergeGroup partitions).
+static size_t ticket_bytes(int32_t num_q_heads, int32_t num_partitions) {
+    return (sizeof(unsigned) * (size_t)num_q_heads * (1 + merge_groups(num_partitions)) + 255) / 256 * 256;
+}
 
 size_t tqb_decode_scratch_bytes(int32_t num_q_heads, int32_t head_dim, int32_t num_partitions) {
     if (num_q_heads <= 0 || head_dim <= 0 || num_partitions <= 0) return 0;
-    return ticket_bytes(num_q_heads) + sizeof(float) * (size_t)num_q_heads * num_partitions * ((size_t)head_dim + 2);
+    return ticket_bytes(num_q_heads, num_partitions) +
+           sizeof(float) * (size_t)num_q_heads * (num_partitions + merge_groups(num_partitions)) * ((size_t)head_dim + 2);
 }
 
 // alias_heads > 0: p is a causal chunk folded into heads (see tqb_chunk_attention)
@@ -455,10 +459,11 @@ static int decode_impl(const tqb_decode_params* p, int alias_heads, tqb_stream_t
     a.q = p->q;
     a.k_idx = p->k_indices; a.k_sc = p->k_scales; a.v_idx = p->v_indices; a.v_sc = p->v_scales;
     unsigned* tickets = reinterpret_cast<unsigned*>(p->scratch);
-    float* sc = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(p->scratch) + ticket_bytes(p->num_q_heads));
+    float* sc = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(p->scratch) + ticket_bytes(p->num_q_heads, P));
     a.partial_out = sc;
     a.partial_max = sc + (size_t)p->num_q_heads * P * p->head_dim;
     a.partial_sum = a.partial_max + (size_t)p->num_q_heads * P;
+    float* group_area = a.partial_sum + (size_t)p->num_q_heads * P;
     a.qjl_signs = p->qjl_signs; a.qjl_norms = p->qjl_norms; a.rq = p->rq; a.qjl_enabled = p->qjl_enabled ? 1 : 0;
     a.dev_codebook = nullptr; a.dev_signs = nullptr;
     a.hq = p->num_q_heads; a.hkv = p->num_kv_heads; a.head_dim = p->head_dim; a.nblk = p->head_dim / kBlock;
@@ -488,13 +493,14 @@ static int decode_impl(const tqb_decode_params* p, int alias_heads, tqb_stream_t
         // (the merge runs inside the kernel, in the CTA that finishes a KV head last)
         st = launch_decode_mma(&local, P, a.partial_out, a.partial_max, a.partial_sum, a.sign_mag,
                                partials_only ? nullptr : tickets, (p->flags & TQB_DECODE_TICKETS_ZERO) != 0, as_stream(stream),
-                               nullptr, 0, nullptr, alias_heads, peer);
+                               nullptr, 0, nullptr, alias_heads, peer, group_area);
         if (peer != nullptr) return st;   // the push exists in the tensor-core kernels only
         if (st == TQB_ERR_UNSUPPORTED && local.append_k != nullptr) {
             st = append_separately();
             if (st != TQB_OK) return st;
             st = launch_decode_mma(&local, P, a.partial_out, a.partial_max, a.partial_sum, a.sign_mag,
-                                   partials_only ? nullptr : tickets, (p->flags & TQB_DECODE_TICKETS_ZERO) != 0, as_stream(stream));
+                                   partials_only ? nullptr : tickets, (p->flags & TQB_DECODE_TICKETS_ZERO) != 0, as_stream(stream),
+                                   nullptr, 0, nullptr, 0, nullptr, group_area);
         }
         if (st != TQB_ERR_UNSUPPORTED) return st;
     }

@@ -69,7 +69,10 @@ struct MmaArgs {
     float sign_mag;
     float lut[8];     // 3-bit path: centroid / kappa
     // fused merge: the CTA that finishes a KV head last combines its partitions (counters == nullptr: off)
-    unsigned* counters;   // [hkv], zero before the launch; left zero by it
+    unsigned* counters;   // [hq] (one per KV head used) then [hkv][merge_groups(P)]: zero before the launch; left zero by it
+    float* group_out;     // two-level merge: group partials [hq][merge_groups(P)][128], max and sum [hq][merge_groups(P)]
+    float* group_max;
+    float* group_sum;
     void* out;
     float* lse_out;
     int out_dtype;
@@ -1076,37 +1079,66 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
         }
     }
     if (a.counters != nullptr) {
-        // Last-arriver merge: every CTA publishes its partial (fence), then takes a ticket; the CTA that
-        // draws the last ticket of its KV head sees all partials of that head and merges them.
+        // Last-arriver merge: every CTA publishes its partial (fence), then takes a ticket; the CTA that draws the last
+        // ticket sees all partials it merges.  Up to 2 kMergeGroup partitions: one level, the last CTA of the KV head
+        // merges them.  More: the last CTA of each group of kMergeGroup partitions merges its group into one more
+        // partial, then takes a ticket of the KV head, and the last of those merges the group results.
         __shared__ int s_last;
+        const int P = a.num_partitions;
+        const int ngroups = merge_groups(P);
+        MergeArgs m;
+        m.partial_out = a.partial_out; m.partial_max = a.partial_max; m.partial_sum = a.partial_sum;
+        m.dev_signs = nullptr; m.out = a.out; m.lse_out = a.lse_out;
+        m.head_dim = kD; m.nblk = kD / 32; m.num_partitions = P; m.rotate = 1;
+        m.out_dtype = a.out_dtype; m.sign_mag = a.sign_mag;
+        m.num_copies = a.peer.world; m.num_q_heads = a.hq;
+#pragma unroll
+        for (int c = 0; c < kMaxPeers; ++c) m.copy_rec[c] = a.peer.rec[c];
+        m.group_out = a.group_out; m.group_max = a.group_max; m.group_sum = a.group_sum;
+        float* s_work = reinterpret_cast<float*>(s_raw);   // the ring memory is idle by now
+        bool merged = false;
         __threadfence();
         __syncthreads();
-        if (tid == 0) s_last = atomicAdd(a.counters + kvh, 1u) == (unsigned)(a.num_partitions - 1) ? 1 : 0;
-        __syncthreads();
-        if (s_last) {
-            __threadfence();
-            MergeArgs m;
-            m.partial_out = a.partial_out; m.partial_max = a.partial_max; m.partial_sum = a.partial_sum;
-            m.dev_signs = nullptr; m.out = a.out; m.lse_out = a.lse_out;
-            m.head_dim = kD; m.nblk = kD / 32; m.num_partitions = a.num_partitions; m.rotate = 1;
-            m.out_dtype = a.out_dtype; m.sign_mag = a.sign_mag;
-            m.num_copies = a.peer.world; m.num_q_heads = a.hq;
-#pragma unroll
-            for (int c = 0; c < kMaxPeers; ++c) m.copy_rec[c] = a.peer.rec[c];
-            // all heads of the group at once when the weight table fits the (now idle) ring memory (the host
-            // checks that it does before it asks for a peer push)
-            if ((size_t)(16 + g * a.num_partitions) * sizeof(float) <= (size_t)kWarps * G::kRingB)
-                merge_group128(m, kvh * g, g, tid, reinterpret_cast<float*>(s_raw));
-            else
-                for (int hh = warp; hh < g; hh += kWarps) merge_head(m, kvh * g + hh, lane, 0, 1);   // one warp per query head
-            if (tid == 0) a.counters[kvh] = 0u;   // ready for the next launch
-            if (a.peer.world > 0) {
-                // the records are in the peers' memory: make them visible system-wide, then release this KV head's flag
-                // on every rank (plain stores over NVLink; nobody is waited for here)
-                __threadfence_system();
-                __syncthreads();
-                if (tid < a.peer.world) st_release_sys(a.peer.flag[tid] + kvh, a.peer.seq);
+        if (ngroups == 0) {
+            if (tid == 0) s_last = atomicAdd(a.counters + kvh, 1u) == (unsigned)(P - 1) ? 1 : 0;
+            __syncthreads();
+            if (s_last) {
+                __threadfence();
+                merge_group128<false>(m, kvh * g, g, tid, s_work, 0, P, P);
+                if (tid == 0) a.counters[kvh] = 0u;   // ready for the next launch
+                merged = true;
             }
+        } else {
+            const int grp = part / kMergeGroup;
+            const int gsize = min(kMergeGroup, P - grp * kMergeGroup);
+            unsigned* c1 = a.counters + a.hq + kvh * ngroups + grp;
+            if (tid == 0) s_last = atomicAdd(c1, 1u) == (unsigned)(gsize - 1) ? 1 : 0;
+            __syncthreads();
+            if (s_last) {
+                __threadfence();
+                merge_group128<true>(m, kvh * g, g, tid, s_work, grp * kMergeGroup, gsize, P, grp, ngroups);
+                if (tid == 0) *c1 = 0u;
+                __threadfence();
+                __syncthreads();
+                if (tid == 0) s_last = atomicAdd(a.counters + kvh, 1u) == (unsigned)(ngroups - 1) ? 1 : 0;
+                __syncthreads();
+                if (s_last) {
+                    __threadfence();
+                    m.partial_out = a.group_out; m.partial_max = a.group_max; m.partial_sum = a.group_sum;
+                    merge_group128<false>(m, kvh * g, g, tid, s_work, 0, ngroups, ngroups);
+                    if (tid == 0) a.counters[kvh] = 0u;
+                    merged = true;
+                }
+            }
+        }
+        if (merged && a.peer.world > 0) {
+            // the records are in the peers' memory: make them visible system-wide, then release this KV head's flag
+            // on every rank (plain stores over NVLink; nobody is waited for here)
+            __threadfence_system();
+            __syncthreads();
+#pragma unroll
+            for (int c = 0; c < kMaxPeers; ++c)
+                if (tid == c && c < a.peer.world) st_release_sys(a.peer.flag[c] + kvh, a.peer.seq);
         }
     }
 }
@@ -1235,7 +1267,8 @@ int launch(const MmaArgs& a, int g, int q_dtype, bool allow_tma, const Codebook&
 // caller vouches for them (counters_clean).
 int launch_decode_mma(const tqb_decode_params* p, int num_partitions, float* partial_out, float* partial_max,
                       float* partial_sum, float sign_mag, unsigned* counters, bool counters_clean, cudaStream_t s,
-                      const int* gate, int gate_want, const float* dev_signs, int alias_heads, const PeerPush* peer) {
+                      const int* gate, int gate_want, const float* dev_signs, int alias_heads, const PeerPush* peer,
+                      float* group_area) {
     const int g = p->num_q_heads / p->num_kv_heads;
     const int nblk = p->head_dim / kBlock;
     const bool all_outlier = p->outlier_blocks < 0 || p->outlier_blocks >= nblk;
@@ -1284,19 +1317,22 @@ int launch_decode_mma(const tqb_decode_params* p, int num_partitions, float* par
     a.kv_len0 = alias_heads > 0 ? p->kv_len - p->num_kv_heads / alias_heads + 1 : p->kv_len;
     if (alias_heads > 0 && p->append_k != nullptr) return TQB_ERR_UNSUPPORTED;
     if (peer != nullptr && peer->world > 0) {
-        // the push happens in the CTA-wide merge, which needs its weight table to fit the idle ring memory
-        const size_t ring = (size_t)kWarps * (p->bits == 4 ? Geo<4>::kRingB : Geo<3>::kRingB);
-        if (counters == nullptr || peer->world > kMaxPeers || p->num_kv_heads > kPeerFlagHeads ||
-            (size_t)(16 + g * num_partitions) * sizeof(float) > ring)
-            return TQB_ERR_UNSUPPORTED;
+        if (counters == nullptr || peer->world > kMaxPeers || p->num_kv_heads > kPeerFlagHeads) return TQB_ERR_UNSUPPORTED;
         a.peer = *peer;
     }
     a.counters = counters;
     a.out = p->out;
     a.lse_out = p->lse_out;
     a.out_dtype = p->out_dtype;
+    const int ngroups = merge_groups(num_partitions);
+    if (counters != nullptr && ngroups > 0) {
+        if (group_area == nullptr) return TQB_ERR_INVALID_ARGUMENT;
+        a.group_out = group_area;
+        a.group_max = group_area + (size_t)p->num_q_heads * ngroups * kD;
+        a.group_sum = a.group_max + (size_t)p->num_q_heads * ngroups;
+    }
     if (counters != nullptr && !counters_clean) {
-        cudaError_t e = cudaMemsetAsync(counters, 0, sizeof(unsigned) * (size_t)p->num_kv_heads, s);
+        cudaError_t e = cudaMemsetAsync(counters, 0, sizeof(unsigned) * (size_t)p->num_q_heads * (1 + ngroups), s);
         if (e != cudaSuccess) { set_cuda_error(e); return TQB_ERR_CUDA; }
     }
     dim3 grid(p->num_kv_heads, num_partitions);

@@ -55,8 +55,9 @@ struct DevBuf {
 // ---------------------------------------------------------------------------------------
 // PqoCache
 // ---------------------------------------------------------------------------------------
-// Grows the decode scratch when needed and keeps its ticket area (the first bytes) zero: it is cleared
-// when the buffer is new or the head count changed; completed decode calls leave it zero.
+// Grows the decode scratch when needed and keeps its ticket area (the first bytes) zero: it is cleared when the
+// buffer is new or the (head count, partition count) pair it was laid out for changed - the ticket area's extent
+// depends on both; completed decode calls leave it zero.
 static int prepare_scratch(DevBuf& scratch, int& ticket_heads, size_t need, int num_q_heads, int head_dim,
                            int num_partitions, cudaStream_t s) {
     if (need > scratch.bytes) {
@@ -64,10 +65,11 @@ static int prepare_scratch(DevBuf& scratch, int& ticket_heads, size_t need, int 
         TQB_TRY(scratch.reserve(need + need / 4));
         ticket_heads = -1;
     }
-    if (ticket_heads != num_q_heads) {
+    const int key = num_q_heads * 4096 + num_partitions;
+    if (ticket_heads != key) {
         const size_t partials = sizeof(float) * (size_t)num_q_heads * num_partitions * ((size_t)head_dim + 2);
-        TQB_CUDA(cudaMemsetAsync(scratch.p, 0, need - partials, s));
-        ticket_heads = num_q_heads;
+        TQB_CUDA(cudaMemsetAsync(scratch.p, 0, need - partials, s));   // at least the ticket area at the start
+        ticket_heads = key;
     }
     return TQB_OK;
 }
