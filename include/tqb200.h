@@ -281,8 +281,13 @@ typedef struct tqb_decode_params {
  * when kv_stride is odd or a cache array is not 16-byte aligned. */
 #define TQB_DECODE_TMA 8
 
+/* flags (tqb_chunk_attention only): fold the chunk into decode launches (one per query token, see below) instead of
+ * running the chunk kernel; the cross-check of that kernel. */
+#define TQB_DECODE_FOLD_CHUNK 16
+
 /* Diagnostic: how many bounded waits on a staged tile ran out on the current device since the library was
- * loaded (synchronises the device).  Always 0 in a healthy run; -1 on a CUDA error.  No reference counterpart. */
+ * loaded (synchronises the device).  Always 0 in a healthy run; -1 on a CUDA error.  A non-zero count invalidates
+ * the outputs of the TQB_DECODE_TMA calls since the last check.  No reference counterpart. */
 long long tqb_decode_stage_timeouts(void);
 
 /* Partitions the library would use for this shape, and the scratch it then needs. */
@@ -294,13 +299,19 @@ int tqb_decode_attention(const tqb_decode_params *p, tqb_stream_t stream);
  * stored, e.g. by tqb_block_quantize_pair or tqb_pqo_cache_prefill).  No counterpart kernel in the reference:
  * its prefill dequantizes the whole cache and hands it to the engine's attention (src/cache/pqo.rs:184-200,
  * src/cache/common.rs:16-62).
+ * head_dim 128, GQA group 1 / 2 / 4 / 8, PQO4 or a 3-bit format of the tensor-core kernels, no QJL: a dedicated kernel
+ * on the tcgen05 tensor cores (128 query rows per CTA, every K / V tile unpacked once per CTA; scratch unused).
+ * Everything else, or TQB_DECODE_FOLD_CHUNK: the chunk is folded into the decode kernels, one grid head per query
+ * token.  tqb_chunk_umma_timeouts() counts bounded waits of the dedicated kernel that ran out (always 0 in a healthy
+ * run; a non-zero count invalidates the outputs since the last check; synchronises the device).
  *   q, out   [q_len, num_q_heads, head_dim] (token-major); query token i attends to the first
  *            kv_len - q_len + i + 1 tokens, so p->kv_len counts the chunk and must be >= q_len.
  *   scratch  >= tqb_decode_scratch_bytes(num_q_heads * q_len, head_dim, P), with P = p->num_partitions or
- *            tqb_decode_num_partitions(num_kv_heads * q_len, kv_len) when that is 0.
+ *            tqb_decode_num_partitions(num_kv_heads * q_len, kv_len) when that is 0 (used by the folded path).
  *   lse_out  [q_len, num_q_heads][2] when given; append_k / append_v must be NULL; rq (QJL) is
  *            [q_len, num_q_heads, head_dim].  All other fields as for tqb_decode_attention. */
 int tqb_chunk_attention(const tqb_decode_params *p, int32_t q_len, tqb_stream_t stream);
+long long tqb_chunk_umma_timeouts(void);
 
 /* tqb_decode_attention for callers that cannot allocate device memory.  No counterpart in the
  * reference (there the caller always allocates the partial buffers, src/cache/cuda/attention.rs:65-77).

@@ -394,15 +394,22 @@ def test_packed_shard_merge_equals_plain_shard_merge():
     assert torch.equal(got, want)
 
 
+@pytest.mark.parametrize("fold", [False, True])
 @pytest.mark.parametrize("bits,hq,hkv,past,q_len,dtype,general", [
-    (4, 8, 2, 300, 17, torch.bfloat16, False),     # tensor-core kernel, g = 4
-    (3, 4, 2, 0, 33, torch.float32, False),        # no past: the first query sees one token; empty partitions
+    (4, 8, 2, 300, 17, torch.bfloat16, False),     # g = 4
+    (3, 4, 2, 0, 33, torch.float32, False),        # no past: the first query sees one token
     (4, 16, 2, 1000, 5, torch.float16, False),     # g = 8
     (4, 4, 4, 64, 9, torch.float32, True),         # general kernel
-    (3, 6, 2, 129, 12, torch.bfloat16, False),     # g = 3
+    (3, 6, 2, 129, 12, torch.bfloat16, False),     # g = 3: folded into decode launches whatever `fold` says
+    (4, 32, 8, 700, 150, torch.bfloat16, False),   # several row tiles and cache tiles per CTA, ragged ends
+    (3, 16, 8, 65, 130, torch.float32, False),     # g = 2, 3-bit
+    (4, 2, 2, 40, 200, torch.float32, False),      # g = 1
 ])
-def test_chunk_attention_is_causal_decode_per_query_token(bits, hq, hkv, past, q_len, dtype, general):
-    # prefill chunk over the packed cache: query token i must equal a decode step that sees past + i + 1 tokens
+def test_chunk_attention_is_causal_decode_per_query_token(bits, hq, hkv, past, q_len, dtype, general, fold):
+    # prefill chunk over the packed cache: query token i must equal a decode step that sees past + i + 1 tokens.
+    # fold = False: the dedicated tcgen05 kernel where it applies (128 query rows per CTA; P and the dequantized V go
+    # through f16, so it agrees with the oracle to a few 1e-4, inside the 2e-3 contract); fold = True: the chunk as
+    # one decode grid head per query token (same kernels as decode: a few 1e-5).
     rng = np.random.default_rng(bits * 100 + hq + past + q_len)
     kv_len, stride, d = past + q_len, past + q_len + 7, 128
     k = rng.standard_normal((hkv * stride, d)).astype(np.float32)
@@ -413,18 +420,26 @@ def test_chunk_attention_is_causal_decode_per_query_token(bits, hq, hkv, past, q
     q = torch.from_numpy((rng.standard_normal((q_len, hq, d)) / np.sqrt(d)).astype(np.float32)).to(dtype)
     scale = 1.0 / np.sqrt(d)
     got = tq.chunk_attention(q.cuda(), ki, ks, vi, vs, kv_len, bits, scale, out_dtype=torch.float32,
-                             force_general=general).cpu().numpy()
+                             force_general=general, fold=fold).cpu().numpy()
     assert got.shape == (q_len, hq, d)
     kin, ksn, vin, vsn = ki.cpu().numpy(), u16(ks), vi.cpu().numpy(), u16(vs)
     qf = q.float().numpy()
-    for i in range(q_len):
+    folded = fold or general or (hq // hkv) not in (1, 2, 4, 8)
+    worst = 0.0
+    for i in sorted(set(range(0, q_len, max(1, q_len // 24))) | {q_len - 1}):
         want = o.block_attention(bits, d, 0, -1, qf[i], kin, ksn, vin, vsn, past + i + 1, scale, nthreads=4)
-        assert np.abs(got[i] - want).max() < 2e-3, (i, np.abs(got[i] - want).max())
-        assert np.abs(got[i] - want).max() < 1e-4     # measured: a few 1e-5
-    # a chunk of one token is a decode step
-    one = tq.chunk_attention(q[-1:].cuda(), ki, ks, vi, vs, kv_len, bits, scale, out_dtype=torch.float32).cpu().numpy()
-    dec = tq.decode_attention(q[-1].cuda(), ki, ks, vi, vs, kv_len, bits, scale, out_dtype=torch.float32).cpu().numpy()
-    assert np.array_equal(one[0], dec)
+        err = float(np.abs(got[i] - want).max())
+        worst = max(worst, err)
+        assert err < 2e-3, (i, err)
+        if folded:
+            assert err < 1e-4     # measured: a few 1e-5
+    print(f"\n[chunk {q_len} on {past} past tokens, {bits}-bit, g = {hq // hkv}, {'folded' if folded else 'tcgen05 kernel'}] max-abs error {worst:.2e}")
+    assert lib.tqb_chunk_umma_timeouts() == 0
+    if folded:
+        # a chunk of one token is a decode step
+        one = tq.chunk_attention(q[-1:].cuda(), ki, ks, vi, vs, kv_len, bits, scale, out_dtype=torch.float32, fold=True).cpu().numpy()
+        dec = tq.decode_attention(q[-1].cuda(), ki, ks, vi, vs, kv_len, bits, scale, out_dtype=torch.float32).cpu().numpy()
+        assert np.array_equal(one[0], dec)
 
 
 def test_chunk_attention_argument_errors():

@@ -88,6 +88,7 @@ def _declare(lib):
         "tqb_decode_scratch_bytes": (S, [I, I, I]),
         "tqb_decode_attention": (c_int, [P, P]),
         "tqb_chunk_attention": (c_int, [P, ctypes.c_int32, P]),
+        "tqb_chunk_umma_timeouts": (ctypes.c_longlong, []),
         "tqb_decode_attention_static": (c_int, [P, P]),
         "tqb_decode_static_scratch_capacity": (S, []),
         "tqb_lse_combine": (c_int, [P, P, I, I, I, P, I, P]),

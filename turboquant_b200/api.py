@@ -557,8 +557,9 @@ def decode_attention(q, k_idx, k_sc, v_idx, v_sc, kv_len, bits, softmax_scale, n
 
 
 def chunk_attention(q, k_idx, k_sc, v_idx, v_sc, kv_len, bits, softmax_scale, norm_mode=QuantNormMode.MaxNorm,
-                    outlier_blocks=ALL_BLOCKS, num_partitions=0, out_dtype=None, qjl=None, force_general=False):
+                    outlier_blocks=ALL_BLOCKS, num_partitions=0, out_dtype=None, qjl=None, force_general=False, fold=False):
     """Causal attention of a chunk of query tokens over the packed cache (tqb_chunk_attention).
+    fold=True takes the path that folds the chunk into decode launches instead of the dedicated tcgen05 kernel.
 
     q [q_len, Hq, D]; the cache arrays as for decode_attention, with the chunk's own K/V rows already stored;
     query token i attends to the first kv_len - q_len + i + 1 tokens.  Returns [q_len, Hq, D]."""
@@ -581,7 +582,7 @@ def chunk_attention(q, k_idx, k_sc, v_idx, v_sc, kv_len, bits, softmax_scale, no
     p.bits, p.head_dim, p.norm_mode, p.outlier_blocks = bits, d, int(norm_mode), outlier_blocks
     p.num_q_heads, p.num_kv_heads, p.kv_len, p.kv_stride = hq, hkv, kv_len, stride
     p.num_partitions, p.softmax_scale = parts, softmax_scale
-    p.flags = 2 if force_general else 0
+    p.flags = (2 if force_general else 0) | (16 if fold else 0)
     check(lib.tqb_chunk_attention(ctypes.byref(p), q_len, _stream()))
     return out
 

@@ -28,6 +28,8 @@ int launch_decode_mma(const tqb_decode_params* p, int num_partitions, float* par
                       const int* gate = nullptr, int gate_want = 0, const float* dev_signs = nullptr, int alias_heads = 0,
                       const PeerPush* peer = nullptr, float* group_area = nullptr);
 
+int launch_chunk_umma(const tqb_decode_params* p, int q_len, cudaStream_t s);
+
 namespace {
 
 constexpr int kWarps = 4;
@@ -532,7 +534,17 @@ int tqb_chunk_attention(const tqb_decode_params* p, int32_t q_len, tqb_stream_t 
     if (p->kv_len < q_len) return TQB_ERR_RANGE_OUT_OF_BOUNDS;
     if (p->num_q_heads <= 0 || p->num_kv_heads <= 0) return TQB_ERR_INVALID_ARGUMENT;
     if ((long long)p->num_q_heads * q_len > (1 << 24)) return TQB_ERR_TOO_LARGE;
+    if (!(p->flags & (TQB_DECODE_FORCE_GENERAL | TQB_DECODE_FOLD_CHUNK | TQB_DECODE_PARTIALS_ONLY))) {
+        // the dedicated kernel on the tcgen05 tensor cores, for the shapes it covers
+        if (!p->q || !p->out) return TQB_ERR_NULL_POINTER;
+        if (p->num_q_heads % p->num_kv_heads != 0) return TQB_ERR_INVALID_ARGUMENT;
+        if (p->kv_len > p->kv_stride) return TQB_ERR_RANGE_OUT_OF_BOUNDS;
+        if (!p->k_indices || !p->k_scales || !p->v_indices || !p->v_scales) return TQB_ERR_NULL_POINTER;
+        const int st = launch_chunk_umma(p, q_len, as_stream(stream));
+        if (st != TQB_ERR_UNSUPPORTED) return st;
+    }
     tqb_decode_params f = *p;
+    f.flags &= ~TQB_DECODE_FOLD_CHUNK;
     f.num_q_heads = p->num_q_heads * q_len;
     f.num_kv_heads = p->num_kv_heads * q_len;
     return decode_impl(&f, p->num_kv_heads, stream);
