@@ -528,6 +528,7 @@ extern "C" {
 // head (i, kv head) reads cache head `kv head` and stops after kv_len - q_len + i + 1 tokens.  The chunk
 // re-reads the cache once per query position, mostly from L2.
 int tqb_chunk_attention(const tqb_decode_params* p, int32_t q_len, tqb_stream_t stream) {
+    TQB_NVTX_RANGE();
     if (!p) return TQB_ERR_NULL_POINTER;
     if (q_len <= 0) return TQB_ERR_INVALID_ARGUMENT;
     if (p->append_k != nullptr || p->append_v != nullptr) return TQB_ERR_INVALID_ARGUMENT;   // the chunk is stored first
@@ -567,12 +568,14 @@ static int lse_combine_impl(const float* po, const float* lse, size_t po_stride,
 
 int tqb_lse_combine(const float* partial_out, const float* partial_lse, int32_t num_shards, int32_t num_q_heads,
                     int32_t head_dim, void* out, int32_t out_dtype, tqb_stream_t stream) {
+    TQB_NVTX_RANGE();
     return lse_combine_impl(partial_out, partial_lse, (size_t)num_q_heads * head_dim, (size_t)num_q_heads * 2, num_shards,
                             num_q_heads, head_dim, out, out_dtype, stream);
 }
 
 int tqb_lse_combine_packed(const float* gathered, int32_t num_shards, int32_t num_q_heads, int32_t head_dim, void* out,
                            int32_t out_dtype, tqb_stream_t stream) {
+    TQB_NVTX_RANGE();
     if (!gathered) return TQB_ERR_NULL_POINTER;
     const size_t rec = (size_t)num_q_heads * ((size_t)head_dim + 2);
     return lse_combine_impl(gathered, gathered + (size_t)num_q_heads * head_dim, rec, rec, num_shards, num_q_heads, head_dim,
@@ -586,6 +589,7 @@ int tqb_fused_attention(const float* q, const uint8_t* k_indices, const uint16_t
                         int32_t num_attention_heads, int32_t num_kv_heads, int32_t head_dim, int32_t kv_len,
                         int32_t kv_stride, int32_t packed_dim, int32_t num_qblocks, int32_t bits, float softmax_scale,
                         int32_t num_partitions, tqb_stream_t stream) {
+    TQB_NVTX_RANGE();
     if (kv_len == 0 || num_kv_heads == 0) return TQB_OK;  // tq_attention_kernel.cu:366
     if (bits < 2 || bits > 4) return TQB_ERR_UNSUPPORTED_BITS;
     if (head_dim <= 0 || head_dim % kBlock != 0) return TQB_ERR_INVALID_DIMENSION;
@@ -703,6 +707,7 @@ extern "C" {
 size_t tqb_decode_static_scratch_capacity(void) { return kStaticScratchBytes; }
 
 int tqb_decode_attention_static(const tqb_decode_params* p, tqb_stream_t stream) {
+    TQB_NVTX_RANGE();
     if (!p) return TQB_ERR_NULL_POINTER;
     if (p->num_q_heads <= 0 || p->num_kv_heads <= 0 || p->head_dim <= 0) return TQB_ERR_INVALID_ARGUMENT;
     // the partials would stay in the library's array, whose address the caller cannot obtain

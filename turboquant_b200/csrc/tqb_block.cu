@@ -511,6 +511,7 @@ int tqb_block_quantize(int32_t bits, int32_t head_dim, int32_t norm_mode, int32_
                        int32_t x_dtype, int64_t n, int64_t x_row_stride, uint8_t* indices, uint16_t* scales,
                        int64_t rows_per_group, int64_t out_group_stride, int64_t out_row_offset,
                        tqb_stream_t stream) {
+    TQB_NVTX_RANGE();
     return block_quantize_impl(bits, head_dim, norm_mode, outlier_blocks, x, nullptr, x_dtype, n, x_row_stride, indices,
                                scales, nullptr, nullptr, rows_per_group, out_group_stride, out_row_offset, stream);
 }
@@ -519,6 +520,7 @@ int tqb_block_quantize_pair(int32_t bits, int32_t head_dim, int32_t norm_mode, i
                             const void* v, int32_t x_dtype, int64_t n, int64_t x_row_stride, uint8_t* k_indices,
                             uint16_t* k_scales, uint8_t* v_indices, uint16_t* v_scales, int64_t rows_per_group,
                             int64_t out_group_stride, int64_t out_row_offset, tqb_stream_t stream) {
+    TQB_NVTX_RANGE();
     if (n > 0 && !v) return TQB_ERR_NULL_POINTER;
     return block_quantize_impl(bits, head_dim, norm_mode, outlier_blocks, k, v, x_dtype, n, x_row_stride, k_indices,
                                k_scales, v_indices, v_scales, rows_per_group, out_group_stride, out_row_offset, stream);
@@ -528,6 +530,7 @@ int tqb_block_dequantize(int32_t bits, int32_t head_dim, int32_t norm_mode, int3
                          const uint8_t* indices, const uint16_t* scales, int64_t n, int64_t rows_per_group,
                          int64_t in_group_stride, int64_t in_row_offset, void* out, int32_t out_dtype,
                          tqb_stream_t stream) {
+    TQB_NVTX_RANGE();
     int st = block_cfg_check(bits, head_dim, norm_mode);
     if (st != TQB_OK) return st;
     if (n < 0 || rows_per_group < 0) return TQB_ERR_INVALID_ARGUMENT;
@@ -560,6 +563,7 @@ int tqb_block_dequantize(int32_t bits, int32_t head_dim, int32_t norm_mode, int3
 int tqb_dequant_batch(const uint8_t* packed_indices, const uint16_t* scales, const float* codebook,
                       const float* sign_pattern, float* output, int32_t num_blocks, int32_t block_size, int32_t bits,
                       int32_t bytes_per_block, tqb_stream_t stream) {
+    TQB_NVTX_RANGE();
     if (num_blocks == 0) return TQB_OK;  // tq_dequant_kernel.cu:116
     if (num_blocks < 0) return TQB_ERR_INVALID_ARGUMENT;
     if (bits < 2 || bits > 4) return TQB_ERR_UNSUPPORTED_BITS;
@@ -587,6 +591,7 @@ int tqb_quant_maxnorm_batch(const float* rotated_input, const float* boundaries,
                             uint16_t* scales_out, int32_t num_blocks, int32_t block_size, int32_t bits,
                             int32_t num_boundaries, int32_t bytes_per_block, float outer_centroid, float scale_sign,
                             tqb_stream_t stream) {
+    TQB_NVTX_RANGE();
     if (num_blocks == 0) return TQB_OK;  // tq_quant_kernel.cu:430
     if (num_blocks < 0) return TQB_ERR_INVALID_ARGUMENT;
     if (bits < 2 || bits > 4) return TQB_ERR_UNSUPPORTED_BITS;
@@ -621,6 +626,7 @@ int tqb_quant_maxnorm_batch(const float* rotated_input, const float* boundaries,
 
 int tqb_pack_indices(const uint8_t* indices, uint8_t* packed_out, int32_t num_vectors, int32_t block_size,
                      int32_t bits, int32_t bytes_per_block, tqb_stream_t stream) {
+    TQB_NVTX_RANGE();
     if (num_vectors == 0) return TQB_OK;  // tq_quant_kernel.cu:450
     if (num_vectors < 0) return TQB_ERR_INVALID_ARGUMENT;
     if (bits < 2 || bits > 4) return TQB_ERR_UNSUPPORTED_BITS;

@@ -5,20 +5,21 @@
 // One CTA owns 128 query rows - 128 / g consecutive query tokens times the g query heads of one KV head - and walks the
 // cache in tiles of 64 tokens.  Each K / V tile is unpacked ONCE per CTA (the decode kernels, run once per query token,
 // unpack it once per token) and feeds M = 128 MMAs:
-//   S  = Q~ K~^T         K~ = |s_k| (c - 7.5) (4-bit grid; |s_k| centroid / kappa for 3-bit) as an f16 hi + lo pair that
-//                        holds the product exactly (a code has at most 11 significant bits, the f16 scale 11), the
-//                        rotated query as an f16 hi + lo pair: Qhi Khi^T + Qlo Khi^T + Qhi Klo^T, three MMAs per
-//                        16 dims into one 128 x 64 f32 accumulator in tensor memory (double-buffered, so the
-//                        tensor cores score tile i + 1 while the softmax threads work on tile i).
+//   S  = Q~ K~^T         K~ = |s_k| (c - 7.5) (4-bit grid; |s_k| centroid / kappa for 3-bit) and the rotated, pre-scaled
+//                        query, each rounded once to f16: eight MMAs (16 dims each) into a 128 x 64 f32 accumulator in
+//                        tensor memory.  Three accumulators rotate, so the tensor cores score tiles i + 1 and i + 2
+//                        while the softmax threads work on tile i.
 //   O  += P V            P = exp2(s - m) as f16 (K-major A operand, written by the softmax threads, double-buffered),
 //                        V dequantized with its scale to f16 (MN-major B operand), N = 128 dims: one 128 x 128 f32
 //                        accumulator.
+// The f16 roundings of Q~, K~, P and V are this kernel's error budget (a few 1e-4 of the value range on the outputs;
+// the decode kernels, which keep the query in f32 or as 20-bit integers, stay below 1e-5).
 // Thread r of the four softmax warps owns query row r = tensor-memory lane r, so the online softmax needs no
 // shuffles; the output is rotated back in registers (one 32-point butterfly per block) at the end.
 //
-// Warp roles: warps 0-3 softmax / correction / epilogue, warps 4-7 load and unpack K and V tiles (two stages),
-// warp 8 issues the MMAs.  All hand-offs go through mbarriers; every wait is bounded and a wait that runs out sets a
-// flag, drains and returns (tqb_chunk_umma_timeouts).
+// Warp roles: warps 0-3 softmax / correction / epilogue, warps 4-5 load and unpack K tiles (three stages), warps 6-9
+// V tiles (two stages), warp 10 issues the MMAs.  All hand-offs go through mbarriers; every wait is bounded and a wait
+// that runs out sets a flag, drains and returns (tqb_chunk_umma_timeouts).
 #include <cuda.h>
 #include <float.h>
 
@@ -32,20 +33,19 @@ namespace {
 constexpr int kRows = 128;          // query rows per CTA
 constexpr int kTile = 64;           // cache tokens per step
 constexpr int kD = 128;
-constexpr int kThreads = 9 * 32;
+constexpr int kThreads = 11 * 32;
 constexpr float kNegBig = -1.0e30f;
 
 // shared-memory map (bytes from a 1024-aligned base)
-constexpr int kOffQhi = 0;                       // [2 atoms][128 rows][128 B]
-constexpr int kOffQlo = 32768;
-constexpr int kOffKhi = 65536;                   // [2 stages][2 atoms][64 tokens][128 B]
-constexpr int kOffKlo = kOffKhi + 2 * 16384;
-constexpr int kOffV = kOffKlo + 2 * 16384;       // [2 stages][2 dim halves][8 token groups][8 tokens][128 B]
+constexpr int kKStages = 3;                      // K stages = S buffers: the scores run two tiles ahead of the softmax
+constexpr int kOffQ = 0;                         // [2 atoms][128 rows][128 B]
+constexpr int kOffK = 32768;                     // [3 stages][2 atoms][64 tokens][128 B]
+constexpr int kOffV = kOffK + kKStages * 16384;  // [2 stages][2 dim halves][8 token groups][8 tokens][128 B]
 constexpr int kOffP = kOffV + 2 * 16384;         // [2 buffers][128 rows][128 B]
 constexpr int kOffLut = kOffP + 2 * 16384;       // 3-bit: 64 half2
 constexpr int kOffBar = kOffLut + 256;           // mbarriers
 constexpr int kSmemBytes = kOffBar + 128 + 1024; // + alignment slack
-constexpr uint32_t kTmemCols = 256;              // S buffers at columns 0 and 64, O at 128
+constexpr uint32_t kTmemCols = 512;              // S buffers at columns 0, 64, 128; O at 192
 
 struct ChunkArgs {
     const void* q;        // [q_len, hq, 128]
@@ -84,14 +84,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // The first wait that runs out leaves a note of who waited for what: (role << 24) | (barrier << 16) | tile.
 __device__ unsigned g_chunk_first_timeout = 0;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned note = 0) {
-    if (mbar_try_wait(bar, parity)) return true;
-    // The clock is read only every 64th poll: special-register reads share a narrow pipe with the exponentials of the
-    // softmax warps, and a warp that polls in a tight loop takes issue slots from the warp it is waiting for.
+    // try_wait suspends the thread in hardware for a short while when the phase is not complete, so this loop does
+    // not spin hot; the clock (a special-register read) is looked at only every 256th poll.
     long long t0 = 0;
     for (unsigned n = 1;; ++n) {
         if (mbar_try_wait(bar, parity)) return true;
-        __nanosleep(32);
-        if ((n & 63u) == 0u) {
+        if ((n & 255u) == 0u) {
             const long long now = clock64();
             if (t0 == 0) t0 = now;
             else if (now - t0 > (1ll << 29)) {
@@ -195,6 +193,82 @@ __device__ __forceinline__ float wht32_lane(float v, int lane) {
 // 16 consecutive bytes of a swizzled 128-byte row: chunk c of row `row` of a tile whose rows are 128 bytes apart
 __device__ __forceinline__ uint32_t sw128(int row, int chunk) { return (uint32_t)(row * 128 + ((chunk ^ (row & 7)) << 4)); }
 
+// ---- load + unpack role: IS_K ? warps 4-5 (K tiles, four pieces per thread) : warps 6-9 (V tiles, two pieces) ----
+// A piece is one (token, block): 32 codes and their scale.  Eight consecutive lanes take the eight tokens of one token
+// group (eight distinct swizzle phases, so the 16-byte stores of a quarter-warp fall into eight different bank
+// groups), the four lane octets take the four blocks.  The packed pieces are fetched two tiles ahead of their use
+// (two register sets), so that the trip to L2 / HBM is never waited for.
+template <int BITS, bool IS_K>
+__device__ __forceinline__ bool unpack_role(const ChunkArgs& a, unsigned char* sm, uint32_t bar_full, uint32_t bar_empty, int w2, int lane,
+                                            size_t row0, int kv_hi, int ntiles) {
+    constexpr int NP = IS_K ? 4 : 2;             // pieces per thread and tile
+    constexpr int TSTEP = kTile / NP;            // token distance between a thread's pieces
+    constexpr int NST = IS_K ? kKStages : 2;
+    const int tl = 8 * w2 + (lane & 7), b = lane >> 3;
+    const uint8_t* src_b = IS_K ? a.kb : a.vb;
+    const uint16_t* src_s = IS_K ? a.ks : a.vs;
+    uint4 pq[2][NP];
+    uint32_t sr[2][NP];
+    auto fetch = [&](int i, uint4 (&pqs)[NP], uint32_t (&srs)[NP]) {
+#pragma unroll
+        for (int h = 0; h < NP; ++h) {
+            const size_t row = row0 + (size_t)min(i * kTile + tl + TSTEP * h, kv_hi - 1);
+            if (BITS == 4) {
+                pqs[h] = __ldg(reinterpret_cast<const uint4*>(src_b + row * 64) + b);
+            } else {
+                const uint32_t* pp = reinterpret_cast<const uint32_t*>(src_b + row * 48) + 3 * b;
+                pqs[h] = make_uint4(__ldg(pp), __ldg(pp + 1), __ldg(pp + 2), 0u);
+            }
+            srs[h] = (uint32_t)__ldg(src_s + row * 4 + b);
+        }
+    };
+    if (ntiles > 0) fetch(0, pq[0], sr[0]);
+    if (ntiles > 1) fetch(1, pq[1], sr[1]);
+    int s = 0, round = 0;        // stage of tile i and how often the ring has wrapped
+    auto unpack_tile = [&](int i, uint4 (&pqc)[NP], uint32_t (&src)[NP]) -> bool {
+        if (round > 0 && !mbar_wait(bar_empty + 8 * s, (round - 1) & 1, (1u << 24) | ((IS_K ? 2u : 3u) << 16) | (unsigned)i)) return false;
+        unsigned char* dst = sm + (IS_K ? kOffK : kOffV) + s * 16384;
+#pragma unroll
+        for (int h = 0; h < NP; ++h) {
+            const int t = tl + TSTEP * h;
+            const uint32_t w[4] = {pqc[h].x, pqc[h].y, pqc[h].z, pqc[h].w};
+            const __half2 sc2 = __half2half2(__habs(__ushort_as_half((unsigned short)src[h])));
+            // K: atom b / 2, row t, chunks 4 (b % 2) + j;  V: dim half b / 2, token group t / 8, row t % 8, same chunks
+            const uint32_t off = (uint32_t)(b >> 1) * 8192u + (IS_K ? 0u : (uint32_t)(t >> 3) * 1024u);
+            const int row = IS_K ? t : (t & 7);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                uint32_t x[4];
+                if (BITS == 4) {
+                    nibbles_to_half2(w[j], x);
+                } else {
+                    // codes 8j .. 8j+7 of the block: bits 24j .. 24j+23 of the 96-bit stream, natural order
+                    const int bit = 24 * j, wi = bit >> 5, sh = bit & 31;
+                    const uint32_t cc = __funnelshift_r(w[wi], w[min(wi + 1, 2)], sh);
+                    const uint32_t* lut = reinterpret_cast<const uint32_t*>(sm + kOffLut);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) x[e] = lut[(cc >> (6 * e)) & 63u];
+                }
+                // value = |scale| * code value, one rounding to f16
+#pragma unroll
+                for (int e = 0; e < 4; ++e) x[e] = h2_as_u32(__hmul2(u32_as_h2(x[e]), sc2));
+                *reinterpret_cast<uint4*>(dst + off + sw128(row, 4 * (b & 1) + j)) = make_uint4(x[0], x[1], x[2], x[3]);
+            }
+        }
+        if (i + 2 < ntiles) fetch(i + 2, pqc, src);
+        fence_async_smem();
+        mbar_arrive(bar_full + 8 * s);
+        if (++s == NST) { s = 0; ++round; }
+        return true;
+    };
+    bool ok = true;
+    for (int i = 0; i < ntiles && ok; i += 2) {
+        ok = unpack_tile(i, pq[0], sr[0]);
+        if (ok && i + 1 < ntiles) ok = unpack_tile(i + 1, pq[1], sr[1]);
+    }
+    return ok;
+}
+
 template <typename QT, int BITS>
 __global__ void __launch_bounds__(kThreads, 1) chunk_umma_kernel(ChunkArgs a) {
     extern __shared__ unsigned char s_dyn[];
@@ -212,18 +286,24 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_umma_kernel(ChunkArgs a) {
     const int ntiles = (kv_hi + kTile - 1) / kTile;
     const size_t row0 = (size_t)kvh * a.kv_stride;
 
-    // barriers (8 bytes each, two stages / buffers where indexed): K and V tiles are handed over separately, so that
-    // the scores of tile i + 1 never wait for the P V product of tile i - 1
+    // barriers (8 bytes each, indexed by stage / buffer): K and V tiles are handed over separately, so that the scores
+    // of a later tile never wait for the P V product of an earlier one
     const uint32_t bar = base + kOffBar;
-    constexpr uint32_t kKFull = 0, kVFull = 16, kKEmpty = 32, kVEmpty = 48, kSFull = 64, kPFull = 80, kOFull = 96;
+    constexpr uint32_t kKFull = 0, kKEmpty = 24, kVFull = 48, kVEmpty = 64, kSFull = 80, kPFull = 104, kOFull = 120;
     if (tid == 0) {
         s_fail = 0;
-        mbar_init(bar + kKFull, 128); mbar_init(bar + kKFull + 8, 128);
-        mbar_init(bar + kVFull, 128); mbar_init(bar + kVFull + 8, 128);
-        mbar_init(bar + kKEmpty, 1); mbar_init(bar + kKEmpty + 8, 1);
-        mbar_init(bar + kVEmpty, 1); mbar_init(bar + kVEmpty + 8, 1);
-        mbar_init(bar + kSFull, 1); mbar_init(bar + kSFull + 8, 1);
-        mbar_init(bar + kPFull, 128); mbar_init(bar + kPFull + 8, 128);
+#pragma unroll
+        for (int i = 0; i < kKStages; ++i) {
+            mbar_init(bar + kKFull + 8 * i, 64);
+            mbar_init(bar + kKEmpty + 8 * i, 1);
+            mbar_init(bar + kSFull + 8 * i, 1);
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar + kVFull + 8 * i, 128);
+            mbar_init(bar + kVEmpty + 8 * i, 1);
+            mbar_init(bar + kPFull + 8 * i, 128);
+        }
         mbar_init(bar + kOFull, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
@@ -235,7 +315,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_umma_kernel(ChunkArgs a) {
         for (int e = tid; e < 64; e += kThreads)
             reinterpret_cast<__half2*>(sm + kOffLut)[e] = __floats2half2_rn(a.lut[e & 7], a.lut[e >> 3]);
     }
-    // ---- rotated queries -> Qhi / Qlo tiles (K-major, 128-byte swizzle, two atoms of 64 dims) ----
+    // ---- rotated queries -> Q tile (K-major, 128-byte swizzle, two atoms of 64 dims), rounded to f16 ----
     {
         const uint32_t neg = 0xB1A6D4B2u;   // src/cache/precomputed/rotation.rs:16-20
         const float sign = ((neg >> lane) & 1u) ? -a.sign_mag : a.sign_mag;
@@ -255,11 +335,8 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_umma_kernel(ChunkArgs a) {
                 pos = (lane & ~7) | ((k & 3) * 2 + (k >> 2));
             }
             const int d = b * 32 + pos;
-            const __half hi = __float2half_rn(v);
-            const __half lo = __float2half_rn(v - __half2float(hi));
             const uint32_t off = (uint32_t)(d >> 6) * 16384u + sw128(r, (d & 63) >> 3) + (uint32_t)(d & 7) * 2u;
-            *reinterpret_cast<__half*>(sm + kOffQhi + off) = hi;
-            *reinterpret_cast<__half*>(sm + kOffQlo + off) = lo;
+            *reinterpret_cast<__half*>(sm + kOffQ + off) = __float2half_rn(v);
         }
     }
     fence_async_smem();
@@ -267,161 +344,55 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_umma_kernel(ChunkArgs a) {
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = s_tmem;
-    const uint32_t tmemS = tmem, tmemO = tmem + 128;   // S buffer b at columns 64 b
+    const uint32_t tmemS = tmem, tmemO = tmem + kKStages * kTile;   // S buffer b at columns 64 b
 
-    if (warp >= 4 && warp < 8) {
-        // ================= load + unpack =================
-        const int u = tid - 128;
-        uint4 kq[2], vq[2];
-        uint2 ksr[2], vsr[2];
-        // Thread -> (token, block) of its two pieces per tile: eight consecutive lanes take the eight tokens of one token
-        // group (eight distinct swizzle phases, so the 16-byte stores of a quarter-warp fall into eight different bank
-        // groups), the four lane octets take the four blocks.
-        const int tl = 8 * (u >> 5) + (u & 7), bl = (u & 31) >> 3;
-        auto fetch = [&](int i) {
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int t = tl + 32 * h, b = bl;
-                const size_t row = row0 + (size_t)min(i * kTile + t, kv_hi - 1);
-                if (BITS == 4) {
-                    kq[h] = __ldg(reinterpret_cast<const uint4*>(a.kb + row * 64) + b);
-                    vq[h] = __ldg(reinterpret_cast<const uint4*>(a.vb + row * 64) + b);
-                } else {
-                    const uint32_t* kp = reinterpret_cast<const uint32_t*>(a.kb + row * 48) + 3 * b;
-                    const uint32_t* vp = reinterpret_cast<const uint32_t*>(a.vb + row * 48) + 3 * b;
-                    kq[h] = make_uint4(__ldg(kp), __ldg(kp + 1), __ldg(kp + 2), 0u);
-                    vq[h] = make_uint4(__ldg(vp), __ldg(vp + 1), __ldg(vp + 2), 0u);
-                }
-                ksr[h] = __ldg(reinterpret_cast<const uint2*>(a.ks + row * 4));
-                vsr[h] = __ldg(reinterpret_cast<const uint2*>(a.vs + row * 4));
-            }
-        };
-        if (ntiles > 0) fetch(0);
-        bool ok = true;
-        for (int i = 0; i < ntiles && ok; ++i) {
-            const int s = i & 1;
-            unsigned char* khi = sm + kOffKhi + s * 16384;
-            unsigned char* klo = sm + kOffKlo + s * 16384;
-            unsigned char* vt = sm + kOffV + s * 16384;
-            // ---- K tile (its stage is free once the scores of tile i - 2 are done) ----
-            if (i >= 2 && !mbar_wait(bar + kKEmpty + 8 * s, ((i >> 1) - 1) & 1, (1u << 24) | (2u << 16) | (unsigned)i)) { ok = false; break; }
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int t = tl + 32 * h, b = bl;
-                const uint32_t kw[4] = {kq[h].x, kq[h].y, kq[h].z, kq[h].w};
-                const uint32_t ksw = (b < 2 ? ksr[h].x : ksr[h].y);
-                const __half2 sk2 = __half2half2(__habs(__ushort_as_half((unsigned short)((b & 1) ? (ksw >> 16) : (ksw & 0xFFFFu)))));
-                const uint32_t koff = (uint32_t)(b >> 1) * 8192u;   // atom b / 2, row t, chunks 4 (b % 2) + j
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    uint32_t x[4];
-                    if (BITS == 4) {
-                        nibbles_to_half2(kw[j], x);
-                    } else {
-                        // codes 8j .. 8j+7 of the block: bits 24j .. 24j+23 of the 96-bit stream, natural order
-                        const int bit = 24 * j, wi = bit >> 5, sh = bit & 31;
-                        const uint32_t kk = __funnelshift_r(kw[wi], kw[min(wi + 1, 2)], sh);
-                        const uint32_t* lut = reinterpret_cast<const uint32_t*>(sm + kOffLut);
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) x[e] = lut[(kk >> (6 * e)) & 63u];
-                    }
-                    // K~ = |s_k| c as hi = rn(c s), lo = c s - hi: both factors have at most 11 significant bits, so the
-                    // product has at most 22 and the pair holds it exactly
-                    uint32_t xh[4], xl[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const __half2 c2 = u32_as_h2(x[e]);
-                        const __half2 hi = __hmul2(c2, sk2);
-                        xh[e] = h2_as_u32(hi);
-                        xl[e] = h2_as_u32(__hfma2(c2, sk2, __hneg2(hi)));
-                    }
-                    const int chunk = 4 * (b & 1) + j;
-                    *reinterpret_cast<uint4*>(khi + koff + sw128(t, chunk)) = make_uint4(xh[0], xh[1], xh[2], xh[3]);
-                    *reinterpret_cast<uint4*>(klo + koff + sw128(t, chunk)) = make_uint4(xl[0], xl[1], xl[2], xl[3]);
-                }
-            }
-            fence_async_smem();
-            mbar_arrive(bar + kKFull + 8 * s);
-            // ---- V tile (free once the P V product of tile i - 2 is done): one rounding to f16 ----
-            if (i >= 2 && !mbar_wait(bar + kVEmpty + 8 * s, ((i >> 1) - 1) & 1, (1u << 24) | (3u << 16) | (unsigned)i)) { ok = false; break; }
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int t = tl + 32 * h, b = bl;
-                const uint32_t vw[4] = {vq[h].x, vq[h].y, vq[h].z, vq[h].w};
-                const uint32_t vsw = (b < 2 ? vsr[h].x : vsr[h].y);
-                const __half2 sv2 = __half2half2(__habs(__ushort_as_half((unsigned short)((b & 1) ? (vsw >> 16) : (vsw & 0xFFFFu)))));
-                const uint32_t voff = (uint32_t)(b >> 1) * 8192u + (uint32_t)(t >> 3) * 1024u;   // dim half, token group; row t % 8
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    uint32_t y[4];
-                    if (BITS == 4) {
-                        nibbles_to_half2(vw[j], y);
-                    } else {
-                        const int bit = 24 * j, wi = bit >> 5, sh = bit & 31;
-                        const uint32_t vv = __funnelshift_r(vw[wi], vw[min(wi + 1, 2)], sh);
-                        const uint32_t* lut = reinterpret_cast<const uint32_t*>(sm + kOffLut);
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) y[e] = lut[(vv >> (6 * e)) & 63u];
-                    }
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) y[e] = h2_as_u32(__hmul2(u32_as_h2(y[e]), sv2));
-                    *reinterpret_cast<uint4*>(vt + voff + sw128(t & 7, 4 * (b & 1) + j)) = make_uint4(y[0], y[1], y[2], y[3]);
-                }
-            }
-            if (i + 1 < ntiles) fetch(i + 1);
-            fence_async_smem();
-            mbar_arrive(bar + kVFull + 8 * s);
-        }
-        if (!ok) atomicExch(&s_fail, 1);
-    } else if (warp == 8) {
+    if (warp >= 4 && warp < 6) {
+        if (!unpack_role<BITS, true>(a, sm, bar + kKFull, bar + kKEmpty, warp - 4, lane, row0, kv_hi, ntiles)) atomicExch(&s_fail, 1);
+    } else if (warp >= 6 && warp < 10) {
+        if (!unpack_role<BITS, false>(a, sm, bar + kVFull, bar + kVEmpty, warp - 6, lane, row0, kv_hi, ntiles)) atomicExch(&s_fail, 1);
+    } else if (warp == 10) {
         // ================= MMA issue (one lane) =================
         if (lane == 0) {
             constexpr uint32_t idescS = umma_idesc(kTile, false), idescO = umma_idesc(kD, true);
             bool ok = true;
-            // S(i) = Qhi Khi^T + Qlo Khi^T + Qhi Klo^T over 8 k-steps of 16 dims (atom = 64 dims, 32 bytes per k-step)
-            auto issue_qk = [&](int i) {
-                const int s = i & 1;
-                const uint32_t khi = base + kOffKhi + s * 16384, klo = base + kOffKlo + s * 16384;
+            // Descriptors are built once: inside the loops a descriptor is its base plus a compile-time offset in the
+            // address field (bytes >> 4), so that the one issuing thread spends a handful of instructions per MMA.
+            const uint64_t dQ = umma_desc(base + kOffQ, 16, 1024), dK = umma_desc(base + kOffK, 16, 1024);
+            const uint64_t dP = umma_desc(base + kOffP, 16, 1024), dV = umma_desc(base + kOffV, 8192, 1024);
+            // S = Q~ K~^T over 8 k-steps of 16 dims (atom = 64 dims, 32 bytes per k-step)
+            auto issue_qk = [&](int s) {      // s: K stage = S buffer of the tile
+                const uint64_t kk0 = dK + (uint64_t)(s * (16384 >> 4));
 #pragma unroll
-                for (int part = 0; part < 3; ++part) {
-#pragma unroll
-                    for (int kk = 0; kk < 8; ++kk) {
-                        const uint32_t offq = (uint32_t)(kk >> 2) * 16384u + (uint32_t)(kk & 3) * 32u;
-                        const uint32_t offk = (uint32_t)(kk >> 2) * 8192u + (uint32_t)(kk & 3) * 32u;
-                        const uint64_t da = umma_desc(base + (part == 1 ? kOffQlo : kOffQhi) + offq, 16, 1024);
-                        const uint64_t db = umma_desc((part == 2 ? klo : khi) + offk, 16, 1024);
-                        umma_f16(tmemS + s * kTile, da, db, idescS, (part | kk) ? 1u : 0u);
-                    }
+                for (int kk = 0; kk < 8; ++kk) {
+                    const uint64_t offq = (uint64_t)(((kk >> 2) * 16384 + (kk & 3) * 32) >> 4);
+                    const uint64_t offk = (uint64_t)(((kk >> 2) * 8192 + (kk & 3) * 32) >> 4);
+                    umma_f16(tmemS + s * kTile, dQ + offq, kk0 + offk, idescS, kk ? 1u : 0u);
                 }
                 umma_commit(bar + kSFull + 8 * s);
                 umma_commit(bar + kKEmpty + 8 * s);   // the K stage is free when these MMAs are done
             };
-            if (ntiles > 0) {
-                if (mbar_wait(bar + kKFull, 0, (2u << 24) | (0u << 16))) {
-                    tc_fence_after();
-                    issue_qk(0);
-                } else ok = false;
-            }
+            // The scores run two tiles ahead of the softmax: S(i + 2) is issued before P(i) V(i), into the buffer that the
+            // softmax of tile i - 1 has finished reading (its p_full arrival was waited for one iteration earlier).
+            int sk = 0, rk = 0;   // K stage / S buffer of the next tile to score, and its ring round
+            auto score_next = [&](int i) -> bool {
+                if (!mbar_wait(bar + kKFull + 8 * sk, rk & 1, (2u << 24) | (0u << 16) | (unsigned)i)) return false;
+                tc_fence_after();
+                issue_qk(sk);
+                if (++sk == kKStages) { sk = 0; ++rk; }
+                return true;
+            };
+            for (int i = 0; i < 2 && i < ntiles && ok; ++i) ok = score_next(i);
             for (int i = 0; i < ntiles && ok; ++i) {
                 const int s = i & 1;
-                if (i + 1 < ntiles) {
-                    // score the next tile while the softmax threads work on this one (its S buffer was released by the
-                    // p_full arrival of tile i - 1, waited for below in the previous iteration)
-                    if (!mbar_wait(bar + kKFull + 8 * (s ^ 1), ((i + 1) >> 1) & 1, (2u << 24) | (0u << 16) | (unsigned)(i + 1))) { ok = false; break; }
-                    tc_fence_after();
-                    issue_qk(i + 1);
-                }
+                if (i + 2 < ntiles && !score_next(i + 2)) { ok = false; break; }
                 if (!mbar_wait(bar + kPFull + 8 * s, (i >> 1) & 1, (2u << 24) | (5u << 16) | (unsigned)i)) { ok = false; break; }
                 if (!mbar_wait(bar + kVFull + 8 * s, (i >> 1) & 1, (2u << 24) | (1u << 16) | (unsigned)i)) { ok = false; break; }
                 tc_fence_after();
                 // O += P V : four k-steps of 16 tokens
-                const uint32_t vt = base + kOffV + s * 16384, pt = base + kOffP + s * 16384;
+                const uint64_t pv = dP + (uint64_t)(s * (16384 >> 4)), vv = dV + (uint64_t)(s * (16384 >> 4));
 #pragma unroll
-                for (int kk = 0; kk < 4; ++kk) {
-                    const uint64_t da = umma_desc(pt + kk * 32u, 16, 1024);
-                    const uint64_t db = umma_desc(vt + kk * 2048u, 8192, 1024);
-                    umma_f16(tmemO, da, db, idescO, (i | kk) ? 1u : 0u);
-                }
+                for (int kk = 0; kk < 4; ++kk)
+                    umma_f16(tmemO, pv + (uint64_t)((kk * 32) >> 4), vv + (uint64_t)((kk * 2048) >> 4), idescO, (i | kk) ? 1u : 0u);
                 umma_commit(bar + kVEmpty + 8 * s);      // frees this V stage (and P buffer) when the MMAs issued so far are done
             }
             if (ok) umma_commit(bar + kOFull);           // everything issued so far has completed when this arrives
@@ -434,40 +405,54 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_umma_kernel(ChunkArgs a) {
         const int tq = r / g, hh = r - tq * g;
         const bool row_valid = tq < ntok;
         const int limit = past + tok0 + tq + 1;                 // visible cache tokens of this row
+        const int limit_min = past + tok0 + 1;                  // ... of the tile's first row
         const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
         float m_run = kNegBig, l_run = 0.0f;
         bool ok = true;
+        int ss = 0, rs = 0;          // S buffer of tile i and its ring round
         for (int i = 0; i < ntiles && ok; ++i) {
-            const int s = i & 1;
+            const int s = i & 1;     // P buffer / V stage
             // (the tensor-memory accesses below are warp-collective: the whole warp goes on, or none of it)
-            if (!__all_sync(0xffffffffu, mbar_wait(bar + kSFull + 8 * s, (i >> 1) & 1, (3u << 24) | (4u << 16) | (unsigned)i))) { ok = false; break; }
+            if (!__all_sync(0xffffffffu, mbar_wait(bar + kSFull + 8 * ss, rs & 1, (3u << 24) | (4u << 16) | (unsigned)i))) { ok = false; break; }
             tc_fence_after();
             float p[kTile];
-            float mx = kNegBig;
             {
                 uint32_t v0[32], v1[32];
-                tmem_ld32(tmemS + lane_base + s * kTile, v0);
-                tmem_ld32(tmemS + lane_base + s * kTile + 32, v1);
+                tmem_ld32(tmemS + lane_base + ss * kTile, v0);
+                tmem_ld32(tmemS + lane_base + ss * kTile + 32, v1);
                 tmem_wait_ld();
+                if ((i + 1) * kTile <= limit_min) {
+                    // every token of the tile is visible to every row (all tiles but the last one or two)
 #pragma unroll
-                for (int t = 0; t < 32; ++t) {
-                    const int tok = i * kTile + t;
-                    p[t] = (row_valid && tok < limit) ? __uint_as_float(v0[t]) : kNegBig;
-                    p[32 + t] = (row_valid && tok + 32 < limit) ? __uint_as_float(v1[t]) : kNegBig;
-                    mx = fmaxf(mx, fmaxf(p[t], p[32 + t]));
+                    for (int t = 0; t < 32; ++t) {
+                        p[t] = __uint_as_float(v0[t]);
+                        p[32 + t] = __uint_as_float(v1[t]);
+                    }
+                } else {
+#pragma unroll
+                    for (int t = 0; t < 32; ++t) {
+                        const int tok = i * kTile + t;
+                        p[t] = (row_valid && tok < limit) ? __uint_as_float(v0[t]) : kNegBig;
+                        p[32 + t] = (row_valid && tok + 32 < limit) ? __uint_as_float(v1[t]) : kNegBig;
+                    }
                 }
             }
+            // four interleaved partial maxima / sums keep the dependency chains short
+            float mx4[4] = {kNegBig, kNegBig, kNegBig, kNegBig};
+#pragma unroll
+            for (int t = 0; t < kTile; ++t) mx4[t & 3] = fmaxf(mx4[t & 3], p[t]);
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             // lazy maximum: raise the reference only when this tile exceeds it by more than 2^6
             const float m_new = (mx - m_run > 6.0f) ? mx : m_run;
             const float resc = ex2(m_run - m_new);
             m_run = m_new;
-            float lsum = 0.0f;
+            float ls4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
             for (int t = 0; t < kTile; ++t) {
                 p[t] = ex2(p[t] - m_new);
-                lsum += p[t];
+                ls4[t & 3] += p[t];
             }
-            l_run = l_run * resc + lsum;
+            l_run = l_run * resc + ((ls4[0] + ls4[1]) + (ls4[2] + ls4[3]));
             if (i > 0 && __any_sync(0xffffffffu, resc != 1.0f)) {
                 // rescale this row of O, once the P V product of the previous tile has landed in it (warp-collective
                 // tensor-memory accesses: every lane takes part with its own factor)
@@ -484,7 +469,9 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_umma_kernel(ChunkArgs a) {
                 }
                 tmem_wait_st();
             }
-            // P -> shared memory (K-major A operand: row r, 64 tokens = 128 bytes, swizzled 16-byte chunks)
+            // P -> shared memory (K-major A operand: row r, 64 tokens = 128 bytes, swizzled 16-byte chunks).  The buffer was
+            // read by the P V product of tile i - 2, which the scores of tile i (issued before it) do not order.
+            if (i >= 2 && !__all_sync(0xffffffffu, mbar_wait(bar + kVEmpty + 8 * s, ((i - 2) >> 1) & 1, (3u << 24) | (7u << 16) | (unsigned)i))) { ok = false; break; }
             unsigned char* pt = sm + kOffP + s * 16384;
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
@@ -496,6 +483,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_umma_kernel(ChunkArgs a) {
             fence_async_smem();
             tc_fence_before();
             mbar_arrive(bar + kPFull + 8 * s);
+            if (++ss == kKStages) { ss = 0; ++rs; }
         }
         if (ok && ntiles > 0 && !__all_sync(0xffffffffu, mbar_wait(bar + kOFull, 0, (3u << 24) | (6u << 16)))) ok = false;
         if (!ok) atomicExch(&s_fail, 1);

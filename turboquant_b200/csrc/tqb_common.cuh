@@ -8,6 +8,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "../../include/tqb200.h"
 
 namespace tqb {
@@ -71,6 +73,16 @@ __device__ __forceinline__ uint32_t extract_bits(uint32_t w0, uint32_t w1, int b
 }
 
 inline cudaStream_t as_stream(tqb_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
+
+// NVTX range around a C-ABI entry point (a few nanoseconds when no tool is attached): profilers show the library's
+// calls by name on the host timeline.
+struct NvtxRange {
+    explicit NvtxRange(const char* name) { nvtxRangePushA(name); }
+    ~NvtxRange() { nvtxRangePop(); }
+    NvtxRange(const NvtxRange&) = delete;
+    NvtxRange& operator=(const NvtxRange&) = delete;
+};
+#define TQB_NVTX_RANGE() ::tqb::NvtxRange tqb_nvtx_range_(__func__)
 
 // Sequence-parallel decode, fused exchange: where the CTA that finishes a KV head stores the head group's shard-local
 // record (un-normalised outputs, then (max, sum) pairs) - once per rank of the group, into that rank's receive buffer

@@ -356,6 +356,7 @@ static int check_layer(const tqb_pqo_cache* c, int32_t layer) {
 
 int tqb_pqo_cache_prefill(tqb_pqo_cache* c, int32_t layer, const void* k, const void* v, int32_t dtype,
                           int32_t new_tokens, void* k_out, void* v_out, int32_t host_buffers, tqb_stream_t stream) {
+    TQB_NVTX_RANGE();
     TQB_TRY(check_layer(c, layer));
     if (new_tokens < 0) return TQB_ERR_INVALID_ARGUMENT;
     if (dtype != TQB_F32 && dtype != TQB_F16 && dtype != TQB_BF16) return TQB_ERR_INVALID_ARGUMENT;
@@ -383,6 +384,7 @@ int tqb_pqo_cache_prefill(tqb_pqo_cache* c, int32_t layer, const void* k, const 
 int tqb_pqo_cache_prefill_attend(tqb_pqo_cache* c, int32_t layer, const void* k, const void* v, const void* q, int32_t dtype,
                                  int32_t new_tokens, int32_t num_q_heads, float softmax_scale, void* out,
                                  tqb_stream_t stream) {
+    TQB_NVTX_RANGE();
     TQB_TRY(check_layer(c, layer));
     if (new_tokens <= 0) return TQB_ERR_INVALID_ARGUMENT;
     if (dtype != TQB_F32 && dtype != TQB_F16 && dtype != TQB_BF16) return TQB_ERR_INVALID_ARGUMENT;
@@ -396,6 +398,7 @@ int tqb_pqo_cache_prefill_attend(tqb_pqo_cache* c, int32_t layer, const void* k,
 int tqb_pqo_cache_decode(tqb_pqo_cache* c, int32_t layer, const void* k, const void* v, const void* q, int32_t dtype,
                          int32_t num_q_heads, float softmax_scale, void* out, int32_t host_buffers,
                          tqb_stream_t stream) {
+    TQB_NVTX_RANGE();
     TQB_TRY(check_layer(c, layer));
     if (!k || !v || !q || !out) return TQB_ERR_NULL_POINTER;
     if (dtype != TQB_F32 && dtype != TQB_F16 && dtype != TQB_BF16) return TQB_ERR_INVALID_ARGUMENT;
@@ -444,6 +447,7 @@ int tqb_pqo_cache_host_sync(tqb_pqo_cache* c) {
 
 int tqb_pqo_cache_attend_partial(tqb_pqo_cache* c, int32_t layer, const void* q, int32_t dtype, int32_t num_q_heads,
                                  float softmax_scale, float* out_unnorm, float* lse_out, tqb_stream_t stream) {
+    TQB_NVTX_RANGE();
     TQB_TRY(check_layer(c, layer));
     if (!q || !out_unnorm || !lse_out) return TQB_ERR_NULL_POINTER;
     if (num_q_heads <= 0 || num_q_heads % c->cfg.num_kv_heads != 0) return TQB_ERR_INVALID_ARGUMENT;
@@ -452,6 +456,7 @@ int tqb_pqo_cache_attend_partial(tqb_pqo_cache* c, int32_t layer, const void* q,
 
 int tqb_pqo_cache_attend_push(tqb_pqo_cache* c, int32_t layer, const void* q, int32_t dtype, int32_t num_q_heads,
                               float softmax_scale, tqb_peer_exchange* x, tqb_stream_t stream) {
+    TQB_NVTX_RANGE();
     TQB_TRY(check_layer(c, layer));
     if (!q || !x) return TQB_ERR_NULL_POINTER;
     if (dtype != TQB_F32 && dtype != TQB_F16 && dtype != TQB_BF16) return TQB_ERR_INVALID_ARGUMENT;
@@ -465,6 +470,7 @@ int tqb_pqo_cache_attend_push(tqb_pqo_cache* c, int32_t layer, const void* q, in
 
 int tqb_pqo_cache_dequantize_full(tqb_pqo_cache* c, int32_t layer, void* k_out, void* v_out, int32_t dtype,
                                   int32_t host_buffers, tqb_stream_t stream) {
+    TQB_NVTX_RANGE();
     TQB_TRY(check_layer(c, layer));
     if (!k_out || !v_out) return TQB_ERR_NULL_POINTER;
     if (dtype != TQB_F32 && dtype != TQB_F16 && dtype != TQB_BF16) return TQB_ERR_INVALID_ARGUMENT;
@@ -642,6 +648,7 @@ static int kv_check_layer(const tqb_kv_cache* c, int32_t layer) {
 
 int tqb_kv_cache_push_batch(tqb_kv_cache* c, int32_t layer, const float* keys, const float* values, int64_t n,
                             int64_t vec_dim, tqb_stream_t stream) {
+    TQB_NVTX_RANGE();
     TQB_TRY(kv_check_layer(c, layer));
     if (vec_dim != c->cfg.dim) return TQB_ERR_DIMENSION_MISMATCH;  // attention.rs:241-242, :102-116
     if (n < 0) return TQB_ERR_INVALID_ARGUMENT;
@@ -668,6 +675,7 @@ int tqb_kv_cache_push_batch(tqb_kv_cache* c, int32_t layer, const float* keys, c
 
 int tqb_kv_cache_attention_scores(tqb_kv_cache* c, int32_t layer, const float* query, int64_t query_len, float* scores,
                                   tqb_stream_t stream) {
+    TQB_NVTX_RANGE();
     TQB_TRY(kv_check_layer(c, layer));
     if (query_len != c->cfg.dim) return TQB_ERR_DIMENSION_MISMATCH;
     auto& L = c->layers[layer];
@@ -690,6 +698,7 @@ int tqb_kv_cache_attention_scores(tqb_kv_cache* c, int32_t layer, const float* q
 
 int tqb_kv_cache_weighted_values(tqb_kv_cache* c, int32_t layer, const float* weights, int64_t num_weights, float* out,
                                  tqb_stream_t stream) {
+    TQB_NVTX_RANGE();
     TQB_TRY(kv_check_layer(c, layer));
     auto& L = c->layers[layer];
     if (num_weights != L.nk) return TQB_ERR_DIMENSION_MISMATCH;  // attention.rs:373
@@ -965,6 +974,7 @@ static int tq_check(const tqb_tq_cache* c, int32_t layer) {
 int tqb_tq_cache_prefill(tqb_tq_cache* c, int32_t layer, const void* k, const void* v, const void* q, int32_t dtype,
                          int32_t new_tokens, int32_t num_q_heads, int32_t q_len, void* k_out, void* v_out,
                          void* logit_bias, tqb_stream_t stream) {
+    TQB_NVTX_RANGE();
     TQB_TRY(tq_check(c, layer));
     if (new_tokens < 0 || q_len <= 0 || num_q_heads <= 0 || num_q_heads % c->base->cfg.num_kv_heads != 0)
         return TQB_ERR_INVALID_ARGUMENT;
@@ -980,6 +990,7 @@ int tqb_tq_cache_prefill(tqb_tq_cache* c, int32_t layer, const void* k, const vo
 
 int tqb_tq_cache_decode(tqb_tq_cache* c, int32_t layer, const void* k, const void* v, const void* q, int32_t dtype,
                         int32_t num_q_heads, void* k_out, void* v_out, void* logit_bias, tqb_stream_t stream) {
+    TQB_NVTX_RANGE();
     TQB_TRY(tq_check(c, layer));
     if (num_q_heads <= 0 || num_q_heads % c->base->cfg.num_kv_heads != 0) return TQB_ERR_INVALID_ARGUMENT;
     if (dtype != TQB_F32 && dtype != TQB_F16 && dtype != TQB_BF16) return TQB_ERR_INVALID_ARGUMENT;
@@ -992,6 +1003,7 @@ int tqb_tq_cache_decode(tqb_tq_cache* c, int32_t layer, const void* k, const voi
 
 int tqb_tq_cache_decode_fused(tqb_tq_cache* c, int32_t layer, const void* k, const void* v, const void* q, int32_t dtype,
                               int32_t num_q_heads, float softmax_scale, void* out, tqb_stream_t stream) {
+    TQB_NVTX_RANGE();
     TQB_TRY(tq_check(c, layer));
     if (num_q_heads <= 0 || num_q_heads % c->base->cfg.num_kv_heads != 0) return TQB_ERR_INVALID_ARGUMENT;
     if (dtype != TQB_F32 && dtype != TQB_F16 && dtype != TQB_BF16) return TQB_ERR_INVALID_ARGUMENT;

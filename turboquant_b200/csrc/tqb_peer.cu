@@ -187,6 +187,7 @@ int tqb_peer_exchange_check(const tqb_peer_exchange* x) {
 // merges them: out [num_q_heads, 128] of out_dtype.
 int tqb_peer_exchange_combine(tqb_peer_exchange* x, int32_t num_kv_heads, void* out, int32_t out_dtype, int64_t wait_cycles,
                               tqb_stream_t stream) {
+    TQB_NVTX_RANGE();
     if (!x || !out) return TQB_ERR_NULL_POINTER;
     if (!x->connected || x->seq == 0) return TQB_ERR_INVALID_ARGUMENT;
     if (num_kv_heads <= 0 || num_kv_heads > kPeerFlagHeads || x->hq % num_kv_heads != 0 || wait_cycles <= 0)

@@ -1014,6 +1014,7 @@ extern "C" {
 
 int tqb_quantize_batch(const tqb_config* cfg, const float* x, int64_t n, uint8_t* packed, uint16_t* scales,
                        tqb_stream_t stream) {
+    TQB_NVTX_RANGE();
     int st = tqb_config_validate(cfg);
     if (st != TQB_OK) return st;
     if (n < 0) return TQB_ERR_INVALID_ARGUMENT;
@@ -1031,6 +1032,7 @@ int tqb_quantize_batch(const tqb_config* cfg, const float* x, int64_t n, uint8_t
 
 int tqb_qjl_quantize_batch(const tqb_config* cfg, const uint32_t* rbits, const float* x, int64_t n, uint8_t* packed,
                            uint16_t* scales, uint8_t* signs, uint16_t* rnorms, tqb_stream_t stream) {
+    TQB_NVTX_RANGE();
     if (!cfg) return TQB_ERR_NULL_POINTER;
     if (cfg->bits < 3 || cfg->bits > 4) return TQB_ERR_UNSUPPORTED_BITS;  // src/qjl.rs:277-279
     tqb_config polar = *cfg;
@@ -1081,6 +1083,7 @@ static int dequant_common(const tqb_config* cfg, const uint8_t* packed, const ui
 
 int tqb_dequantize_batch(const tqb_config* cfg, const uint8_t* packed, const uint16_t* scales, int64_t n, float* out,
                          tqb_stream_t stream) {
+    TQB_NVTX_RANGE();
     return dequant_common(cfg, packed, scales, n, out, 0, stream);
 }
 
@@ -1111,6 +1114,7 @@ int tqb_qjl_query_projections(int32_t dim, const uint32_t* rbits, const float* q
 int tqb_qjl_attention_scores(const tqb_config* cfg, const float* q, const float* rq, const uint8_t* packed,
                              const uint16_t* scales, const uint8_t* signs, const uint16_t* rnorms, int64_t n,
                              float* scores, tqb_stream_t stream) {
+    TQB_NVTX_RANGE();
     if (!cfg) return TQB_ERR_NULL_POINTER;
     if (cfg->bits < 3 || cfg->bits > 4) return TQB_ERR_UNSUPPORTED_BITS;
     tqb_config polar = *cfg;
@@ -1158,6 +1162,7 @@ size_t tqb_weighted_values_scratch_bytes(int32_t dim) {
 
 int tqb_weighted_values(const tqb_config* cfg, const float* w, const uint8_t* packed, const uint16_t* scales, int64_t n,
                         float* out, void* scratch, size_t scratch_bytes, tqb_stream_t stream) {
+    TQB_NVTX_RANGE();
     if (!cfg) return TQB_ERR_NULL_POINTER;
     if (cfg->bits < 3 || cfg->bits > 4) return TQB_ERR_UNSUPPORTED_BITS;
     tqb_config polar = *cfg;
@@ -1205,6 +1210,7 @@ extern "C" {
 int tqb_residual_sketch(int32_t dim, const uint32_t* rbits, const void* original, int32_t dtype,
                         const float* dequantized, int64_t n, uint8_t* signs, uint16_t* norms, int64_t rows_per_group,
                         int64_t out_group_stride, int64_t out_row_offset, tqb_stream_t stream) {
+    TQB_NVTX_RANGE();
     if (dim != 32 && dim != 64 && dim != 128 && dim != 256)
         return (dim > 0 && dim % 32 == 0) ? TQB_ERR_UNSUPPORTED : TQB_ERR_INVALID_DIMENSION;
     if (n < 0 || rows_per_group < 0) return TQB_ERR_INVALID_ARGUMENT;
@@ -1238,6 +1244,7 @@ int tqb_residual_sketch(int32_t dim, const uint32_t* rbits, const void* original
 int tqb_qjl_logit_bias(int32_t head_dim, const float* rq, const uint8_t* signs, const uint16_t* norms, void* bias,
                        int32_t bias_dtype, int32_t num_q_heads, int32_t num_kv_heads, int32_t q_len, int32_t kv_len,
                        int32_t kv_stride, tqb_stream_t stream) {
+    TQB_NVTX_RANGE();
     if (head_dim <= 0 || head_dim % 32 != 0) return TQB_ERR_INVALID_DIMENSION;
     if (num_q_heads <= 0 || num_kv_heads <= 0 || num_q_heads % num_kv_heads != 0 || q_len <= 0) return TQB_ERR_INVALID_ARGUMENT;
     if (kv_len < 0 || kv_len > kv_stride) return TQB_ERR_RANGE_OUT_OF_BOUNDS;
