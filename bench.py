@@ -766,17 +766,21 @@ def run_chunk(args):
         vi, vs = tq.block_quantize(v, bits)
         ki, ks, vi, vs = (t.view(hkv, n, -1) for t in (ki, ks, vi, vs))
         q = (torch.randn((q_len, hq, d), device=dev) / d ** 0.5).bfloat16()
-        ts = []
-        for _ in range(args.warmup + args.steps):
-            e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
-            e0.record()
-            tq.chunk_attention(q, ki, ks, vi, vs, n, bits, 1.0 / d ** 0.5)
-            e1.record()
-            e1.synchronize()
-            ts.append(e0.elapsed_time(e1))
-        ms = float(np.median(ts[args.warmup:]))
+        def timed(fold):
+            ts, out = [], None
+            for _ in range(args.warmup + args.steps):
+                e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
+                e0.record()
+                out = tq.chunk_attention(q, ki, ks, vi, vs, n, bits, 1.0 / d ** 0.5, fold=fold)
+                e1.record()
+                e1.synchronize()
+                ts.append(e0.elapsed_time(e1))
+            return float(np.median(ts[args.warmup:])), out
+        ms, out = timed(False)                  # the tcgen05 chunk kernel
+        ms_fold, out_fold = timed(True)         # the chunk folded into decode launches (f32 / integer score path)
         attended = sum(past + i + 1 for i in range(q_len))          # (query token, key token) pairs per KV head group
-        rows.append({"past_tokens": past, "q_len": q_len, "ms": round(ms, 4),
+        rows.append({"past_tokens": past, "q_len": q_len, "ms": round(ms, 4), "ms_folded_into_decode": round(ms_fold, 4),
+                     "max_abs_diff_vs_folded": float((out.float() - out_fold.float()).abs().max()),
                      "cache_MB": round(n * hkv * bytes_per_token_head() / 1e6, 1),
                      "attended_GB/s": round(attended * hkv * bytes_per_token_head() / ms / 1e6, 1),
                      "attended_frac_of_measured_hbm_peak": round(attended * hkv * bytes_per_token_head() / ms / 1e6 / peak, 3),

@@ -404,6 +404,8 @@ def test_packed_shard_merge_equals_plain_shard_merge():
     (4, 32, 8, 700, 150, torch.bfloat16, False),   # several row tiles and cache tiles per CTA, ragged ends
     (3, 16, 8, 65, 130, torch.float32, False),     # g = 2, 3-bit
     (4, 2, 2, 40, 200, torch.float32, False),      # g = 1
+    (4, 32, 8, 0, 300, torch.bfloat16, False),     # first row tile sees 32 tokens: the second softmax group's tile is all masked
+    (3, 32, 8, 4000, 96, torch.float32, False),    # many steps: the stage and buffer rings wrap often
 ])
 def test_chunk_attention_is_causal_decode_per_query_token(bits, hq, hkv, past, q_len, dtype, general, fold):
     # prefill chunk over the packed cache: query token i must equal a decode step that sees past + i + 1 tokens.

@@ -6,20 +6,23 @@
 // cache in tiles of 64 tokens.  Each K / V tile is unpacked ONCE per CTA (the decode kernels, run once per query token,
 // unpack it once per token) and feeds M = 128 MMAs:
 //   S  = Q~ K~^T         K~ = |s_k| (c - 7.5) (4-bit grid; |s_k| centroid / kappa for 3-bit) and the rotated, pre-scaled
-//                        query, each rounded once to f16: eight MMAs (16 dims each) into a 128 x 64 f32 accumulator in
-//                        tensor memory.  Three accumulators rotate, so the tensor cores score tiles i + 1 and i + 2
-//                        while the softmax threads work on tile i.
-//   O  += P V            P = exp2(s - m) as f16 (K-major A operand, written by the softmax threads, double-buffered),
-//                        V dequantized with its scale to f16 (MN-major B operand), N = 128 dims: one 128 x 128 f32
-//                        accumulator.
+//                        query, each rounded once to f16.  The scores are taken 128 tokens (two tiles) at a time: eight
+//                        MMAs (16 dims each, N = 128) into a 128 x 128 f32 accumulator in tensor memory,
+//                        double-buffered, so the tensor cores score step j + 1 while the softmax threads work on step j.
+//   O_G += P V           P = exp2(s - m) as f16 (K-major A operand, written by the softmax threads), V dequantized with
+//                        its scale to f16 (MN-major B operand), N = 128 dims, one 128 x 128 f32 accumulator per
+//                        softmax group G.
+// Two softmax groups of four warps each: group G takes tile 2 j + G of every step (columns 64 G .. 64 G + 63 of the
+// step's scores) with its own running (max, sum), P buffer and O accumulator - two independent online softmaxes over
+// the even and the odd tiles, merged once at the end like two split-K partitions.  Thread r of a group owns query
+// row r = tensor-memory lane r, so the online softmax needs no shuffles; the output is rotated back in registers
+// (one 32-point butterfly per block) at the end.
 // The f16 roundings of Q~, K~, P and V are this kernel's error budget (a few 1e-4 of the value range on the outputs;
 // the decode kernels, which keep the query in f32 or as 20-bit integers, stay below 1e-5).
-// Thread r of the four softmax warps owns query row r = tensor-memory lane r, so the online softmax needs no
-// shuffles; the output is rotated back in registers (one 32-point butterfly per block) at the end.
 //
-// Warp roles: warps 0-3 softmax / correction / epilogue, warps 4-5 load and unpack K tiles (three stages), warps 6-9
-// V tiles (two stages), warp 10 issues the MMAs.  All hand-offs go through mbarriers; every wait is bounded and a wait
-// that runs out sets a flag, drains and returns (tqb_chunk_umma_timeouts).
+// Warp roles: warps 0-3 / 4-7 softmax group 0 / 1 (correction, epilogue), warps 8-9 load and unpack K tiles, warps
+// 10-13 V tiles (two stages each), warp 14 issues the MMAs.  All hand-offs go through mbarriers; every wait is
+// bounded and a wait that runs out sets a flag, drains and returns (tqb_chunk_umma_timeouts).
 #include <cuda.h>
 #include <float.h>
 
@@ -33,19 +36,19 @@ namespace {
 constexpr int kRows = 128;          // query rows per CTA
 constexpr int kTile = 64;           // cache tokens per step
 constexpr int kD = 128;
-constexpr int kThreads = 11 * 32;
+constexpr int kThreads = 15 * 32;
 constexpr float kNegBig = -1.0e30f;
 
 // shared-memory map (bytes from a 1024-aligned base)
-constexpr int kKStages = 3;                      // K stages = S buffers: the scores run two tiles ahead of the softmax
 constexpr int kOffQ = 0;                         // [2 atoms][128 rows][128 B]
-constexpr int kOffK = 32768;                     // [3 stages][2 atoms][64 tokens][128 B]
-constexpr int kOffV = kOffK + kKStages * 16384;  // [2 stages][2 dim halves][8 token groups][8 tokens][128 B]
+constexpr int kOffK = 32768;                     // [2 stages][2 atoms][128 tokens = two tiles][128 B]
+constexpr int kOffV = kOffK + 2 * 32768;         // [2 stages][2 dim halves][8 token groups][8 tokens][128 B]
 constexpr int kOffP = kOffV + 2 * 16384;         // [2 buffers][128 rows][128 B]
 constexpr int kOffLut = kOffP + 2 * 16384;       // 3-bit: 64 half2
 constexpr int kOffBar = kOffLut + 256;           // mbarriers
-constexpr int kSmemBytes = kOffBar + 128 + 1024; // + alignment slack
-constexpr uint32_t kTmemCols = 512;              // S buffers at columns 0, 64, 128; O at 192
+constexpr int kOffMl = kOffBar + 128;            // (max, sum) of every row of both softmax groups, for the final merge
+constexpr int kSmemBytes = kOffMl + 2048 + 1024; // + alignment slack
+constexpr uint32_t kTmemCols = 512;              // S buffers (128 columns: two tiles) at 0 and 128; O of group 0 at 256, of group 1 at 384
 
 struct ChunkArgs {
     const void* q;        // [q_len, hq, 128]
@@ -193,17 +196,18 @@ __device__ __forceinline__ float wht32_lane(float v, int lane) {
 // 16 consecutive bytes of a swizzled 128-byte row: chunk c of row `row` of a tile whose rows are 128 bytes apart
 __device__ __forceinline__ uint32_t sw128(int row, int chunk) { return (uint32_t)(row * 128 + ((chunk ^ (row & 7)) << 4)); }
 
-// ---- load + unpack role: IS_K ? warps 4-5 (K tiles, four pieces per thread) : warps 6-9 (V tiles, two pieces) ----
+// ---- load + unpack role: IS_K ? warps 8-9 (K tiles, four pieces per thread) : warps 10-13 (V tiles, two pieces) ----
 // A piece is one (token, block): 32 codes and their scale.  Eight consecutive lanes take the eight tokens of one token
 // group (eight distinct swizzle phases, so the 16-byte stores of a quarter-warp fall into eight different bank
 // groups), the four lane octets take the four blocks.  The packed pieces are fetched two tiles ahead of their use
 // (two register sets), so that the trip to L2 / HBM is never waited for.
+// K tiles 2 j and 2 j + 1 fill the two halves of K stage j % 2 (the scores are taken 128 tokens at a time); V tile i
+// goes to V stage i % 2.
 template <int BITS, bool IS_K>
 __device__ __forceinline__ bool unpack_role(const ChunkArgs& a, unsigned char* sm, uint32_t bar_full, uint32_t bar_empty, int w2, int lane,
                                             size_t row0, int kv_hi, int ntiles) {
     constexpr int NP = IS_K ? 4 : 2;             // pieces per thread and tile
     constexpr int TSTEP = kTile / NP;            // token distance between a thread's pieces
-    constexpr int NST = IS_K ? kKStages : 2;
     const int tl = 8 * w2 + (lane & 7), b = lane >> 3;
     const uint8_t* src_b = IS_K ? a.kb : a.vb;
     const uint16_t* src_s = IS_K ? a.ks : a.vs;
@@ -224,17 +228,20 @@ __device__ __forceinline__ bool unpack_role(const ChunkArgs& a, unsigned char* s
     };
     if (ntiles > 0) fetch(0, pq[0], sr[0]);
     if (ntiles > 1) fetch(1, pq[1], sr[1]);
-    int s = 0, round = 0;        // stage of tile i and how often the ring has wrapped
     auto unpack_tile = [&](int i, uint4 (&pqc)[NP], uint32_t (&src)[NP]) -> bool {
-        if (round > 0 && !mbar_wait(bar_empty + 8 * s, (round - 1) & 1, (1u << 24) | ((IS_K ? 2u : 3u) << 16) | (unsigned)i)) return false;
-        unsigned char* dst = sm + (IS_K ? kOffK : kOffV) + s * 16384;
+        const int use = IS_K ? (i >> 1) : i;      // the use-th filling of the stage ring (two stages)
+        const int st = use & 1;
+        if (use >= 2 && !mbar_wait(bar_empty + 8 * st, ((use >> 1) - 1) & 1, (1u << 24) | ((IS_K ? 2u : 3u) << 16) | (unsigned)i)) return false;
+        unsigned char* dst = sm + (IS_K ? kOffK + st * 32768 : kOffV + st * 16384);
 #pragma unroll
         for (int h = 0; h < NP; ++h) {
             const int t = tl + TSTEP * h;
             const uint32_t w[4] = {pqc[h].x, pqc[h].y, pqc[h].z, pqc[h].w};
             const __half2 sc2 = __half2half2(__habs(__ushort_as_half((unsigned short)src[h])));
-            // K: atom b / 2, row t, chunks 4 (b % 2) + j;  V: dim half b / 2, token group t / 8, row t % 8, same chunks
-            const uint32_t off = (uint32_t)(b >> 1) * 8192u + (IS_K ? 0u : (uint32_t)(t >> 3) * 1024u);
+            // K: atom b / 2 (16 KB apart), row 64 (i % 2) + t, chunks 4 (b % 2) + j;
+            // V: dim half b / 2 (8 KB apart), token group t / 8, row t % 8, same chunks
+            const uint32_t off = IS_K ? (uint32_t)(b >> 1) * 16384u + (uint32_t)(i & 1) * 8192u
+                                      : (uint32_t)(b >> 1) * 8192u + (uint32_t)(t >> 3) * 1024u;
             const int row = IS_K ? t : (t & 7);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -257,14 +264,13 @@ __device__ __forceinline__ bool unpack_role(const ChunkArgs& a, unsigned char* s
         }
         if (i + 2 < ntiles) fetch(i + 2, pqc, src);
         fence_async_smem();
-        mbar_arrive(bar_full + 8 * s);
-        if (++s == NST) { s = 0; ++round; }
+        mbar_arrive(bar_full + 8 * st);
         return true;
     };
     bool ok = true;
-    for (int i = 0; i < ntiles && ok; i += 2) {
+    for (int i = 0; i < ntiles && ok; i += 2) {     // ntiles is even
         ok = unpack_tile(i, pq[0], sr[0]);
-        if (ok && i + 1 < ntiles) ok = unpack_tile(i + 1, pq[1], sr[1]);
+        if (ok) ok = unpack_tile(i + 1, pq[1], sr[1]);
     }
     return ok;
 }
@@ -283,23 +289,21 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_umma_kernel(ChunkArgs a) {
     const int ntok = min(TQ, a.q_len - tok0);                   // valid query tokens in the tile
     const int past = a.kv_len - a.q_len;                        // tokens before the chunk
     const int kv_hi = past + tok0 + ntok;                       // cache tokens visible to the tile's last query token
-    const int ntiles = (kv_hi + kTile - 1) / kTile;
+    const int npairs = (kv_hi + 2 * kTile - 1) / (2 * kTile);   // steps of two tiles (128 tokens); a tile past the end is
+    const int ntiles = 2 * npairs;                              // unpacked from clamped rows and fully masked
     const size_t row0 = (size_t)kvh * a.kv_stride;
 
-    // barriers (8 bytes each, indexed by stage / buffer): K and V tiles are handed over separately, so that the scores
-    // of a later tile never wait for the P V product of an earlier one
+    // barriers (8 bytes each, indexed by stage / buffer / softmax group): K and V tiles are handed over separately, so
+    // that the scores of a later step never wait for the P V product of an earlier one
     const uint32_t bar = base + kOffBar;
-    constexpr uint32_t kKFull = 0, kKEmpty = 24, kVFull = 48, kVEmpty = 64, kSFull = 80, kPFull = 104, kOFull = 120;
+    constexpr uint32_t kKFull = 0, kKEmpty = 16, kVFull = 32, kVEmpty = 48, kSFull = 64, kPFull = 80, kOFull = 96;
     if (tid == 0) {
         s_fail = 0;
 #pragma unroll
-        for (int i = 0; i < kKStages; ++i) {
-            mbar_init(bar + kKFull + 8 * i, 64);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar + kKFull + 8 * i, 128);    // 64 threads, two tiles per stage
             mbar_init(bar + kKEmpty + 8 * i, 1);
             mbar_init(bar + kSFull + 8 * i, 1);
-        }
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
             mbar_init(bar + kVFull + 8 * i, 128);
             mbar_init(bar + kVEmpty + 8 * i, 1);
             mbar_init(bar + kPFull + 8 * i, 128);
@@ -344,85 +348,88 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_umma_kernel(ChunkArgs a) {
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = s_tmem;
-    const uint32_t tmemS = tmem, tmemO = tmem + kKStages * kTile;   // S buffer b at columns 64 b
+    const uint32_t tmemS = tmem, tmemO = tmem + 256;   // S buffer b at columns 128 b; O of softmax group G at 256 + 128 G
 
-    if (warp >= 4 && warp < 6) {
-        if (!unpack_role<BITS, true>(a, sm, bar + kKFull, bar + kKEmpty, warp - 4, lane, row0, kv_hi, ntiles)) atomicExch(&s_fail, 1);
-    } else if (warp >= 6 && warp < 10) {
-        if (!unpack_role<BITS, false>(a, sm, bar + kVFull, bar + kVEmpty, warp - 6, lane, row0, kv_hi, ntiles)) atomicExch(&s_fail, 1);
-    } else if (warp == 10) {
+    if (warp >= 8 && warp < 10) {
+        if (!unpack_role<BITS, true>(a, sm, bar + kKFull, bar + kKEmpty, warp - 8, lane, row0, kv_hi, ntiles)) atomicExch(&s_fail, 1);
+    } else if (warp >= 10 && warp < 14) {
+        if (!unpack_role<BITS, false>(a, sm, bar + kVFull, bar + kVEmpty, warp - 10, lane, row0, kv_hi, ntiles)) atomicExch(&s_fail, 1);
+    } else if (warp == 14) {
         // ================= MMA issue (one lane) =================
         if (lane == 0) {
-            constexpr uint32_t idescS = umma_idesc(kTile, false), idescO = umma_idesc(kD, true);
+            constexpr uint32_t idescS = umma_idesc(2 * kTile, false), idescO = umma_idesc(kD, true);
             bool ok = true;
             // Descriptors are built once: inside the loops a descriptor is its base plus a compile-time offset in the
             // address field (bytes >> 4), so that the one issuing thread spends a handful of instructions per MMA.
             const uint64_t dQ = umma_desc(base + kOffQ, 16, 1024), dK = umma_desc(base + kOffK, 16, 1024);
             const uint64_t dP = umma_desc(base + kOffP, 16, 1024), dV = umma_desc(base + kOffV, 8192, 1024);
-            // S = Q~ K~^T over 8 k-steps of 16 dims (atom = 64 dims, 32 bytes per k-step)
-            auto issue_qk = [&](int s) {      // s: K stage = S buffer of the tile
-                const uint64_t kk0 = dK + (uint64_t)(s * (16384 >> 4));
+            // S(j) = Q~ K~^T for the 128 tokens of step j: 8 k-steps of 16 dims (atom = 64 dims = 16 KB, 32 bytes per
+            // k-step), N = 128
+            auto score = [&](int j) -> bool {
+                const int st = j & 1;
+                if (!mbar_wait(bar + kKFull + 8 * st, (j >> 1) & 1, (2u << 24) | (0u << 16) | (unsigned)j)) return false;
+                tc_fence_after();
+                const uint64_t kk0 = dK + (uint64_t)(st * (32768 >> 4));
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk) {
-                    const uint64_t offq = (uint64_t)(((kk >> 2) * 16384 + (kk & 3) * 32) >> 4);
-                    const uint64_t offk = (uint64_t)(((kk >> 2) * 8192 + (kk & 3) * 32) >> 4);
-                    umma_f16(tmemS + s * kTile, dQ + offq, kk0 + offk, idescS, kk ? 1u : 0u);
+                    const uint64_t off = (uint64_t)(((kk >> 2) * 16384 + (kk & 3) * 32) >> 4);
+                    umma_f16(tmemS + st * 2 * kTile, dQ + off, kk0 + off, idescS, kk ? 1u : 0u);
                 }
-                umma_commit(bar + kSFull + 8 * s);
-                umma_commit(bar + kKEmpty + 8 * s);   // the K stage is free when these MMAs are done
-            };
-            // The scores run two tiles ahead of the softmax: S(i + 2) is issued before P(i) V(i), into the buffer that the
-            // softmax of tile i - 1 has finished reading (its p_full arrival was waited for one iteration earlier).
-            int sk = 0, rk = 0;   // K stage / S buffer of the next tile to score, and its ring round
-            auto score_next = [&](int i) -> bool {
-                if (!mbar_wait(bar + kKFull + 8 * sk, rk & 1, (2u << 24) | (0u << 16) | (unsigned)i)) return false;
-                tc_fence_after();
-                issue_qk(sk);
-                if (++sk == kKStages) { sk = 0; ++rk; }
+                umma_commit(bar + kSFull + 8 * st);
+                umma_commit(bar + kKEmpty + 8 * st);   // the K stage is free when these MMAs are done
                 return true;
             };
-            for (int i = 0; i < 2 && i < ntiles && ok; ++i) ok = score_next(i);
-            for (int i = 0; i < ntiles && ok; ++i) {
-                const int s = i & 1;
-                if (i + 2 < ntiles && !score_next(i + 2)) { ok = false; break; }
-                if (!mbar_wait(bar + kPFull + 8 * s, (i >> 1) & 1, (2u << 24) | (5u << 16) | (unsigned)i)) { ok = false; break; }
-                if (!mbar_wait(bar + kVFull + 8 * s, (i >> 1) & 1, (2u << 24) | (1u << 16) | (unsigned)i)) { ok = false; break; }
-                tc_fence_after();
-                // O += P V : four k-steps of 16 tokens
-                const uint64_t pv = dP + (uint64_t)(s * (16384 >> 4)), vv = dV + (uint64_t)(s * (16384 >> 4));
+            // The scores run one step (two tiles) ahead of the softmax groups: S(j + 1) is issued before the P V products
+            // of step j, into the buffer that both groups finished reading in step j - 1 (their p_full arrivals were
+            // waited for one iteration earlier).
+            if (npairs > 0) ok = score(0);
+            for (int j = 0; j < npairs && ok; ++j) {
+                if (j + 1 < npairs && !score(j + 1)) { ok = false; break; }
 #pragma unroll
-                for (int kk = 0; kk < 4; ++kk)
-                    umma_f16(tmemO, pv + (uint64_t)((kk * 32) >> 4), vv + (uint64_t)((kk * 2048) >> 4), idescO, (i | kk) ? 1u : 0u);
-                umma_commit(bar + kVEmpty + 8 * s);      // frees this V stage (and P buffer) when the MMAs issued so far are done
+                for (int G = 0; G < 2; ++G) {
+                    if (!mbar_wait(bar + kPFull + 8 * G, j & 1, (2u << 24) | (5u << 16) | (unsigned)j)) { ok = false; break; }
+                    if (!mbar_wait(bar + kVFull + 8 * G, j & 1, (2u << 24) | (1u << 16) | (unsigned)j)) { ok = false; break; }
+                    tc_fence_after();
+                    // O_G += P V : four k-steps of 16 tokens
+                    const uint64_t pv = dP + (uint64_t)(G * (16384 >> 4)), vv = dV + (uint64_t)(G * (16384 >> 4));
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk)
+                        umma_f16(tmemO + G * kD, pv + (uint64_t)((kk * 32) >> 4), vv + (uint64_t)((kk * 2048) >> 4), idescO, (j | kk) ? 1u : 0u);
+                    umma_commit(bar + kVEmpty + 8 * G);      // frees this V stage and P buffer when the MMAs issued so far are done
+                }
             }
             if (ok) umma_commit(bar + kOFull);           // everything issued so far has completed when this arrives
             else atomicExch(&s_fail, 1);
         }
         __syncwarp();
     } else {
-        // ================= softmax, correction, epilogue: thread = query row =================
-        const int r = tid;
+        // ================= softmax, correction, epilogue: two groups of four warps, thread = query row =================
+        // Group G takes tile 2 j + G of every step j (columns 64 G .. 64 G + 63 of the step's scores), with its own
+        // running (max, sum), P buffer and O accumulator: two independent online softmaxes over the even and the odd
+        // tiles, merged once at the end like two split-K partitions.
+        const int G = warp >> 2;
+        const int r = tid & 127;
         const int tq = r / g, hh = r - tq * g;
         const bool row_valid = tq < ntok;
         const int limit = past + tok0 + tq + 1;                 // visible cache tokens of this row
         const int limit_min = past + tok0 + 1;                  // ... of the tile's first row
-        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+        const uint32_t tmemOG = tmemO + G * kD;
         float m_run = kNegBig, l_run = 0.0f;
         bool ok = true;
-        int ss = 0, rs = 0;          // S buffer of tile i and its ring round
-        for (int i = 0; i < ntiles && ok; ++i) {
-            const int s = i & 1;     // P buffer / V stage
+        for (int j = 0; j < npairs && ok; ++j) {
+            const int i = 2 * j + G, sb = j & 1;
             // (the tensor-memory accesses below are warp-collective: the whole warp goes on, or none of it)
-            if (!__all_sync(0xffffffffu, mbar_wait(bar + kSFull + 8 * ss, rs & 1, (3u << 24) | (4u << 16) | (unsigned)i))) { ok = false; break; }
+            if (!__all_sync(0xffffffffu, mbar_wait(bar + kSFull + 8 * sb, (j >> 1) & 1, (3u << 24) | (4u << 16) | (unsigned)j))) { ok = false; break; }
             tc_fence_after();
             float p[kTile];
             {
                 uint32_t v0[32], v1[32];
-                tmem_ld32(tmemS + lane_base + ss * kTile, v0);
-                tmem_ld32(tmemS + lane_base + ss * kTile + 32, v1);
+                tmem_ld32(tmemS + lane_base + sb * 2 * kTile + G * kTile, v0);
+                tmem_ld32(tmemS + lane_base + sb * 2 * kTile + G * kTile + 32, v1);
                 tmem_wait_ld();
                 if ((i + 1) * kTile <= limit_min) {
-                    // every token of the tile is visible to every row (all tiles but the last one or two)
+                    // every token of the tile is visible to every row (all tiles but the last few)
 #pragma unroll
                     for (int t = 0; t < 32; ++t) {
                         p[t] = __uint_as_float(v0[t]);
@@ -442,37 +449,38 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_umma_kernel(ChunkArgs a) {
 #pragma unroll
             for (int t = 0; t < kTile; ++t) mx4[t & 3] = fmaxf(mx4[t & 3], p[t]);
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            // lazy maximum: raise the reference only when this tile exceeds it by more than 2^6
+            // lazy maximum: raise the reference only when this tile exceeds it by more than 2^6.  A row that has seen no
+            // visible token yet keeps the sentinel; the floor below then turns its masked scores into exp2(-huge) = 0.
             const float m_new = (mx - m_run > 6.0f) ? mx : m_run;
             const float resc = ex2(m_run - m_new);
+            const float m_use = fmaxf(m_new, -1.0e29f);
             m_run = m_new;
             float ls4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
             for (int t = 0; t < kTile; ++t) {
-                p[t] = ex2(p[t] - m_new);
+                p[t] = ex2(p[t] - m_use);
                 ls4[t & 3] += p[t];
             }
             l_run = l_run * resc + ((ls4[0] + ls4[1]) + (ls4[2] + ls4[3]));
-            if (i > 0 && __any_sync(0xffffffffu, resc != 1.0f)) {
-                // rescale this row of O, once the P V product of the previous tile has landed in it (warp-collective
-                // tensor-memory accesses: every lane takes part with its own factor)
-                if (!__all_sync(0xffffffffu, mbar_wait(bar + kVEmpty + 8 * (s ^ 1), ((i - 1) >> 1) & 1, (3u << 24) | (3u << 16) | (unsigned)i))) { ok = false; break; }
+            // the group's P V product of the previous step must be done: it read the P buffer written below and wrote
+            // the O accumulator rescaled here
+            if (j > 0 && !__all_sync(0xffffffffu, mbar_wait(bar + kVEmpty + 8 * G, (j - 1) & 1, (3u << 24) | (3u << 16) | (unsigned)j))) { ok = false; break; }
+            if (j > 0 && __any_sync(0xffffffffu, resc != 1.0f)) {
+                // rescale this row of O (warp-collective tensor-memory accesses: every lane takes part with its own factor)
                 tc_fence_after();
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     uint32_t v[32];
-                    tmem_ld32(tmemO + lane_base + c * 32, v);
+                    tmem_ld32(tmemOG + lane_base + c * 32, v);
                     tmem_wait_ld();
 #pragma unroll
                     for (int t = 0; t < 32; ++t) v[t] = __float_as_uint(__uint_as_float(v[t]) * resc);
-                    tmem_st32(tmemO + lane_base + c * 32, v);
+                    tmem_st32(tmemOG + lane_base + c * 32, v);
                 }
                 tmem_wait_st();
             }
-            // P -> shared memory (K-major A operand: row r, 64 tokens = 128 bytes, swizzled 16-byte chunks).  The buffer was
-            // read by the P V product of tile i - 2, which the scores of tile i (issued before it) do not order.
-            if (i >= 2 && !__all_sync(0xffffffffu, mbar_wait(bar + kVEmpty + 8 * s, ((i - 2) >> 1) & 1, (3u << 24) | (7u << 16) | (unsigned)i))) { ok = false; break; }
-            unsigned char* pt = sm + kOffP + s * 16384;
+            // P -> shared memory (K-major A operand: row r, 64 tokens = 128 bytes, swizzled 16-byte chunks)
+            unsigned char* pt = sm + kOffP + G * 16384;
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
                 uint32_t w[4];
@@ -482,30 +490,41 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_umma_kernel(ChunkArgs a) {
             }
             fence_async_smem();
             tc_fence_before();
-            mbar_arrive(bar + kPFull + 8 * s);
-            if (++ss == kKStages) { ss = 0; ++rs; }
+            mbar_arrive(bar + kPFull + 8 * G);
         }
-        if (ok && ntiles > 0 && !__all_sync(0xffffffffu, mbar_wait(bar + kOFull, 0, (3u << 24) | (6u << 16)))) ok = false;
+        if (ok && npairs > 0 && !__all_sync(0xffffffffu, mbar_wait(bar + kOFull, 0, (3u << 24) | (6u << 16)))) ok = false;
         if (!ok) atomicExch(&s_fail, 1);
         tc_fence_after();
-        if (ok && ntiles > 0) {
-            // ---- epilogue: O row -> rotate each 32-block back, normalise, store (every lane reads its row: the
-            // tensor-memory loads are warp-collective; rows past the chunk's end are just not stored) ----
-            const float inv_l = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+        // ---- merge of the two groups: exchange (max, sum) through shared memory; all eight warps meet here ----
+        float2* ml = reinterpret_cast<float2*>(sm + kOffMl);
+        ml[G * kRows + r] = make_float2(m_run, l_run);
+        asm volatile("bar.sync 1, 256;\n" ::: "memory");
+        if (ok && npairs > 0) {
+            const float2 other = ml[(G ^ 1) * kRows + r];
+            const float M = fmaxf(m_run, other.x);
+            const float w_self = ex2(fmaxf(m_run - M, -200.0f)), w_other = ex2(fmaxf(other.x - M, -200.0f));
+            const float w0 = G == 0 ? w_self : w_other, w1 = G == 0 ? w_other : w_self;
+            const float l_tot = l_run * w_self + other.y * w_other;
+            // ---- epilogue: group G takes blocks 2 G and 2 G + 1 of the row: O = w0 O_0 + w1 O_1, rotate the 32-block
+            // back, normalise, store (every lane reads its row: the tensor-memory loads are warp-collective; rows past
+            // the chunk's end are just not stored) ----
+            const float inv_l = l_tot > 0.0f ? 1.0f / l_tot : 0.0f;
             const float inv_sqrt = 1.0f / sqrtf(32.0f);
             const uint32_t neg = 0xB1A6D4B2u;
             const size_t orow = ((size_t)(tok0 + tq) * a.hq + kvh * g + hh) * kD;
 #pragma unroll 1
-            for (int b = 0; b < 4; ++b) {
-                uint32_t v[32];
-                tmem_ld32(tmemO + lane_base + b * 32, v);
+            for (int b = 2 * G; b < 2 * G + 2; ++b) {
+                uint32_t va[32], vb[32];
+                tmem_ld32(tmemO + lane_base + b * 32, va);
+                tmem_ld32(tmemO + kD + lane_base + b * 32, vb);
                 tmem_wait_ld();
                 float x[32];
 #pragma unroll
                 for (int pz = 0; pz < 32; ++pz) {
                     const int d = BITS == 4 ? ((pz & ~7) | perm4(pz & 7)) : pz;   // column pz of the block holds dim d
                     const float sgn = ((neg >> d) & 1u) ? -a.sign_mag : a.sign_mag;
-                    x[d] = (__uint_as_float(v[pz]) * a.v_const) * sgn;
+                    const float o = __uint_as_float(va[pz]) * w0 + __uint_as_float(vb[pz]) * w1;
+                    x[d] = (o * a.v_const) * sgn;
                 }
 #pragma unroll
                 for (int h = 1; h < 32; h <<= 1)
@@ -528,10 +547,10 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_umma_kernel(ChunkArgs a) {
                     else reinterpret_cast<__nv_bfloat16*>(a.out)[idx] = __float2bfloat16_rn(o);
                 }
             }
-            if (a.lse_out != nullptr && row_valid) {
+            if (a.lse_out != nullptr && row_valid && G == 0) {
                 float* lse = a.lse_out + ((size_t)(tok0 + tq) * a.hq + kvh * g + hh) * 2;
-                lse[0] = m_run * 0.6931471805599453f;
-                lse[1] = l_run;
+                lse[0] = M * 0.6931471805599453f;
+                lse[1] = l_tot;
             }
         }
     }
