@@ -158,6 +158,9 @@ def run_ours(args):
     peak, peak_src = peaks()
     cache = tq.PqoCache(tq.CacheConfig(bits=BITS, head_dim=D, num_kv_heads=HKV, num_layers=L, batch=BL))
     att = tq.AttendConfig(softmax_scale=scale, n_kv_groups=HQ // HKV)
+    # the launches of successive layers overlap head to tail (programmatic dependent launch): a step's inputs are not
+    # outputs of the launch before them
+    cache.set_overlap(not args.no_overlap)
 
     # ---- fill the cache with the batched quantize kernel ----
     # The bulk-quantize figure is taken on the last layer's K/V into buffers allocated beforehand (a cache
@@ -285,6 +288,7 @@ def run_ours(args):
             "config": {"workload": WORKLOAD, "format": "PQO4 block-32 MaxNorm", "kv_dtype": "bf16", "q_dtype": "bf16",
                        "accumulate_dtype": "f32 (f16 tensor-core operands split hi + lo; every product exact)",
                        "l2": "inputs larger than L2 (%.1f GB packed cache per GPU)" % (L * BL * HKV * CTX * bytes_per_token_head() / 1e9),
+                       "launches": "one per layer; %s" % ("strictly ordered" if args.no_overlap else "successive layers overlap head to tail (programmatic dependent launch)"),
                        "sharding": "one batch-64 problem dealt out by (batch, kv head) units, %d sequences per GPU, no collective" % BL},
             "tokens_per_s": round(B * args.steps / (ms * 1e-3), 1),
             "pct_of_hbm_peak": round(100 * value / (peak * world), 2),
@@ -796,6 +800,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU legs (baseline and parity against the oracle)")
+    ap.add_argument("--no-overlap", action="store_true", help="headline: order the layers' launches strictly (no programmatic dependent launch)")
     ap.add_argument("--no-extras", action="store_true", help="headline only: skip the pqo3 / config3 / seq_parallel records")
     ap.add_argument("--profile-case", action="store_true",
                     help="small case for profiler captures: 2 layers, batch 16 (151 MB of packed cache per launch, "

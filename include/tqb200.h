@@ -285,6 +285,15 @@ typedef struct tqb_decode_params {
  * running the chunk kernel; the cross-check of that kernel. */
 #define TQB_DECODE_FOLD_CHUNK 16
 
+/* flags: this launch may START before the previous kernel on the stream has finished (programmatic dependent launch),
+ * when that kernel is one of the library's tensor-core decode launches: its streaming pass then overlaps the
+ * predecessor's tail and split-K merge, and waits for the predecessor's completion only before it writes the scratch,
+ * the tickets and the outputs.  The caller vouches that nothing this launch READS - q, append_k / append_v, rq, the
+ * cache arrays - is written by the immediately preceding kernel on the stream, except rows appended by that kernel
+ * (those are stored and fenced before a successor may start).  Honoured together with TQB_DECODE_TICKETS_ZERO on the
+ * head_dim-128 tensor-core path; ignored elsewhere (the launch is then ordered like any other). */
+#define TQB_DECODE_OVERLAP 32
+
 /* Diagnostic: how many bounded waits on a staged tile ran out on the current device since the library was
  * loaded (synchronises the device).  Always 0 in a healthy run; -1 on a CUDA error.  A non-zero count invalidates
  * the outputs of the TQB_DECODE_TMA calls since the last check.  No reference counterpart. */
@@ -386,6 +395,12 @@ int tqb_pqo_cache_dequantize_full(tqb_pqo_cache *c, int32_t layer, void *k_out, 
 int64_t tqb_pqo_cache_seq_len(const tqb_pqo_cache *c, int32_t layer);
 int64_t tqb_pqo_cache_capacity(const tqb_pqo_cache *c, int32_t layer);
 int tqb_pqo_cache_reset(tqb_pqo_cache *c);
+/* enabled != 0: the decode launches of this cache (tqb_pqo_cache_decode with device buffers, tqb_pqo_cache_attend_partial,
+ * tqb_pqo_cache_attend_push) are made with TQB_DECODE_OVERLAP whenever the layer differs from the layer of the
+ * cache's previous decode launch, so that the launches of successive layers overlap head to tail.  The caller vouches
+ * that q / new_k / new_v of a call are not written by the immediately preceding kernel on the stream (in a model
+ * they come from a projection kernel in between, which orders them).  Off by default.  No reference counterpart. */
+int tqb_pqo_cache_set_overlap(tqb_pqo_cache *c, int32_t enabled);
 size_t tqb_pqo_cache_memory_usage(const tqb_pqo_cache *c);
 /* Device pointers of one layer's storage (k_indices, k_scales, v_indices, v_scales). */
 int tqb_pqo_cache_layer_ptrs(const tqb_pqo_cache *c, int32_t layer, const uint8_t **k_indices,

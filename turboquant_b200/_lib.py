@@ -103,6 +103,7 @@ def _declare(lib):
         "tqb_pqo_cache_seq_len": (L, [P, I]),
         "tqb_pqo_cache_capacity": (L, [P, I]),
         "tqb_pqo_cache_reset": (c_int, [P]),
+        "tqb_pqo_cache_set_overlap": (c_int, [P, I]),
         "tqb_pqo_cache_memory_usage": (S, [P]),
         "tqb_pqo_cache_layer_ptrs": (c_int, [P, I, P, P, P, P]),
         "tqb_pqo_cache_export_layer": (c_int, [P, I, P, P, P, P, I, P]),

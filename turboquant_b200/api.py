@@ -635,6 +635,11 @@ class PqoCache:
             lib.tqb_pqo_cache_destroy(h)
             self._h = None
 
+    def set_overlap(self, enabled=True):
+        """Let the decode launches of successive layers overlap head to tail (tqb_pqo_cache_set_overlap): the caller
+        vouches that a call's q / k / v are not written by the kernel launched just before it."""
+        check(lib.tqb_pqo_cache_set_overlap(self._h, 1 if enabled else 0))
+
     def _host(self, t):
         return 0 if t.is_cuda else 1
 

@@ -96,6 +96,8 @@ struct MmaArgs {
     float qjl_const;
     // sequence-parallel decode: the merging CTA of a KV head pushes the head group's record to every rank (world == 0: off)
     PeerPush peer;
+    // host side only: launch with programmatic stream serialization (TQB_DECODE_OVERLAP)
+    int overlap;
 };
 
 __device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
@@ -485,10 +487,16 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
             }
             const_cast<uint16_t*>(is_v ? a.vs : a.ks)[row * 4 + warp] = f32_to_f16_bits(-scale);   // outlier blocks store -scale
         }
-        __threadfence_block();
+        __threadfence();   // device-wide: a later launch that starts early (below) reads these rows
         if (TMA) asm volatile("fence.proxy.async;\n" ::: "memory");   // the tensor copies read through the async proxy
         __syncthreads();
     }
+    // Programmatic dependent launch.  From here on the next kernel on the stream may start on the SMs this grid leaves
+    // free, IF it was launched with programmatic stream serialization (TQB_DECODE_OVERLAP): its streaming pass then
+    // overlaps this grid's tail and merge.  Such a launch reads q, the appended vectors and the cache early, and
+    // waits for this grid's completion (griddepcontrol.wait, further down) before it touches what the two share: the
+    // split-K scratch, the tickets and the outputs.  The appended row was stored and fenced above.
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     // cp.async: every warp owns a ring of 16-token stages.  TMA: the CTA owns a ring of 64-token tiles and
     // `ring` / `st` address this warp's K rows inside a tile.
     constexpr uint32_t kPitch = TMA ? G::kTileB : G::kStageB;           // distance between stages
@@ -1056,6 +1064,9 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
             s_o[warp][2 * j + 1][d0 + 1] = o[b][m][3];
         }
     __syncthreads();
+    // everything below writes memory that the previous launch on the stream may still use (scratch, tickets, outputs):
+    // wait for it to complete (returns at once unless this launch was allowed to start early)
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
     {
         const int d = tid;
         for (int hh = 0; hh < g; ++hh) {
@@ -1232,6 +1243,21 @@ int launch_one(const MmaArgs& a, const TmaMaps& maps, const Codebook& app_cb, di
         if (e != cudaSuccess) { set_cuda_error(e); return TQB_ERR_CUDA; }
         if (dev >= 0) configured.fetch_or(1ull << dev, std::memory_order_release);
     }
+    if (a.overlap) {
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = dyn;
+        cfg.stream = s;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        cudaError_t e = cudaLaunchKernelEx(&cfg, decode_mma_kernel<QT, BITS, NSPLIT, TMA, QJL>, a, maps, app_cb);
+        if (e != cudaSuccess) { set_cuda_error(e); return TQB_ERR_CUDA; }
+        return check_launch(s);
+    }
     decode_mma_kernel<QT, BITS, NSPLIT, TMA, QJL><<<grid, kThreads, dyn, s>>>(a, maps, app_cb);
     return check_launch(s);
 }
@@ -1320,6 +1346,8 @@ int launch_decode_mma(const tqb_decode_params* p, int num_partitions, float* par
         if (counters == nullptr || peer->world > kMaxPeers || p->num_kv_heads > kPeerFlagHeads) return TQB_ERR_UNSUPPORTED;
         a.peer = *peer;
     }
+    // early start only for the plain fused launch: no gate written by a check kernel, no memset between the launches
+    a.overlap = ((p->flags & TQB_DECODE_OVERLAP) != 0 && gate == nullptr && counters != nullptr && counters_clean) ? 1 : 0;
     a.counters = counters;
     a.out = p->out;
     a.lse_out = p->lse_out;

@@ -85,6 +85,9 @@ struct tqb_pqo_cache {
     };
     std::vector<Layer> layers;
     DevBuf stage_k, stage_v, stage_q, stage_out, scratch;
+    // tqb_pqo_cache_set_overlap: decode launches of different layers may start before their predecessor has finished
+    bool overlap = false;
+    int last_attend_layer = -1;
     // Host-buffer decode: two staging slots and a copy stream, so that the host->device copies of
     // one call and the device->host copy of the previous call overlap with kernels.
     struct Slot {
@@ -257,6 +260,9 @@ struct tqb_pqo_cache {
         p.scratch = scratch.p;
         p.scratch_bytes = scratch.bytes;
         p.flags = TQB_DECODE_TICKETS_ZERO;
+        // two launches on the same layer in a row stay ordered: the second reads what the first appended
+        if (overlap && layer != last_attend_layer) p.flags |= TQB_DECODE_OVERLAP;
+        last_attend_layer = layer;
         p.append_k = append_k;
         p.append_v = append_v;
         return tqb_decode_attention(&p, s);
@@ -482,6 +488,14 @@ int64_t tqb_pqo_cache_seq_len(const tqb_pqo_cache* c, int32_t layer) {
 }
 int64_t tqb_pqo_cache_capacity(const tqb_pqo_cache* c, int32_t layer) {
     return check_layer(c, layer) == TQB_OK ? c->layers[layer].cap : -1;
+}
+
+// No reference counterpart: lets the decode launches of successive layers overlap head to tail (TQB_DECODE_OVERLAP).
+int tqb_pqo_cache_set_overlap(tqb_pqo_cache* c, int32_t enabled) {
+    if (!c) return TQB_ERR_NULL_POINTER;
+    c->overlap = enabled != 0;
+    c->last_attend_layer = -1;
+    return TQB_OK;
 }
 
 // CompressedStorage::reset (src/cache/storage.rs:175-185): drops the buffers.
