@@ -191,7 +191,7 @@ def run_ours(args):
     quant_ms = float(np.median(qt))
 
     g = torch.Generator(device=dev).manual_seed(1234)
-    n_tok = 3 * (args.warmup + args.steps) + 8
+    n_tok = 4 * (args.warmup + args.steps) + 8
     newk = torch.randn((4, B, HKV, 1, D), generator=g, device=dev).to(torch.bfloat16)[:, b_lo:b_hi].contiguous()
     newv = torch.randn((4, B, HKV, 1, D), generator=g, device=dev).to(torch.bfloat16)[:, b_lo:b_hi].contiguous()
     qs = (torch.randn((4, B, HQ, 1, D), generator=g, device=dev) * scale).to(torch.bfloat16)[:, b_lo:b_hi].contiguous()
@@ -206,6 +206,10 @@ def run_ours(args):
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
+
+    def cool_down():
+        barrier()
+        time.sleep(1.0)
 
     def bytes_of_steps(first_len, nsteps):
         # each step attends over the cache after its own append
@@ -226,7 +230,24 @@ def run_ours(args):
     barrier()
     ms = e0.elapsed_time(e1)
     step_bytes = bytes_of_steps(len0, args.steps)
-
+    # the same steps with the launches strictly ordered (no programmatic dependent launch).  Every block starts after a
+    # second of idling and its own warm-up, so that the power state one block leaves behind does not colour the next.
+    ordered = None
+    if not args.no_overlap:
+        cache.set_overlap(False)
+        cool_down()
+        for i in range(args.warmup):
+            step_device(i)
+        barrier()
+        len_o = cache.seq_len(0)
+        o0, o1 = torch.cuda.Event(True), torch.cuda.Event(True)
+        o0.record()
+        for i in range(args.steps):
+            step_device(i)
+        o1.record()
+        barrier()
+        ordered = (o0.elapsed_time(o1), bytes_of_steps(len_o, args.steps))
+        cache.set_overlap(True)
     # ---- e2e: host buffers through PqoCache.decode ----
     hk = [newk[i].cpu().pin_memory() for i in range(4)]
     hv = [newv[i].cpu().pin_memory() for i in range(4)]
@@ -238,6 +259,7 @@ def run_ours(args):
             cache.decode(layer, hk[i % 4], hv[i % 4], hq_[(i + layer) % 4], att, out=hout[layer])
         cache.host_sync()   # the step's results are on the host
 
+    cool_down()
     for i in range(args.warmup):
         step_host(i)
     barrier()
@@ -267,14 +289,15 @@ def run_ours(args):
 
     # ---- max over ranks ----
     if dist is not None:
-        t = torch.tensor([ms, e2e_ms], device=dev)
+        t = torch.tensor([ms, e2e_ms, ordered[0] if ordered else 0.0], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_ms = t.tolist()
-        tb = torch.tensor([float(step_bytes), float(e2e_bytes)], device=dev, dtype=torch.float64)
+        ms, e2e_ms, ord_ms = t.tolist()
+        tb = torch.tensor([float(step_bytes), float(e2e_bytes), float(ordered[1] if ordered else 0)], device=dev, dtype=torch.float64)
         dist.all_reduce(tb)
-        total_bytes, total_e2e_bytes = tb.tolist()
+        total_bytes, total_e2e_bytes, ord_bytes = tb.tolist()
     else:
         total_bytes, total_e2e_bytes = step_bytes, e2e_bytes
+        ord_ms, ord_bytes = ordered if ordered else (0.0, 0)
     value = total_bytes / (ms * 1e-3) / 1e9
     e2e_value = total_e2e_bytes / (e2e_ms * 1e-3) / 1e9
 
@@ -294,6 +317,9 @@ def run_ours(args):
             "pct_of_hbm_peak": round(100 * value / (peak * world), 2),
             "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "tokens_per_s": round(B * args.steps / (e2e_ms * 1e-3), 1)},
+            "ordered_launches": ({"value": round(ord_bytes / (ord_ms * 1e-3) / 1e9, 2), "unit": "GB/s", "ms_per_step": round(ord_ms / args.steps, 4),
+                                  "what": "the same steps with every launch waiting for the one before it (no programmatic dependent launch)"}
+                                 if ordered else None),
             "gpu_launches": args.steps * L * world,   # per layer and rank: one kernel (append of the new token, attention, split-K merge)
             "roofline": {"bound": "hbm", "kernel": "decode attention (split-K pass)", "achieved": round(achieved, 1),
                          "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4), "traffic": None,
@@ -379,7 +405,10 @@ def extra_pqo3(tq, w, lib, dev, args, peak):
     def step():
         for layer in range(L):
             cache.decode(layer, nk, nk, q, att, out=out)
+    ms_ordered = timed_chain(step, 2, max(3, args.steps))
+    cache.set_overlap(True)     # successive layers' launches overlap head to tail, as in the headline
     ms = timed_chain(step, 2, max(3, args.steps))
+    cache.set_overlap(False)
     step_bytes = L * B * HKV * cache.seq_len(0) * bpt
     launch_ms, units = kernel_launch_ms(lib, cache, list(range(L)), q.reshape(B * HQ, D), B * HQ, 3, scale)
     ach = units * bpt / (launch_ms * 1e-3) / 1e9
@@ -387,6 +416,7 @@ def extra_pqo3(tq, w, lib, dev, args, peak):
     par = float(np.abs(got - w.oracle_decode_of_layer(cache, 0, q, scale, nthreads=os.cpu_count() or 1)).max()) if not args.no_cpu else None
     return {"workload": "the headline shape stored as PQO3: 8 layers x 64 sequences x 8 kv heads x ctx 8192",
             "value": round(step_bytes / (ms * 1e-3) / 1e9, 1), "unit": "GB/s", "ms_per_8_layers": round(ms, 4),
+            "value_ordered_launches": round(step_bytes / (ms_ordered * 1e-3) / 1e9, 1),
             "tokens_per_s_at_32_layers": round(B / (ms * 4e-3), 1),
             "roofline": {"bound": "hbm", "kernel": "decode attention (split-K pass), PQO3", "achieved": round(ach, 1), "peak": peak,
                          "unit": "GB/s", "frac": round(ach / peak, 4), "launch_us": round(launch_ms * 1e3, 1),
@@ -462,7 +492,7 @@ def extra_config3(tq, w, lib, dev, args, peak):
         # (i) one call per layer from Python: rewinds nothing, the cache grows by one token per step
         calls_ms = timed_chain(step, 2, max(5, args.steps))
         # (ii) CUDA graph per copy: 28 launches, replayed round-robin
-        graph_ms = None
+        graph_ms = graph_o_ms = None
         try:
             graphs = []
             side = torch.cuda.Stream()
@@ -480,6 +510,24 @@ def extra_config3(tq, w, lib, dev, args, peak):
                 graphs[it["i"] % copies].replay()
                 it["i"] += 1
             graph_ms = timed_chain(replay, 3, max(20, 2 * args.steps))
+            # (iii) the same graphs captured with the layers' launches allowed to overlap head to tail: an upper bound for
+            # an engine whose other kernels fill the gaps (here nothing sits between two attention launches)
+            cache.set_overlap(True)
+            graphs_o = []
+            with torch.cuda.stream(side):
+                for c in range(copies):
+                    gph = torch.cuda.CUDAGraph()
+                    state["c"] = c
+                    with torch.cuda.graph(gph, stream=side, capture_error_mode="relaxed"):
+                        step()
+                    graphs_o.append(gph)
+            cache.set_overlap(False)
+            torch.cuda.synchronize()
+
+            def replay_o():
+                graphs_o[it["i"] % copies].replay()
+                it["i"] += 1
+            graph_o_ms = timed_chain(replay_o, 3, max(20, 2 * args.steps))
         except Exception as exc:
             graph_ms = None
             rows.append({"ctx": ctx, "graph_error": repr(exc)[:200]})
@@ -491,6 +539,9 @@ def extra_config3(tq, w, lib, dev, args, peak):
             row.update({"graph_us_per_step": round(graph_ms * 1e3, 1), "graph_us_per_layer": round(graph_ms * 1e3 / L, 2),
                         "graph_frac_of_hbm_peak": round(roof_us / (graph_ms * 1e3), 4),
                         "tokens_per_s_graph": round(1.0 / (graph_ms * 1e-3), 1)})
+        if graph_o_ms is not None:
+            row.update({"graph_overlapped_us_per_step": round(graph_o_ms * 1e3, 1),
+                        "graph_overlapped_frac_of_hbm_peak": round(roof_us / (graph_o_ms * 1e3), 4)})
         rows.append(row)
         del cache
         torch.cuda.empty_cache()
