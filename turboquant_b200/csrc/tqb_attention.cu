@@ -409,10 +409,12 @@ int32_t tqb_decode_num_partitions(int32_t num_kv_heads, int32_t kv_len) {
     // between one and two times the 148 x 4 CTAs that are resident at once - 512 heads x 8192 tokens run 4 %
     // faster split in 2 than in 4, and 7 % faster than unsplit (which leaves 14 % of the slots empty); more,
     // shorter partitions pay the per-CTA query prologue and merge again.  So: two residencies' worth of CTAs
-    // while a partition keeps at least 768 tokens, else one residency's worth, never below 64 tokens.
+    // while a partition keeps at least 768 tokens, else one residency's worth, never below 64 tokens.  One
+    // residency's worth is rounded DOWN: 64 heads x 10 partitions are 640 CTAs for 592 slots, and the 48 left over
+    // start when the first ones end - the launch takes twice as long as with 9 partitions.
     const long long resident = 148 * 4;
     const int max_p = (kv_len + 63) / 64;
-    const long long p1 = (resident + num_kv_heads - 1) / num_kv_heads;
+    const long long p1 = resident / num_kv_heads;
     long long p2 = 2 * resident / num_kv_heads;
     if (p2 < 1) p2 = 1;
     long long p = kv_len / p2 >= 768 ? p2 : p1;

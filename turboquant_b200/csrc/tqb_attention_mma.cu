@@ -454,7 +454,15 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
     const int kvh = blockIdx.x, part = blockIdx.y;
     const int g = a.g;
 
-    // ---- start streaming the first stages before anything else: the copies do not depend on q ----
+    // ---- the queries first: eight small loads per thread that are in flight ahead of the bulk copies started next,
+    // instead of queueing behind them (one (head, block) unit per load; consumed after the copies are issued) ----
+    float qpre[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int u = warp + kWarps * i, hh = u >> 2, b = u & 3;
+        qpre[i] = hh < g ? to_f32<QT>(reinterpret_cast<const QT*>(a.q)[(size_t)(kvh * g + hh) * kD + b * 32 + lane]) : 0.0f;
+    }
+    // ---- start streaming the first stages: the copies do not depend on q ----
     int kv_len = a.kv_len, cache_head = kvh;
     if (a.alias_heads > 0) {
         const int pos = kvh / a.alias_heads;
@@ -577,11 +585,10 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
         const float mag = a.dev_signs != nullptr ? fabsf(a.dev_signs[0]) : a.sign_mag;
         const float sign = ((neg >> lane) & 1u) ? -mag : mag;
         const float inv_sqrt = 1.0f / sqrtf(32.0f);
-        for (int u = warp; u < 8 * 4; u += kWarps) {
-            const int hh = u >> 2, b = u & 3;
-            float v = 0.0f;
-            if (hh < g) v = to_f32<QT>(reinterpret_cast<const QT*>(a.q)[(size_t)(kvh * g + hh) * kD + b * 32 + lane]);
-            v = wht32_lane(v, lane);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int u = warp + kWarps * i, hh = u >> 2, b = u & 3;
+            const float v = wht32_lane(qpre[i], lane);
             s_q[hh * kD + b * 32 + lane] = ((v * inv_sqrt) * sign) * a.qk_const;
         }
     }
