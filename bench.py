@@ -98,6 +98,9 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+EXTRA_DECODE_FLAGS = 0   # --profile-general: TQB_DECODE_FORCE_GENERAL on the per-launch timing of the small case
+
+
 def stream_ptr():
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
@@ -123,7 +126,7 @@ def kernel_launch_ms(lib, cache, layers, q2, hq_total, bits, scale, reps=2):
             p.q_dtype = p.out_dtype = code
             p.bits, p.head_dim, p.norm_mode, p.outlier_blocks = bits, d, 0, -1
             p.num_q_heads, p.num_kv_heads, p.kv_len, p.kv_stride = hq_total, nheads, kv_len, cache.capacity(layer)
-            p.num_partitions, p.softmax_scale, p.flags = parts, scale, 1     # split-K pass only
+            p.num_partitions, p.softmax_scale, p.flags = parts, scale, 1 | EXTRA_DECODE_FLAGS     # split-K pass only
             s0, s1 = torch.cuda.Event(True), torch.cuda.Event(True)
             s0.record()
             rc = lib.tqb_decode_attention(ctypes.byref(p), stream_ptr())
@@ -858,6 +861,8 @@ def main():
                          "above the L2 size, 0.4 GB on the device); its numbers are not bench values")
     ap.add_argument("--profile-bits", type=int, default=4, choices=[3, 4],
                     help="with --profile-case: code width of the small case (3 = PQO3, 4 = PQO4)")
+    ap.add_argument("--profile-general", action="store_true",
+                    help="with --profile-case: the per-launch timing runs the general (any shape, SIMT) decode kernel")
     ap.add_argument("--whole-vector", action="store_true",
                     help="secondary report: the whole-vector (core crate) kernels, 2^19 vectors / 2^21 keys of d = 128 "
                          "(0.3 GB on the device); also the small case for profiler captures of those kernels")
@@ -878,6 +883,9 @@ def main():
         return
     if args.profile_case:
         CFG.update(layers=2, batch=16, bits=args.profile_bits)
+        if args.profile_general:
+            global EXTRA_DECODE_FLAGS
+            EXTRA_DECODE_FLAGS = 2
         args.no_cpu = True
         args.no_extras = True
     if args.impl == "reference":
