@@ -312,7 +312,7 @@ def run_ours(args):
             "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": WORKLOAD, "format": "PQO4 block-32 MaxNorm", "kv_dtype": "bf16", "q_dtype": "bf16",
-                       "accumulate_dtype": "f32 (f16 tensor-core operands split hi + lo; every product exact)",
+                       "accumulate_dtype": "scores: s8 x s8 integer tensor-core MMAs on 20-bit query digits, s32 accumulate, exact; P V: f16 tensor-core operands split hi + lo, f32 accumulate",
                        "l2": "inputs larger than L2 (%.1f GB packed cache per GPU)" % (L * BL * HKV * CTX * bytes_per_token_head() / 1e9),
                        "launches": "one per layer; %s" % ("strictly ordered" if args.no_overlap else "successive layers overlap head to tail (programmatic dependent launch)"),
                        "sharding": "one batch-64 problem dealt out by (batch, kv head) units, %d sequences per GPU, no collective" % BL},
