@@ -100,8 +100,8 @@ struct MmaArgs {
     int overlap;
 };
 
-__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_relaxed_sys(unsigned* p, unsigned v) {
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
 }
 
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -1154,9 +1154,18 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
             // on every rank (plain stores over NVLink; nobody is waited for here)
             __threadfence_system();
             __syncthreads();
+            // Lane c of the first warp releases rank c's flag: ONE system-scope fence for the warp, then eight stores
+            // that travel side by side.  (A release-store per rank, one after the other, paid a fence - a round trip
+            // over NVLink - per rank: 26 us at eight ranks.)  The pointer is picked by selects: a run-time index
+            // into the argument block would move it to local memory.
+            if (tid < kMaxPeers) {
+                unsigned* f = nullptr;
 #pragma unroll
-            for (int c = 0; c < kMaxPeers; ++c)
-                if (tid == c && c < a.peer.world) st_release_sys(a.peer.flag[c] + kvh, a.peer.seq);
+                for (int c = 0; c < kMaxPeers; ++c)
+                    if (tid == c && c < a.peer.world) f = a.peer.flag[c];
+                __threadfence_system();
+                if (f != nullptr) st_relaxed_sys(f + kvh, a.peer.seq);
+            }
         }
     }
 }
