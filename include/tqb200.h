@@ -301,6 +301,9 @@ long long tqb_decode_stage_timeouts(void);
 
 /* Partitions the library would use for this shape, and the scratch it then needs. */
 int32_t tqb_decode_num_partitions(int32_t num_kv_heads, int32_t kv_len);
+/* The same for launches made with TQB_DECODE_OVERLAP: fewer, longer partitions (several launches are resident at
+ * once, so one launch need not fill the GPU by itself). */
+int32_t tqb_decode_num_partitions_overlapped(int32_t num_kv_heads, int32_t kv_len);
 size_t tqb_decode_scratch_bytes(int32_t num_q_heads, int32_t head_dim, int32_t num_partitions);
 int tqb_decode_attention(const tqb_decode_params *p, tqb_stream_t stream);
 

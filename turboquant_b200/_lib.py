@@ -85,6 +85,7 @@ def _declare(lib):
         "tqb_block_quantize_pair": (c_int, [I, I, I, I, P, P, I, L, L, P, P, P, P, L, L, L, P]),
         "tqb_block_dequantize": (c_int, [I, I, I, I, P, P, L, L, L, L, P, I, P]),
         "tqb_decode_num_partitions": (I, [I, I]),
+        "tqb_decode_num_partitions_overlapped": (I, [I, I]),
         "tqb_decode_scratch_bytes": (S, [I, I, I]),
         "tqb_decode_attention": (c_int, [P, P]),
         "tqb_chunk_attention": (c_int, [P, ctypes.c_int32, P]),

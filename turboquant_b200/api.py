@@ -519,12 +519,15 @@ def block_dequantize(indices, scales, bits, head_dim, norm_mode=QuantNormMode.Ma
 
 def decode_attention(q, k_idx, k_sc, v_idx, v_sc, kv_len, bits, softmax_scale, norm_mode=QuantNormMode.MaxNorm,
                      outlier_blocks=ALL_BLOCKS, num_partitions=0, out_dtype=None, return_lse=False, qjl=None,
-                     scratch=None, out=None, partials_only=False, force_general=False, tma=False, append=None):
+                     scratch=None, out=None, partials_only=False, force_general=False, tma=False, append=None,
+                     overlap=False):
     """Fused decode attention over packed K/V.
 
     q [Hq, D]; k_idx/v_idx [Hkv, kv_stride, D*bits/8]; k_sc/v_sc [Hkv, kv_stride, D/32].
     qjl = (signs [Hkv, kv_stride, D/8], norms [Hkv, kv_stride], rq [Hq, D]) enables the
-    correction of tq_attention_kernel.cu:197-231."""
+    correction of tq_attention_kernel.cu:197-231.
+    overlap=True: TQB_DECODE_OVERLAP | TQB_DECODE_TICKETS_ZERO - the launch may start before the previous decode
+    launch on the stream has finished; `scratch` must then be given, zero-filled once by the caller."""
     hq, d = q.shape
     hkv, stride = k_idx.shape[0], k_idx.shape[1]
     q = q.contiguous()
@@ -548,6 +551,9 @@ def decode_attention(q, k_idx, k_sc, v_idx, v_sc, kv_len, bits, softmax_scale, n
     p.num_q_heads, p.num_kv_heads, p.kv_len, p.kv_stride = hq, hkv, kv_len, stride
     p.num_partitions, p.softmax_scale = parts, softmax_scale
     p.flags = (1 if partials_only else 0) | (2 if force_general else 0) | (8 if tma else 0)
+    if overlap:
+        assert scratch is not None, "overlap=True needs a caller-owned scratch whose ticket area is zero"
+        p.flags |= 4 | 32
     if append is not None:   # (k, v): the new token's vectors [Hkv, D] in q's dtype, written to row kv_len - 1
         ak, av = (t.contiguous() for t in append)
         assert ak.dtype == q.dtype and av.dtype == q.dtype

@@ -423,6 +423,21 @@ int32_t tqb_decode_num_partitions(int32_t num_kv_heads, int32_t kv_len) {
     return (int32_t)p;
 }
 
+// Partition count for launches made with TQB_DECODE_OVERLAP.  Several such launches are resident at once (the next one
+// fills the slots the previous one frees), so a launch need not fill the GPU by itself: fewer, longer partitions pay
+// the query prologue and the split-K merge less often.  Measured on B200 (PQO4, 8192 tokens, overlapped chain, us per
+// launch): 64 heads: P = 2 or 3 -> 15.0, P = 9 -> 18.3; 128 heads: P = 1 or 2 -> 28.2, P = 4 -> 29.8; 256 heads: P = 1 ->
+// 55.5, P = 4 -> 61.1; 512 heads: P = 1 -> 110.5, P = 2 -> 112.5.  So: about one CTA per SM and launch, partitions of
+// at least 768 tokens.
+int32_t tqb_decode_num_partitions_overlapped(int32_t num_kv_heads, int32_t kv_len) {
+    if (num_kv_heads <= 0 || kv_len <= 0) return 1;
+    long long p = 148 / num_kv_heads;
+    const long long cap = kv_len / 768;
+    if (p > cap) p = cap;
+    if (p < 1) p = 1;
+    return (int32_t)p;
+}
+
 // Scratch layout: [merge tickets: (1 + G) u32 per query head, rounded up to 256 bytes][partial out [hq, P, D]]
 // [partial max [hq, P]][partial sum [hq, P]][group partials: out [hq, G, D], max [hq, G], sum [hq, G]], where
 // G = merge_groups(P) is the number of partition groups of the two-level merge (0 up to kMergeGroup partitions).

@@ -1040,12 +1040,26 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
             if (boff + 8 == 8 * kStages) { boff = 0; parity ^= 1u; } else boff += 8;
         }
     }
+    bool gave_up = false;
     if (TMA) {
         if (!stage_ok && lane == 0) atomicAdd(&g_stage_timeouts, 1u);
+        // a wait on a staged tile ran out in some warp: the whole partition is dropped (it merges as an empty
+        // partition: weight 0) rather than merged half done; the count above tells the host
+        gave_up = __syncthreads_or(stage_ok ? 0 : 1) != 0;
     } else {
         cp_async_wait<0>();
+        __syncthreads();    // all rings idle: the memory is reused for the merge
     }
-    __syncthreads();    // all rings idle: the memory is reused for the merge
+    if (gave_up) {
+#pragma unroll
+        for (int e = 0; e < kE; ++e) { m_run[e] = kNegBig; l_run[e] = 0.0f; }
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+#pragma unroll
+            for (int m = 0; m < 2; ++m)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) o[b][m][i] = 0.0f;
+    }
 
     // ---- merge the four warps (scores are in log2 units; partials are stored in natural units) ----
 #pragma unroll

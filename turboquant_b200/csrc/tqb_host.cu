@@ -253,16 +253,20 @@ struct tqb_pqo_cache {
         p.num_kv_heads = heads;
         p.kv_len = (int32_t)l.len;
         p.kv_stride = (int32_t)l.cap;
-        p.num_partitions = tqb_decode_num_partitions(heads, (int32_t)l.len);
+        // two launches on the same layer in a row stay ordered: the second reads what the first appended
+        const bool early = overlap && layer != last_attend_layer;
+        last_attend_layer = layer;
+        // (with the overlap switched on every launch takes the overlapped partition count, also the ordered ones in
+        // between: the scratch layout then stays the same from launch to launch)
+        p.num_partitions = overlap ? tqb_decode_num_partitions_overlapped(heads, (int32_t)l.len)
+                                   : tqb_decode_num_partitions(heads, (int32_t)l.len);
         p.softmax_scale = softmax_scale;
         const size_t need = tqb_decode_scratch_bytes(p.num_q_heads, cfg.head_dim, p.num_partitions);
         TQB_TRY(prepare_scratch(scratch, ticket_heads, need, p.num_q_heads, cfg.head_dim, p.num_partitions, s));
         p.scratch = scratch.p;
         p.scratch_bytes = scratch.bytes;
         p.flags = TQB_DECODE_TICKETS_ZERO;
-        // two launches on the same layer in a row stay ordered: the second reads what the first appended
-        if (overlap && layer != last_attend_layer) p.flags |= TQB_DECODE_OVERLAP;
-        last_attend_layer = layer;
+        if (early) p.flags |= TQB_DECODE_OVERLAP;
         p.append_k = append_k;
         p.append_v = append_v;
         return tqb_decode_attention(&p, s);
