@@ -380,9 +380,13 @@ int tqb_pqo_cache_prefill(tqb_pqo_cache *c, int32_t layer, const void *k, const 
 int tqb_pqo_cache_decode(tqb_pqo_cache *c, int32_t layer, const void *k, const void *v, const void *q,
                          int32_t dtype, int32_t num_q_heads, float softmax_scale, void *out,
                          int32_t host_buffers, tqb_stream_t stream);
-/* With host_buffers != 0, tqb_pqo_cache_decode moves data on an internal copy stream so that copies overlap
- * kernels of neighbouring calls; the host `out` buffers are complete once this call returns (it blocks the
- * calling thread on the last outstanding result copy). */
+/* With host_buffers != 0, tqb_pqo_cache_decode takes host pointers.  Pinned, device-mapped buffers (cudaHostAlloc or
+ * cudaHostRegister under unified addressing) are read and written by the attention kernel itself over PCIe - no
+ * staging copy, nothing between two launches, so they overlap like device-resident ones (tqb_pqo_cache_set_overlap).
+ * Other host memory is staged: inputs go up on an internal copy stream into one of two slots, the result comes down
+ * on a second one, so that copies overlap the kernels of neighbouring calls.  Either way the caller's k / v / q are
+ * in use and `out` is incomplete until tqb_pqo_cache_host_sync() returns (it blocks the calling thread on the
+ * outstanding work of this cache). */
 int tqb_pqo_cache_host_sync(tqb_pqo_cache *c);
 /* Prefill with attention inside the cache: quantize and append the chunk (as tqb_pqo_cache_prefill), then causal
  * attention of its new_tokens queries over everything stored (tqb_chunk_attention).  The reference's prefill

@@ -380,6 +380,42 @@ def test_pqo_cache_growth_batch_and_host_buffers():
     assert np.abs(out_host.float().numpy().reshape(24, 128) - want).max() < 1e-2   # bf16 output rounding
 
 
+@pytest.mark.parametrize("overlap", [False, True])
+def test_host_buffer_modes_give_the_same_bits(overlap):
+    """tqb_pqo_cache_decode with host buffers: pinned (mapped) buffers are read and written by the kernel itself,
+    pageable ones are staged through copy streams; both must give the bits of the device-buffer call, over several
+    layers and steps, with and without overlapping launches."""
+    layers, batch, hkv, hq, d, ctx, steps = 3, 4, 2, 8, 128, 700, 3
+    g = torch.Generator().manual_seed(9)
+    k = torch.randn((batch, hkv, ctx, d), generator=g).bfloat16()
+    v = torch.randn((batch, hkv, ctx, d), generator=g).bfloat16()
+    nk = torch.randn((steps, layers, batch, hkv, 1, d), generator=g).bfloat16()
+    nv = torch.randn((steps, layers, batch, hkv, 1, d), generator=g).bfloat16()
+    q = (torch.randn((steps, layers, batch, hq, 1, d), generator=g) / d ** 0.5).bfloat16()
+    att = tq.AttendConfig(1.0 / d ** 0.5, hq // hkv)
+    outs = {}
+    for mode in ("device", "pinned", "pageable"):
+        cache = tq.PqoCache(tq.CacheConfig(bits=4, head_dim=d, num_kv_heads=hkv, num_layers=layers, batch=batch))
+        cache.set_overlap(overlap)
+        for layer in range(layers):
+            cache.prefill(layer, k.cuda(), v.cuda())
+        conv = {"device": lambda t: t.cuda(), "pinned": lambda t: t.clone().pin_memory(), "pageable": lambda t: t.clone()}[mode]
+        res = torch.zeros((steps, layers, batch, hq, 1, d), dtype=torch.bfloat16)
+        res = conv(res)
+        held = []
+        for s_ in range(steps):
+            for layer in range(layers):
+                args = [conv(nk[s_, layer]), conv(nv[s_, layer]), conv(q[s_, layer])]
+                held.append(args)          # host buffers stay alive (and untouched) until host_sync
+                cache.decode(layer, *args, att, out=res[s_, layer])
+            cache.host_sync()
+        torch.cuda.synchronize()
+        outs[mode] = res.cpu().clone()
+    assert torch.equal(outs["device"], outs["pinned"])
+    assert torch.equal(outs["device"], outs["pageable"])
+    assert float(outs["device"].float().abs().max()) > 0.0
+
+
 def test_packed_shard_merge_equals_plain_shard_merge():
     # tqb_lse_combine_packed reads [out | (max, sum)] records, one per shard: the layout of a single all-gather
     g = torch.Generator(device="cuda").manual_seed(5)

@@ -99,6 +99,10 @@ struct tqb_pqo_cache {
     cudaStream_t copy_stream = nullptr;   // host -> device
     cudaStream_t down_stream = nullptr;   // device -> host
     cudaEvent_t last_out = nullptr;   // completion of the most recent device->host output copy
+    // Host buffers that are pinned and mapped are read and written by the kernels themselves (no staging copies):
+    // the stream of the most recent such call, waited for by tqb_pqo_cache_host_sync
+    bool direct_pending = false;
+    cudaStream_t direct_stream = nullptr;
 
     int ensure_pipeline() {
         if (copy_stream) return TQB_OK;
@@ -418,6 +422,27 @@ int tqb_pqo_cache_decode(tqb_pqo_cache* c, int32_t layer, const void* k, const v
     const size_t kv_bytes = (size_t)c->heads * c->cfg.head_dim * esz;
     const size_t q_bytes = (size_t)c->cfg.batch * num_q_heads * c->cfg.head_dim * esz;
     if (!host_buffers) return c->append_and_attend(layer, k, v, q, dtype, num_q_heads, softmax_scale, out, s);
+    // Pinned, device-mapped host buffers (cudaHostAlloc / cudaHostRegister under unified addressing): the attention
+    // kernel reads k, v and q over PCIe itself and the merging CTAs store the result straight into `out`.  No copy
+    // engine, no event between two launches - so the launches of successive layers can overlap like device-resident
+    // ones - and the bytes cross PCIe once per step all the same.  The caller's buffers are in use until
+    // tqb_pqo_cache_host_sync(), exactly as with the staged copies below.
+    {
+        void* dev[4] = {nullptr, nullptr, nullptr, nullptr};
+        const void* host[4] = {k, v, q, out};
+        bool mapped = true;
+        for (int i = 0; i < 4 && mapped; ++i) {
+            cudaPointerAttributes at{};
+            if (cudaPointerGetAttributes(&at, host[i]) != cudaSuccess) { cudaGetLastError(); mapped = false; break; }
+            mapped = at.type == cudaMemoryTypeHost && at.devicePointer != nullptr;
+            dev[i] = at.devicePointer;
+        }
+        if (mapped) {
+            const int st = c->append_and_attend(layer, dev[0], dev[1], dev[2], dtype, num_q_heads, softmax_scale, dev[3], s);
+            if (st == TQB_OK) { c->direct_pending = true; c->direct_stream = s; }
+            return st;
+        }
+    }
     // Host buffers: inputs go up on one copy stream into one of two staging slots, the kernels run on
     // the caller's stream once the slot is filled, and the result goes down on a second copy stream
     // once they are done, so the next call's inputs travel while this call's kernels run.  A slot is
@@ -452,6 +477,10 @@ int tqb_pqo_cache_decode(tqb_pqo_cache* c, int32_t layer, const void* k, const v
 int tqb_pqo_cache_host_sync(tqb_pqo_cache* c) {
     if (!c) return TQB_ERR_NULL_POINTER;
     if (c->last_out) TQB_CUDA(cudaEventSynchronize(c->last_out));
+    if (c->direct_pending) {
+        c->direct_pending = false;
+        TQB_CUDA(cudaStreamSynchronize(c->direct_stream));
+    }
     return TQB_OK;
 }
 
