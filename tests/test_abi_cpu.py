@@ -121,3 +121,19 @@ def test_argument_errors_are_reported_before_any_launch():
     assert lib.tqb_decode_attention(None, None) == 6
     assert lib.tqb_decode_num_partitions(8, 1024) >= 1
     assert lib.tqb_decode_scratch_bytes(16, 128, 4) == 256 + 4 * 16 * 4 * 130   # merge tickets + partials
+
+
+def test_partition_choosers_are_host_functions():
+    """tqb_decode_num_partitions: one to two residencies' worth of CTAs (148 SMs x 4), the single residency rounded down;
+    tqb_decode_num_partitions_overlapped: about one CTA per SM and launch, partitions of at least 768 tokens."""
+    from turboquant_b200._lib import lib
+    assert lib.tqb_decode_num_partitions(512, 8192) == 2        # 2 x 592 / 512 = 2, partitions of 4096 tokens
+    assert lib.tqb_decode_num_partitions(64, 8192) == 9         # 592 / 64 rounded down: 576 CTAs, one wave
+    assert lib.tqb_decode_num_partitions(8, 131072) == 148      # two residencies, 885 tokens each
+    assert lib.tqb_decode_num_partitions(8, 100) == 2           # never below 64 tokens per partition
+    assert lib.tqb_decode_num_partitions(1000, 8192) == 1
+    assert lib.tqb_decode_num_partitions_overlapped(512, 8192) == 1
+    assert lib.tqb_decode_num_partitions_overlapped(64, 8192) == 2
+    assert lib.tqb_decode_num_partitions_overlapped(8, 131072) == 18
+    assert lib.tqb_decode_num_partitions_overlapped(8, 1024) == 1
+    assert lib.tqb_decode_num_partitions_overlapped(0, 5) == 1
