@@ -164,3 +164,30 @@ def test_overlapped_launches_equal_ordered_launches_bit_for_bit(bits, parts):
         outs[overlap] = o_.cpu()
     assert torch.equal(outs[False], outs[True])
     assert torch.equal(outs[True][0], outs[True][2])
+
+
+def test_overlapped_launch_after_a_foreign_kernel_sees_its_output():
+    """The contract of TQB_DECODE_OVERLAP in a model: q of a layer is written by another kernel (here a torch
+    elementwise op on the same stream) launched just before the attention call.  That kernel does not let its
+    successor start early, so the overlapped launch is ordered behind it like any other launch and reads the new q."""
+    hkv, hq, d, batch, ctx, layers = 8, 32, 128, 4, 900, 5
+    g = torch.Generator(device="cuda").manual_seed(3)
+    k = torch.randn((batch, hkv, ctx, d), generator=g, device="cuda").to(torch.bfloat16)
+    nk = torch.randn((batch, hkv, 1, d), generator=g, device="cuda").to(torch.bfloat16)
+    q0 = (torch.randn((batch, hq, 1, d), generator=g, device="cuda") / d ** 0.5).float()
+    att = tq.AttendConfig(softmax_scale=1.0 / d ** 0.5, n_kv_groups=hq // hkv)
+    res = []
+    for overlap in (False, True):
+        cache = tq.PqoCache(tq.CacheConfig(bits=4, head_dim=d, num_kv_heads=hkv, num_layers=layers, batch=batch))
+        cache.set_overlap(overlap)
+        for layer in range(layers):
+            cache.prefill(layer, k, k)
+        outs = []
+        x = q0.clone()
+        for step in range(3):
+            for layer in range(layers):
+                x = x * 0.999 + 0.001 * (layer + 1)            # the "projection": a kernel that writes this layer's q
+                outs.append(cache.decode(layer, nk, nk, x, att).fused.clone())
+        torch.cuda.synchronize()
+        res.append(torch.stack(outs).cpu())
+    assert float((res[0] - res[1]).abs().max()) < 1e-5          # same inputs; only the split-K partitioning differs
