@@ -312,7 +312,9 @@ int tqb_decode_attention(const tqb_decode_params *p, tqb_stream_t stream);
  * its prefill dequantizes the whole cache and hands it to the engine's attention (src/cache/pqo.rs:184-200,
  * src/cache/common.rs:16-62).
  * head_dim 128, GQA group 1 / 2 / 4 / 8, PQO4 or a 3-bit format of the tensor-core kernels, no QJL: a dedicated kernel
- * on the tcgen05 tensor cores (128 query rows per CTA, every K / V tile unpacked once per CTA; scratch unused).
+ * on the tcgen05 tensor cores (128 query rows per CTA, every K / V tile unpacked once per CTA; scratch unused).  It
+ * rounds the rotated query, the keys, the probabilities and the values to f16 once each: outputs within 1e-3 of the
+ * CPU attention over the same bytes (the folded path: 1e-4).
  * Everything else, or TQB_DECODE_FOLD_CHUNK: the chunk is folded into the decode kernels, one grid head per query
  * token.  tqb_chunk_umma_timeouts() counts bounded waits of the dedicated kernel that ran out (always 0 in a healthy
  * run; a non-zero count invalidates the outputs since the last check; synchronises the device).
