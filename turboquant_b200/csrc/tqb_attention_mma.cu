@@ -740,7 +740,7 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
         rqc[e] = QJL ? s_qsc[NSPLIT ? j : 2 * j + e] * a.qjl_const : 0.0f;
         rqsum[e] = QJL ? s_rqsum[NSPLIT ? j : 2 * j + e] : 0;
     }
-    // QJL: sketch word j and residual norm of tokens n and n + 8 of the step, fetched one step ahead (tokens past
+    // QJL: sketch word j and residual norm of tokens n and n + 8 of the step, fetched two steps ahead (tokens past
     // the end re-read the last token; they are masked later)
     uint32_t sgw[2] = {0u, 0u};
     uint32_t nrw[2] = {0u, 0u};
@@ -752,7 +752,11 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
             nr[t] = __ldg(a.qjl_norms + row);
         }
     };
+    // (two steps ahead: one step is shorter than a trip to HBM)
+    uint32_t sg1[2] = {0u, 0u};
+    uint32_t nr1[2] = {0u, 0u};
     if (QJL && nsteps > 0) qjl_fetch(0, sgw, nrw);
+    if (QJL && nsteps > 1) qjl_fetch(1, sg1, nr1);
     float m_run[kE], l_run[kE];   // per head; l_run: this lane's tokens only
 #pragma unroll
     for (int e = 0; e < kE; ++e) {
@@ -878,7 +882,7 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
             for (int e = 0; e < kE; ++e) sc[t][e] = BITS == 4 ? s[t][e] * qsc[e] : s[t][e];
         if constexpr (QJL) {
             uint32_t sgn[2] = {0u, 0u}, nrn[2] = {0u, 0u};
-            if (it + 1 < nsteps) qjl_fetch(it + 1, sgn, nrn);   // next step's sketch words, in flight during this step
+            if (it + 2 < nsteps) qjl_fetch(it + 2, sgn, nrn);   // the sketch words of the step after next, in flight for two steps
             int ca[4] = {0, 0, 0, 0}, cb[4] = {0, 0, 0, 0}, cc[4] = {0, 0, 0, 0};
             static_for<0, 4>([&](auto m_) {
                 constexpr int m4 = decltype(m_)::value;
@@ -909,7 +913,8 @@ __global__ void __launch_bounds__(kThreads, 4) decode_mma_kernel(MmaArgs a, cons
                 sc[1][0] = fmaf((float)(2 * iv[2] - rqsum[0]), n1 * rqc[0], sc[1][0]);
                 sc[1][1] = fmaf((float)(2 * iv[3] - rqsum[1]), n1 * rqc[1], sc[1][1]);
             }
-            sgw[0] = sgn[0]; sgw[1] = sgn[1]; nrw[0] = nrn[0]; nrw[1] = nrn[1];
+            sgw[0] = sg1[0]; sgw[1] = sg1[1]; nrw[0] = nr1[0]; nrw[1] = nr1[1];
+            sg1[0] = sgn[0]; sg1[1] = sgn[1]; nr1[0] = nrn[0]; nr1[1] = nrn[1];
         }
         if (it >= rag_from) {   // ragged tail: tokens past the end (of the sequence, or of the partition) get zero weight
             const int gs = first + it * stride;

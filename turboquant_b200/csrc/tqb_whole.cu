@@ -838,18 +838,20 @@ template <int EPL, typename T>
 __global__ void residual_sketch_kernel(const T* __restrict__ x, const float* __restrict__ xhat, long long n,
                                        const uint32_t* __restrict__ rbits, uint8_t* __restrict__ signs,
                                        uint16_t* __restrict__ norms, long long rows_per_group, long long group_stride,
-                                       long long row_offset, float inv_sqrt_d) {
+                                       long long row_offset, float inv_sqrt_d, int vt) {
+    // vt: vectors per warp tile (1..kTile).  A warp sketches the vectors of its tile one after the other (~3 us each),
+    // so a small batch - the 512 new keys of a decode step - is spread one vector per warp instead of 32.
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int D = 32 * EPL, W = EPL;
     uint32_t* s_rb = reinterpret_cast<uint32_t*>(smem_raw);
     const int warps = blockDim.x >> 5, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    float* tile = reinterpret_cast<float*>(s_rb + D * (W + 1)) + (size_t)warp * kTile * (D + 1);
+    float* tile = reinterpret_cast<float*>(s_rb + D * (W + 1)) + (size_t)warp * vt * (D + 1);
     for (int i = threadIdx.x; i < D * W; i += blockDim.x) s_rb[(i / W) * (W + 1) + (i % W)] = rbits[i];
     __syncthreads();
-    const long long tiles = (n + kTile - 1) / kTile;
+    const long long tiles = (n + vt - 1) / vt;
     for (long long t = (long long)blockIdx.x * warps + warp; t < tiles; t += (long long)gridDim.x * warps) {
-        const long long v0 = t * kTile;
-        const int nv = (int)min((long long)kTile, n - v0);
+        const long long v0 = t * vt;
+        const int nv = (int)min((long long)vt, n - v0);
         for (int r = 0; r < nv; ++r)
 #pragma unroll
             for (int i = 0; i < EPL; ++i) {
@@ -1220,8 +1222,12 @@ int tqb_residual_sketch(int32_t dim, const uint32_t* rbits, const void* original
     if (dtype != TQB_F32 && dtype != TQB_F16 && dtype != TQB_BF16) return TQB_ERR_INVALID_ARGUMENT;
     cudaStream_t s = as_stream(stream);
     const int W = dim / 32, warps = dim >= 256 ? 2 : 4;
-    const size_t smem = sizeof(uint32_t) * dim * (W + 1) + sizeof(float) * warps * kTile * (dim + 1);
-    const long long tiles = (n + kTile - 1) / kTile;
+    // vectors per warp tile: enough tiles for ~16 warps on every SM before a warp takes a second vector
+    long long vt = (n + 148 * 16 - 1) / (148 * 16);
+    if (vt > kTile) vt = kTile;
+    if (vt < 1) vt = 1;
+    const size_t smem = sizeof(uint32_t) * dim * (W + 1) + sizeof(float) * warps * vt * (dim + 1);
+    const long long tiles = (n + vt - 1) / vt;
     long long grid = (tiles + warps - 1) / warps;
     if (grid > 148 * 8) grid = 148 * 8;
     const float inv = host_inv_sqrt(dim);
@@ -1232,7 +1238,7 @@ int tqb_residual_sketch(int32_t dim, const uint32_t* rbits, const void* original
         if (e != cudaSuccess) { set_cuda_error(e); return TQB_ERR_CUDA; }                                        \
         residual_sketch_kernel<EPL, T><<<(int)grid, warps * 32, smem, s>>>(                                       \
             (const T*)original, dequantized, n, rbits, signs, norms, rows_per_group, out_group_stride,           \
-            out_row_offset, inv);                                                                                \
+            out_row_offset, inv, (int)vt);                                                                       \
     }) } while (0)
     if (dtype == TQB_F32) TQB_SKETCH(float);
     else if (dtype == TQB_F16) TQB_SKETCH(__half);
