@@ -9,9 +9,11 @@
 //                        query, each rounded once to f16.  The scores are taken 128 tokens (two tiles) at a time: eight
 //                        MMAs (16 dims each, N = 128) into a 128 x 128 f32 accumulator in tensor memory,
 //                        double-buffered, so the tensor cores score step j + 1 while the softmax threads work on step j.
-//   O_G += P V           P = exp2(s - m) as f16 (K-major A operand, written by the softmax threads), V dequantized with
-//                        its scale to f16 (MN-major B operand), N = 128 dims, one 128 x 128 f32 accumulator per
-//                        softmax group G.
+//   O_G += P V           P = exp2(s - m) as f16, handed to the tensor cores through TENSOR MEMORY: a softmax thread
+//                        overwrites the first 32 of the 64 score columns it has just read with its row of P (two f16
+//                        per column) and the MMA takes its A operand from there (no shared-memory round trip); V
+//                        dequantized with its scale to f16 (MN-major B operand in shared memory), N = 128 dims, one
+//                        128 x 128 f32 accumulator per softmax group G.
 // Two softmax groups of four warps each: group G takes tile 2 j + G of every step (columns 64 G .. 64 G + 63 of the
 // step's scores) with its own running (max, sum), P buffer and O accumulator - two independent online softmaxes over
 // the even and the odd tiles, merged once at the end like two split-K partitions.  Thread r of a group owns query
@@ -37,6 +39,10 @@ constexpr int kRows = 128;          // query rows per CTA
 constexpr int kTile = 64;           // cache tokens per step
 constexpr int kD = 128;
 constexpr int kThreads = 15 * 32;
+// P = exp2(s - m) goes to the tensor cores through tensor memory: a softmax thread overwrites the first 32 columns of
+// the 64 score columns it has just read with its row of P (two f16 per column), and the P V product takes its A operand
+// from there.  (false: through shared memory, as a K-major swizzled tile.)
+constexpr bool kPTmem = true;
 constexpr float kNegBig = -1.0e30f;
 
 // shared-memory map (bytes from a 1024-aligned base)
@@ -129,6 +135,17 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint6
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t"
         "}\n"
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+// The same with the A operand in tensor memory: lane = row, one 32-bit column holds two consecutive K elements, so a
+// K = 16 step reads 8 columns starting at a_tmem.
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t"
+        "}\n"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
@@ -393,8 +410,13 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_umma_kernel(ChunkArgs a) {
                     // O_G += P V : four k-steps of 16 tokens
                     const uint64_t pv = dP + (uint64_t)(G * (16384 >> 4)), vv = dV + (uint64_t)(G * (16384 >> 4));
 #pragma unroll
-                    for (int kk = 0; kk < 4; ++kk)
-                        umma_f16(tmemO + G * kD, pv + (uint64_t)((kk * 32) >> 4), vv + (uint64_t)((kk * 2048) >> 4), idescO, (j | kk) ? 1u : 0u);
+                    for (int kk = 0; kk < 4; ++kk) {
+                        if (kPTmem)
+                            umma_f16_ts(tmemO + G * kD, tmemS + (j & 1) * 2 * kTile + G * kTile + kk * 8, vv + (uint64_t)((kk * 2048) >> 4),
+                                        idescO, (j | kk) ? 1u : 0u);
+                        else
+                            umma_f16(tmemO + G * kD, pv + (uint64_t)((kk * 32) >> 4), vv + (uint64_t)((kk * 2048) >> 4), idescO, (j | kk) ? 1u : 0u);
+                    }
                     umma_commit(bar + kVEmpty + 8 * G);      // frees this V stage and P buffer when the MMAs issued so far are done
                 }
             }
@@ -462,10 +484,14 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_umma_kernel(ChunkArgs a) {
                 ls4[t & 3] += p[t];
             }
             l_run = l_run * resc + ((ls4[0] + ls4[1]) + (ls4[2] + ls4[3]));
-            // the group's P V product of the previous step must be done: it read the P buffer written below and wrote
-            // the O accumulator rescaled here
+            // The group's P V product of the previous step must be done: it wrote the O accumulator rescaled here (and,
+            // with P in shared memory, read the P buffer written below).  The wait is also the flow control of the
+            // p_full barrier: without it a group could arrive for steps j and j + 1 before the issuing thread has looked
+            // at step j, and a parity wait cannot tell a phase from the one two later (seen as bounded waits running
+            // out when it was made conditional on a rescale).
+            const bool rescale = j > 0 && __any_sync(0xffffffffu, resc != 1.0f);
             if (j > 0 && !__all_sync(0xffffffffu, mbar_wait(bar + kVEmpty + 8 * G, (j - 1) & 1, (3u << 24) | (3u << 16) | (unsigned)j))) { ok = false; break; }
-            if (j > 0 && __any_sync(0xffffffffu, resc != 1.0f)) {
+            if (rescale) {
                 // rescale this row of O (warp-collective tensor-memory accesses: every lane takes part with its own factor)
                 tc_fence_after();
 #pragma unroll
@@ -479,16 +505,25 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_umma_kernel(ChunkArgs a) {
                 }
                 tmem_wait_st();
             }
-            // P -> shared memory (K-major A operand: row r, 64 tokens = 128 bytes, swizzled 16-byte chunks)
-            unsigned char* pt = sm + kOffP + G * 16384;
+            if (kPTmem) {
+                // P -> tensor memory: column c of the row holds tokens 2c (low half) and 2c + 1
+                uint32_t w[32];
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                uint32_t w[4];
+                for (int c = 0; c < 32; ++c) w[c] = h2_as_u32(__floats2half2_rn(p[2 * c], p[2 * c + 1]));
+                tmem_st32(tmemS + lane_base + sb * 2 * kTile + G * kTile, w);
+                tmem_wait_st();
+            } else {
+                // P -> shared memory (K-major A operand: row r, 64 tokens = 128 bytes, swizzled 16-byte chunks)
+                unsigned char* pt = sm + kOffP + G * 16384;
 #pragma unroll
-                for (int e = 0; e < 4; ++e) w[e] = h2_as_u32(__floats2half2_rn(p[8 * c + 2 * e], p[8 * c + 2 * e + 1]));
-                *reinterpret_cast<uint4*>(pt + sw128(r, c)) = make_uint4(w[0], w[1], w[2], w[3]);
+                for (int c = 0; c < 8; ++c) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) w[e] = h2_as_u32(__floats2half2_rn(p[8 * c + 2 * e], p[8 * c + 2 * e + 1]));
+                    *reinterpret_cast<uint4*>(pt + sw128(r, c)) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+                fence_async_smem();
             }
-            fence_async_smem();
             tc_fence_before();
             mbar_arrive(bar + kPFull + 8 * G);
         }
