@@ -129,7 +129,7 @@ def test_partition_choosers_are_host_functions():
     from turboquant_b200._lib import lib
     assert lib.tqb_decode_num_partitions(512, 8192) == 2        # 2 x 592 / 512 = 2, partitions of 4096 tokens
     assert lib.tqb_decode_num_partitions(64, 8192) == 9         # 592 / 64 rounded down: 576 CTAs, one wave
-    assert lib.tqb_decode_num_partitions(8, 131072) == 148      # two residencies, 885 tokens each
+    assert lib.tqb_decode_num_partitions(8, 131072) == 74       # one residency: 148 partitions would need the two-level merge twice as long
     assert lib.tqb_decode_num_partitions(8, 100) == 2           # never below 64 tokens per partition
     assert lib.tqb_decode_num_partitions(1000, 8192) == 1
     assert lib.tqb_decode_num_partitions_overlapped(512, 8192) == 1
