@@ -114,8 +114,13 @@ class FusedSequenceParallelDecoder:
         check(lib.tqb_peer_exchange_handle(self._x, mine))
         handles = [None] * self.world
         dist.all_gather_object(handles, bytes(mine.raw), group=group)
-        check(lib.tqb_peer_exchange_connect(self._x, b"".join(handles)))
-        dist.barrier(group=group)
+        status = int(lib.tqb_peer_exchange_connect(self._x, b"".join(handles)))
+        # every rank learns whether every rank could map its peers' buffers, so that a failure on one rank raises on
+        # all of them instead of leaving the others waiting in their next collective
+        statuses = [None] * self.world
+        dist.all_gather_object(statuses, status, group=group)
+        for st in statuses:
+            check(st)
         self.out = torch.empty((self.hq, d), dtype=out_dtype, device=dev)
 
     def __del__(self):
