@@ -137,3 +137,23 @@ def test_partition_choosers_are_host_functions():
     assert lib.tqb_decode_num_partitions_overlapped(8, 131072) == 18
     assert lib.tqb_decode_num_partitions_overlapped(8, 1024) == 1
     assert lib.tqb_decode_num_partitions_overlapped(0, 5) == 1
+
+
+def test_public_header_is_plain_c():
+    """include/tqb200.h is what a foreign-function binding reads: it must compile as C99 on its own (no C++ or CUDA
+    types in the signatures)."""
+    import os
+    import shutil
+    import subprocess
+    import tempfile
+    cc = shutil.which("gcc") or shutil.which("cc")
+    if cc is None:
+        pytest.skip("no C compiler")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    with tempfile.TemporaryDirectory() as td:
+        src = os.path.join(td, "hdr.c")
+        with open(src, "w") as f:
+            f.write('#include "tqb200.h"\nint main(void) { return 0; }\n')
+        res = subprocess.run([cc, "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-fsyntax-only",
+                              "-I", os.path.join(root, "include"), src], capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr
