@@ -157,3 +157,20 @@ def test_public_header_is_plain_c():
         res = subprocess.run([cc, "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-fsyntax-only",
                               "-I", os.path.join(root, "include"), src], capture_output=True, text=True)
     assert res.returncode == 0, res.stderr
+
+
+def test_argument_checks_that_need_no_gpu():
+    """Entry points validate their arguments on the host before they touch the device."""
+    from turboquant_b200._lib import lib
+    x = ctypes.c_void_p()
+    assert lib.tqb_peer_exchange_create(9, 0, 8, 128, ctypes.byref(x)) == 7       # more than 8 ranks
+    assert lib.tqb_peer_exchange_create(2, 2, 8, 128, ctypes.byref(x)) == 7       # rank outside the world
+    assert lib.tqb_peer_exchange_create(2, 0, 0, 128, ctypes.byref(x)) == 7       # no query heads
+    assert lib.tqb_peer_exchange_create(2, 0, 8, 64, ctypes.byref(x)) == 9        # head_dim the pushing kernels do not cover
+    assert lib.tqb_peer_exchange_create(2, 0, 8, 128, None) == 6                  # NULL out pointer
+    assert lib.tqb_pqo_cache_set_overlap(None, 1) == 6
+    assert lib.tqb_peer_exchange_check(None) in (10, 13) or lib.tqb_peer_exchange_timeouts(None) == -1
+    assert lib.tqb_decode_scratch_bytes(0, 128, 4) == 0
+    # tickets (1 + G words per query head, rounded to 256 bytes) + partials + group partials; G = ceil(P / 8) above 16
+    assert lib.tqb_decode_scratch_bytes(64, 128, 4) == 256 + 4 * 64 * 4 * 130
+    assert lib.tqb_decode_scratch_bytes(64, 128, 18) == 1024 + 4 * 64 * (18 + 3) * 130
